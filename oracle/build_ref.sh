@@ -1,0 +1,54 @@
+#!/bin/sh
+# Builds oracle/_ref/libref_oracle.so from the REFERENCE's own C++ CPU ops.
+# Test infrastructure only.  Reads the reference checkout (default
+# /root/reference, override with REFERENCE_ROOT), writes only under
+# oracle/_ref/ (git-ignored; no reference source is ever committed).
+#
+# The reference targets macOS; four mechanical transforms make its CPU path
+# compile with g++ on Linux (each applied to a scratch copy in _ref/src):
+#  1. Accelerate / GCD headers come from oracle/shim (plain-loop stand-ins).
+#  2. Weight constructors say DType::BF16 while every CPU branch reads the
+#     buffers as float; DType::BF16 -> DType::FP32 restores the fp32 CPU engine.
+#     Tensor.cpp is compiled unmodified.
+#  3. The two dispatch_apply(^block) loops in Attention.cpp become
+#     shim_parallel_for(lambda) (g++ has no blocks extension).
+#  4. Alias fix: Tensor copies are shallow, so swiglu() clobbers its gate
+#     argument and h_cache_ aliases every cached hidden state; two clone()
+#     calls give the mathematically intended behaviour.  ALIAS_FIX=0 builds the
+#     as-is variant (_ref/libref_oracle_asis.so) used only to report the delta.
+set -e
+HERE="$(cd "$(dirname "$0")" && pwd)"
+REF="${REFERENCE_ROOT:-/root/reference}"
+ALIAS_FIX="${ALIAS_FIX:-1}"
+CXX_BIN="${ORC_CXX:-g++}"
+[ -d "$REF/cpp/src" ] || { echo "reference checkout not found at $REF" >&2; exit 3; }
+OUT="$HERE/_ref"
+SRC="$OUT/src_fix$ALIAS_FIX"
+mkdir -p "$SRC"
+for f in RMSNorm Activations Positional Loss Transformer Optimizer Attention; do
+  sed 's/DType::BF16/DType::FP32/g' "$REF/cpp/src/$f.cpp" > "$SRC/$f.cpp"
+done
+cp "$REF/cpp/src/Tensor.cpp" "$SRC/Tensor.cpp"
+python3 - "$SRC/Attention.cpp" <<'PY'
+import re, sys
+p = sys.argv[1]
+s = open(p).read()
+pat = re.compile(r"dispatch_apply\(\s*batch \* n_h,\s*dispatch_get_global_queue\(DISPATCH_QUEUE_PRIORITY_HIGH, 0\),\s*\^\(size_t bh\) \{")
+s, n = pat.subn("shim_parallel_for(batch * n_h, [&](size_t bh) {", s)
+assert n == 2, f"expected 2 dispatch_apply sites, found {n}"
+open(p, "w").write(s)
+PY
+if [ "$ALIAS_FIX" = "1" ]; then
+  sed -i 's/Tensor gated = gate;/Tensor gated = gate.clone();/' "$SRC/Activations.cpp"
+  sed -i 's/h_cache_.push_back(h);/h_cache_.push_back(h.clone());/g' "$SRC/Transformer.cpp"
+  grep -q 'gate.clone()' "$SRC/Activations.cpp"
+  [ "$(grep -c 'push_back(h.clone())' "$SRC/Transformer.cpp")" = "2" ]
+  LIB="$OUT/libref_oracle.so"
+else
+  LIB="$OUT/libref_oracle_asis.so"
+fi
+$CXX_BIN -std=c++20 -O2 -fopenmp -fPIC -shared -fvisibility=hidden -ffp-contract=off \
+  -include chrono -include string -include numeric -include cstring -include thread \
+  -I"$HERE/shim" -I"$REF/cpp/include" \
+  "$SRC"/*.cpp "$HERE/shim/bridge_cpu_stub.cpp" "$HERE/ref_driver.cpp" -o "$LIB" -lpthread
+echo "built $LIB"
