@@ -1,0 +1,237 @@
+/*
+ * b200_bridge.h -- C ABI of the B200 (sm_100a) backend for the decoder-block
+ * hot path of the reference C++ training engine.
+ *
+ * The reference talks to its GPU backend through the free functions of
+ * `namespace metal_bridge` (cpp/include/gpu_kernel/MetalBridge.hpp:14-147).
+ * Every compute entry point below replaces one of those functions; the
+ * citation beside each declaration names the interface it stands in for.
+ * Differences that are deliberate:
+ *   - every call returns a status code (the reference prints and returns void);
+ *   - the element type is an explicit argument (the reference's pointers are
+ *     nominally float* while its shaders read bf16);
+ *   - pointers are DEVICE pointers and work is enqueued on the context's
+ *     stream; the host-pointer behaviour of the reference interface (caller
+ *     passes host buffers, results are visible after end_scope) is provided by
+ *     the b200_host_* calls at the end and by the C++ `namespace metal_bridge`
+ *     adaptor built on them (csrc/metal_bridge_shim.cpp).
+ *
+ * All matrices are row-major.  Plain C: no C++ or torch types cross this
+ * boundary.  Functions are not thread-safe per context (the reference
+ * backend is single-threaded with file-static state).
+ */
+#ifndef B200_BRIDGE_H
+#define B200_BRIDGE_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct b200_ctx b200_ctx;
+typedef struct b200_model b200_model;
+
+typedef enum { B200_F32 = 0, B200_BF16 = 1 } b200_dtype;
+
+enum {
+  B200_OK = 0,
+  B200_ERR_INVALID = -1,     /* bad argument (null pointer, shape, alignment) */
+  B200_ERR_CUDA = -2,        /* a CUDA runtime/driver call failed */
+  B200_ERR_UNSUPPORTED = -3, /* shape/dtype combination has no kernel */
+  B200_ERR_NOMEM = -4,
+  B200_ERR_DEVICE_WAIT = -5, /* a bounded device-side wait gave up */
+  B200_ERR_COMM = -6         /* NCCL failure */
+};
+
+/* ---- lifecycle (metal_bridge::initialize / is_available, MetalBridge.hpp:20-21) */
+int b200_init(int device, b200_ctx **out);
+int b200_destroy(b200_ctx *ctx);
+int b200_is_available(void);
+const char *b200_last_error(const b200_ctx *ctx);
+/* cudaStream_t the context enqueues on, as an opaque pointer. */
+void *b200_stream(b200_ctx *ctx);
+/* Use a caller-owned stream (NULL restores the context's own stream). */
+int b200_set_stream(b200_ctx *ctx, void *cuda_stream);
+/* One stream synchronise; also surfaces device-side wait failures.
+ * (metal_bridge::end_scope, MetalBridge.hpp:29-30) */
+int b200_sync(b200_ctx *ctx);
+/* Number of kernels this library has launched on the context since creation. */
+uint64_t b200_launch_count(const b200_ctx *ctx);
+
+/* ---- device memory (the reference wraps host pages zero-copy; a discrete GPU needs mirrors) */
+int b200_malloc(b200_ctx *ctx, size_t bytes, void **dptr);
+int b200_free(b200_ctx *ctx, void *dptr);
+int b200_memcpy_h2d(b200_ctx *ctx, void *dst_dev, const void *src_host, size_t bytes);
+int b200_memcpy_d2h(b200_ctx *ctx, void *dst_host, const void *src_dev, size_t bytes);
+/* metal_bridge::fill_zero_async / copy_buffer_async (MetalBridge.hpp:75-76) */
+int b200_fill_zero(b200_ctx *ctx, void *dptr, size_t bytes);
+int b200_copy(b200_ctx *ctx, void *dst_dev, const void *src_dev, size_t bytes);
+/* dtype conversion between fp32 and bf16 device arrays (n elements). */
+int b200_convert(b200_ctx *ctx, const void *src, b200_dtype src_dtype, void *dst, b200_dtype dst_dtype, size_t n);
+/* Seeded N(0, std) fill of a device array (synthetic weights for benchmarks). */
+int b200_fill_normal(b200_ctx *ctx, void *dptr, b200_dtype dtype, size_t n, uint64_t seed, float std);
+
+/* ---- GEMM: C[M,N] (+)= op(A)[M,K] * op(B)[K,N]
+ * metal_bridge::gemm_bf16 (MetalBridge.hpp:39-42); with trans_b also
+ * gemm_proj_trans_b (:121-122); with trans_a also gemm_backward (:119-120).
+ * trans_a: A is stored [K,M]; trans_b: B is stored [N,K].  in_dtype is the
+ * type of A and B, out_dtype of C.  accumulate != 0 adds into C. bf16 inputs
+ * run on the tcgen05 tensor-core kernel (fp32 accumulation in tensor memory);
+ * fp32 inputs run an fp32 CUDA-core kernel that meets the 1e-4 contract. */
+int b200_gemm(b200_ctx *ctx, const void *A, const void *B, void *C, size_t M, size_t N, size_t K,
+              int trans_a, int trans_b, int accumulate, b200_dtype in_dtype, b200_dtype out_dtype);
+
+/* ---- RMSNorm
+ * metal_bridge::rms_norm_forward (MetalBridge.hpp:60-61). rstd_out (optional,
+ * fp32 [rows]) receives 1/sqrt(mean(x^2)+eps) for reuse by the backward. */
+int b200_rms_norm_forward(b200_ctx *ctx, const void *x, void *y, const void *weight, float *rstd_out,
+                          float eps, size_t rows, size_t dims, b200_dtype dtype);
+/* metal_bridge::rms_norm_backward (MetalBridge.hpp:62-64). grad_weight is
+ * optional fp32 [dims] and is ACCUMULATED into, as the reference does. */
+int b200_rms_norm_backward(b200_ctx *ctx, const void *grad_output, const void *x, const void *weight,
+                           void *grad_input, float *grad_weight, float eps, size_t rows, size_t dims,
+                           b200_dtype dtype);
+/* metal_bridge::fused_add_norm (MetalBridge.hpp:79-81): x_residual += residual; output = rmsnorm(x_residual)*weight */
+int b200_fused_add_norm(b200_ctx *ctx, void *x_residual, const void *residual, const void *weight, void *output,
+                        size_t rows, size_t dims, float eps, b200_dtype dtype);
+/* metal_bridge::fused_backward_add_norm (MetalBridge.hpp:82-85): grad_input = rmsnorm_bwd(grad_output, x, weight) + residual_grad */
+int b200_fused_backward_add_norm(b200_ctx *ctx, const void *grad_output, const void *x, const void *weight,
+                                 const void *residual_grad, void *grad_input, size_t rows, size_t dims, float eps,
+                                 b200_dtype dtype);
+
+/* ---- RoPE on [batch, heads, seq, head_dim], interleaved pairs, in place.
+ * Tables are fp32 [seq, head_dim/2].
+ * metal_bridge::rope_forward (MetalBridge.hpp:130-133) / rope_backward (:68-69). */
+int b200_rope_tables(b200_ctx *ctx, float *cos_table, float *sin_table, size_t max_seq, size_t head_dim, float base);
+int b200_rope_forward(b200_ctx *ctx, void *q, void *k, const float *cos_table, const float *sin_table,
+                      size_t batch, size_t q_heads, size_t kv_heads, size_t seq_len, size_t head_dim, b200_dtype dtype);
+int b200_rope_backward(b200_ctx *ctx, void *grad, const float *cos_table, const float *sin_table, size_t batch,
+                       size_t heads, size_t seq_len, size_t head_dim, b200_dtype dtype);
+
+/* ---- SwiGLU: metal_bridge::swiglu_forward / swiglu_backward (MetalBridge.hpp:65-67) */
+int b200_swiglu_forward(b200_ctx *ctx, const void *gate, const void *up, void *out, size_t n, b200_dtype dtype);
+int b200_swiglu_backward(b200_ctx *ctx, const void *grad_output, const void *gate, const void *up, void *grad_gate,
+                         void *grad_up, size_t n, b200_dtype dtype);
+/* metal_bridge::fused_swiglu_gemm (MetalBridge.hpp:44-46): C[M,N] = (silu(gate)*up)[M,K] * B[K,N].
+ * scratch must hold M*K elements of dtype. */
+int b200_fused_swiglu_gemm(b200_ctx *ctx, const void *gate, const void *up, const void *B, void *C, void *scratch,
+                           size_t M, size_t N, size_t K, b200_dtype dtype);
+
+/* ---- metal_bridge::residual_add (MetalBridge.hpp:78): a += b */
+int b200_residual_add(b200_ctx *ctx, void *a, const void *b, size_t n, b200_dtype dtype);
+
+/* ---- head split / merge: metal_bridge::reshape_to_4d / reshape_to_3d (MetalBridge.hpp:123-129) */
+int b200_reshape_to_4d(b200_ctx *ctx, const void *src, void *dst, size_t batch, size_t heads, size_t seq_len,
+                       size_t head_dim, b200_dtype dtype);
+int b200_reshape_to_3d(b200_ctx *ctx, const void *src, void *dst, size_t batch, size_t heads, size_t seq_len,
+                       size_t head_dim, b200_dtype dtype);
+
+/* ---- causal GQA attention
+ * metal_bridge::flash_attn_fwd (MetalBridge.hpp:49-51).  Q [B,nH,S,hd], K/V
+ * [B,nKV,S,hd], O [B,S,nH*hd] (the caller's contract, cpp/src/Attention.cpp:211,227,282).
+ * lse (optional fp32 [B,nH,S]) receives log-sum-exp of the scaled scores. */
+int b200_flash_attn_fwd(b200_ctx *ctx, const void *Q, const void *K, const void *V, void *O, float *lse,
+                        size_t batch, size_t n_heads, size_t n_kv, size_t seq_len, size_t head_dim, b200_dtype dtype);
+/* metal_bridge::fused_attn_bwd (MetalBridge.hpp:54-57).  dO [B,S,nH*hd]; dQ
+ * like Q, dK/dV like K/V (summed over the nH/nKV query heads of each kv head). */
+int b200_fused_attn_bwd(b200_ctx *ctx, const void *Q, const void *K, const void *V, const void *dO, void *dQ,
+                        void *dK, void *dV, size_t batch, size_t n_heads, size_t n_kv, size_t seq_len,
+                        size_t head_dim, b200_dtype dtype);
+
+/* ---- embedding gather: metal_bridge::embedding_forward (MetalBridge.hpp:86-88) */
+int b200_embedding_forward(b200_ctx *ctx, const uint32_t *token_ids, const void *table, void *output,
+                           size_t total_tokens, size_t hidden_dim, size_t vocab_size, b200_dtype dtype);
+/* scatter-add of hidden-state grads into the fp32 table grad (cpp/src/Transformer.cpp:524-537). */
+int b200_embedding_backward(b200_ctx *ctx, const uint32_t *token_ids, const void *grad_hidden, float *grad_table,
+                            size_t total_tokens, size_t hidden_dim, size_t vocab_size, b200_dtype dtype);
+
+/* ---- metal_bridge::cross_entropy (MetalBridge.hpp:89-91): mean loss into the
+ * device float *loss_out and, when grad_logits != NULL, (softmax - onehot)/tokens.
+ * grad_logits has dtype `dtype` and may alias logits. */
+int b200_cross_entropy(b200_ctx *ctx, const void *logits, const uint32_t *targets, float *loss_out,
+                       void *grad_logits, size_t total_tokens, size_t vocab_size, b200_dtype dtype);
+
+/* ---- metal_bridge::adamw_step (MetalBridge.hpp:92-98). param/m/v fp32; grad
+ * fp32; bf16_shadow (optional) receives the updated parameter rounded to bf16. */
+typedef struct {
+  float lr, beta1, beta2, eps, weight_decay, bias_correction1, bias_correction2;
+} b200_adamw_params;
+int b200_adamw_step(b200_ctx *ctx, float *param, const float *grad, float *m, float *v, void *bf16_shadow,
+                    size_t n, const b200_adamw_params *p);
+
+/* ======================= device-resident training engine =======================
+ * The reference composes the ops above in Transformer::forward / ::backward
+ * (cpp/src/Transformer.cpp:90-197, 571-657) with one h_in kept per layer and
+ * everything else recomputed.  The engine keeps activations in HBM instead
+ * (no recompute) and uses fused [Wq|Wk|Wv] and [Wgate|Wup] weights; parameter
+ * import/export uses the reference's own per-tensor layout:
+ *   embedding[V,H]; per layer attn_norm_w[H], Wq[H,nH*hd], Wk[H,nKV*hd],
+ *   Wv[H,nKV*hd], Wo[nH*hd,H], ffn_norm_w[H], w_gate[H,I], w_up[H,I],
+ *   w_down[I,H]; final_norm_w[H]; output_projection[H,V]   (all [in,out]). */
+typedef struct {   /* mirrors ModelConfig, cpp/include/TransformerConfig.hpp:16-98 */
+  size_t vocab_size, hidden_dim, intermediate_dim, n_layers, n_heads, n_kv_heads, head_dim, max_seq_len;
+  float rope_base, rms_norm_eps;
+} b200_model_config;
+
+int b200_model_create(b200_ctx *ctx, const b200_model_config *cfg, b200_dtype compute_dtype, size_t max_batch,
+                      int with_optimizer, b200_model **out);
+int b200_model_destroy(b200_model *m);
+size_t b200_model_param_count(const b200_model *m);
+int b200_model_load_params(b200_model *m, const float *host_flat);
+int b200_model_read_params(b200_model *m, float *host_flat);
+int b200_model_read_grads(b200_model *m, float *host_flat);
+int b200_model_init_synthetic(b200_model *m, uint64_t seed, float std);
+/* Transformer::forward (cpp/src/Transformer.cpp:90-197): logits_out (optional, device, compute dtype, [B*S,V]). */
+int b200_model_forward(b200_model *m, const int32_t *dev_tokens, size_t batch, size_t seq_len, void *logits_out);
+/* forward + CrossEntropyLoss + Transformer::backward: all weight grads (fp32) and the mean loss (device float). */
+int b200_model_loss_and_grads(b200_model *m, const int32_t *dev_tokens, const int32_t *dev_targets, size_t batch,
+                              size_t seq_len, float *dev_loss);
+/* AdamWOptimizer::step over every registered parameter (cpp/src/Optimizer.cpp:139-149);
+ * norm weights are not trained (cpp/src/Trainer.cpp:195-205). */
+int b200_model_adamw_step(b200_model *m, float lr, float beta1, float beta2, float eps, float weight_decay);
+/* One whole training step from HOST buffers: copies tokens/targets in, runs
+ * forward, loss, backward, (gradient all-reduce when data-parallel), AdamW,
+ * copies the loss out and synchronises. (Trainer::train step body, cpp/src/Trainer.cpp:263-378) */
+int b200_model_train_step_host(b200_model *m, const int32_t *host_tokens, const int32_t *host_targets, size_t batch,
+                               size_t seq_len, float lr, float beta1, float beta2, float eps, float weight_decay,
+                               float *host_loss);
+/* Same with tokens already on the device; loss stays on the device. */
+int b200_model_train_step(b200_model *m, const int32_t *dev_tokens, const int32_t *dev_targets, size_t batch,
+                          size_t seq_len, float lr, float beta1, float beta2, float eps, float weight_decay,
+                          float *dev_loss);
+/* One decoder layer through the engine's fused path, for parity tests:
+ * h_out = layer(h_in); and the backward given grad_out (TransformerLayer::backward,
+ * cpp/src/Transformer.cpp:322-474).  h_in/h_out/grads in compute dtype, [B*S,H]. */
+int b200_model_layer_forward(b200_model *m, size_t layer, const void *h_in, void *h_out, size_t batch, size_t seq_len);
+int b200_model_layer_backward(b200_model *m, size_t layer, const void *grad_out, void *grad_h_in, size_t batch,
+                              size_t seq_len);
+
+/* ---- data parallel (no counterpart in the reference, which is single-device):
+ * replicas all-reduce (average) fp32 gradient buckets with NCCL on a side
+ * stream as soon as each layer's weight gradients are enqueued. */
+int b200_dp_unique_id(void *out128);                     /* rank 0: ncclGetUniqueId */
+int b200_dp_init(b200_model *m, const void *unique_id128, int rank, int world);
+int b200_dp_shutdown(b200_model *m);
+
+/* ======================= host-pointer calls (the reference's calling convention) =========
+ * Same semantics as the device calls, but every pointer is a HOST pointer:
+ * inputs are copied to the device, the kernel runs, outputs are copied back
+ * and the stream is synchronised before returning (the reference's behaviour
+ * outside a begin_scope/end_scope pair, cpp/src/gpu_kernel/MetalBridge.mm:1384-1406). */
+int b200_host_gemm(b200_ctx *ctx, const void *A, const void *B, void *C, size_t M, size_t N, size_t K, int trans_a,
+                   int trans_b, b200_dtype dtype);
+int b200_host_rms_norm_forward(b200_ctx *ctx, const float *x, float *y, const float *w, float eps, size_t rows, size_t dims);
+int b200_host_flash_attn_fwd(b200_ctx *ctx, const float *Q, const float *K, const float *V, float *O, size_t batch,
+                             size_t n_heads, size_t n_kv, size_t seq_len, size_t head_dim);
+int b200_host_fused_attn_bwd(b200_ctx *ctx, const float *Q, const float *K, const float *V, const float *dO, float *dQ,
+                             float *dK, float *dV, size_t batch, size_t n_heads, size_t n_kv, size_t seq_len,
+                             size_t head_dim);
+int b200_host_cross_entropy(b200_ctx *ctx, const float *logits, const uint32_t *targets, float *loss_out,
+                            float *grad_logits, size_t total_tokens, size_t vocab_size);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200_BRIDGE_H */

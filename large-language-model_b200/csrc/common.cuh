@@ -1,0 +1,135 @@
+// Shared declarations of the B200 backend: context, status handling, small
+// device helpers.  Internal to csrc/; the public surface is include/b200_bridge.h.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <cstdint>
+#include <cstdio>
+#include <cstring>
+#include <string>
+
+#include "../../include/b200_bridge.h"
+
+typedef __nv_bfloat16 bf16;
+
+struct b200_ctx {
+  int device = 0;
+  int sm_count = 148;
+  cudaStream_t own_stream = nullptr;
+  cudaStream_t stream = nullptr;
+  uint64_t launches = 0;
+  // device-side status word: kernels with bounded waits record a give-up here
+  int *dev_status = nullptr;
+  int *host_status = nullptr;  // pinned
+  char err[512] = {0};
+  // workspace for split reductions etc. (grown on demand, never shrunk)
+  void *scratch = nullptr;
+  size_t scratch_bytes = 0;
+};
+
+int b200_fail(b200_ctx *ctx, int code, const char *fmt, ...);
+// Returns device scratch of at least `bytes` (reallocates if needed; synchronises first when it must grow).
+void *b200_scratch(b200_ctx *ctx, size_t bytes);
+
+#define B200_CUDA(ctx, call)                                                        \
+  do {                                                                              \
+    cudaError_t e_ = (call);                                                        \
+    if (e_ != cudaSuccess)                                                          \
+      return b200_fail((ctx), B200_ERR_CUDA, "%s failed: %s (%s:%d)", #call,        \
+                       cudaGetErrorString(e_), __FILE__, __LINE__);                 \
+  } while (0)
+
+#define B200_LAUNCHED(ctx)                                                          \
+  do {                                                                              \
+    (ctx)->launches++;                                                              \
+    cudaError_t e_ = cudaGetLastError();                                            \
+    if (e_ != cudaSuccess)                                                          \
+      return b200_fail((ctx), B200_ERR_CUDA, "kernel launch failed: %s (%s:%d)",    \
+                       cudaGetErrorString(e_), __FILE__, __LINE__);                 \
+  } while (0)
+
+#define B200_REQUIRE(ctx, cond, msg)                                                \
+  do {                                                                              \
+    if (!(cond)) return b200_fail((ctx), B200_ERR_INVALID, "%s (%s)", msg, #cond);  \
+  } while (0)
+
+static inline size_t dtype_size(b200_dtype d) { return d == B200_BF16 ? 2 : 4; }
+
+// ---- device helpers ------------------------------------------------------
+__device__ __forceinline__ float to_f(float v) { return v; }
+__device__ __forceinline__ float to_f(bf16 v) { return __bfloat162float(v); }
+template <class T> __device__ __forceinline__ T from_f(float v);
+template <> __device__ __forceinline__ float from_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ bf16 from_f<bf16>(float v) { return __float2bfloat16_rn(v); }
+
+// 16-byte vector of T: 4 floats or 8 bf16.
+template <class T> struct Vec16 {
+  static constexpr int N = 16 / sizeof(T);
+  uint4 raw;
+  __device__ __forceinline__ void load(const T *p) { raw = *reinterpret_cast<const uint4 *>(p); }
+  __device__ __forceinline__ void store(T *p) const { *reinterpret_cast<uint4 *>(p) = raw; }
+  __device__ __forceinline__ void unpack(float *f) const {
+    const T *e = reinterpret_cast<const T *>(&raw);
+#pragma unroll
+    for (int i = 0; i < N; ++i) f[i] = to_f(e[i]);
+  }
+  __device__ __forceinline__ void pack(const float *f) {
+    T *e = reinterpret_cast<T *>(&raw);
+#pragma unroll
+    for (int i = 0; i < N; ++i) e[i] = from_f<T>(f[i]);
+  }
+};
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+// Block-wide sum; `red` is shared float[32]. All threads get the result.
+__device__ __forceinline__ float block_sum(float v, float *red) {
+  int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) red[w] = v;
+  __syncthreads();
+  float t = (lane < nw) ? red[lane] : 0.f;
+  return warp_sum(t);
+}
+__device__ __forceinline__ float block_max(float v, float *red) {
+  int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  v = warp_max(v);
+  __syncthreads();
+  if (lane == 0) red[w] = v;
+  __syncthreads();
+  float t = (lane < nw) ? red[lane] : -INFINITY;
+  return warp_max(t);
+}
+
+// ---- internal launchers shared between translation units -------------------
+int gemm_simt_launch(b200_ctx *ctx, const void *A, const void *B, void *C, size_t M, size_t N, size_t K, int ta,
+                     int tb, int acc, b200_dtype in_dt, b200_dtype out_dt, size_t lda, size_t ldb, size_t ldc);
+int gemm_tc_launch(b200_ctx *ctx, const void *A, const void *B, void *C, size_t M, size_t N, size_t K, int ta, int tb,
+                   int acc, b200_dtype out_dt, size_t lda, size_t ldb, size_t ldc);
+bool gemm_tc_supported(const void *A, const void *B, const void *C, size_t M, size_t N, size_t K, size_t lda,
+                       size_t ldb, size_t ldc, b200_dtype out_dt);
+// Strided general form used by the engine (leading dimensions in elements).
+int b200_gemm_ld(b200_ctx *ctx, const void *A, const void *B, void *C, size_t M, size_t N, size_t K, int ta, int tb,
+                 int acc, b200_dtype in_dt, b200_dtype out_dt, size_t lda, size_t ldb, size_t ldc);
+
+// Attention on strided head layouts (element strides; head_dim contiguous).
+struct AttnStrides {
+  long long q_b, q_h, q_s;     // query  (batch, head, seq) strides
+  long long k_b, k_h, k_s;     // key
+  long long v_b, v_h, v_s;     // value
+  long long o_b, o_h, o_s;     // output / dO
+};
+int attn_fwd_launch(b200_ctx *ctx, const void *Q, const void *K, const void *V, void *O, float *lse, size_t B,
+                    size_t nH, size_t nKV, size_t S, size_t hd, const AttnStrides &st, b200_dtype dt);
+int attn_bwd_launch(b200_ctx *ctx, const void *Q, const void *K, const void *V, const void *O, const void *dO,
+                    const float *lse, void *dQ, void *dK, void *dV, size_t B, size_t nH, size_t nKV, size_t S,
+                    size_t hd, const AttnStrides &st, const AttnStrides &gst, b200_dtype dt);

@@ -1,0 +1,526 @@
+// Device-resident training engine for the decoder-only GQA transformer: the B200
+// counterpart of Transformer::forward / ::backward, CrossEntropyLoss and AdamW
+// (cpp/src/Transformer.cpp:90-197, 322-474, 571-657; cpp/src/Loss.cpp; cpp/src/Optimizer.cpp).
+//
+// What is kept from the reference: the maths of every op, the double RMSNorm in front of
+// the attention projections (cpp/src/Attention.cpp:192-194), interleaved RoPE, [in,out]
+// weights, untied output projection, untrained norm weights (cpp/src/Trainer.cpp:195-205),
+// mean cross-entropy.  What is B200-first: activations stay in HBM (the reference keeps
+// one tensor per layer and recomputes each layer's forward up to three times in
+// backward), Q/K/V and gate/up projections are single GEMMs on fused weights, attention
+// reads the token-major QKV rows directly (no head split/merge passes), gradients are
+// fp32 and all-reduced per layer on a side stream while backward continues.
+#include "common.cuh"
+#include <dlfcn.h>
+#include <vector>
+
+int rope_strided(b200_ctx *, void *, const float *, const float *, size_t, size_t, size_t, size_t, long long,
+                 long long, long long, b200_dtype, bool);
+int swiglu_fwd_strided(b200_ctx *, const void *, const void *, void *, size_t, size_t, size_t, size_t, b200_dtype);
+int swiglu_bwd_strided(b200_ctx *, const void *, const void *, const void *, void *, void *, size_t, size_t, size_t,
+                       size_t, size_t, b200_dtype);
+int add_norm_oop(b200_ctx *, const void *, const void *, void *, const void *, void *, size_t, size_t, float,
+                 b200_dtype);
+int convert2d(b200_ctx *, const void *, b200_dtype, void *, b200_dtype, size_t, size_t, size_t, size_t);
+int fill_const(b200_ctx *, void *, b200_dtype, size_t, float);
+
+// ---- NCCL, resolved at run time from the library already in the process (or libnccl.so.2) ----
+namespace nccl {
+typedef struct ncclComm *comm_t;
+typedef struct { char internal[128]; } unique_id;
+typedef int (*GetUniqueId_t)(unique_id *);
+typedef int (*CommInitRank_t)(comm_t *, int, unique_id, int);
+typedef int (*CommDestroy_t)(comm_t);
+typedef int (*AllReduce_t)(const void *, void *, size_t, int, int, comm_t, cudaStream_t);
+typedef const char *(*GetErrorString_t)(int);
+typedef int (*CommGetAsyncError_t)(comm_t, int *);
+constexpr int kFloat32 = 7, kSum = 0, kAvg = 4;
+struct Api {
+  void *handle = nullptr;
+  GetUniqueId_t GetUniqueId = nullptr; CommInitRank_t CommInitRank = nullptr; CommDestroy_t CommDestroy = nullptr;
+  AllReduce_t AllReduce = nullptr; GetErrorString_t GetErrorString = nullptr; CommGetAsyncError_t CommGetAsyncError = nullptr;
+  bool ok() const { return GetUniqueId && CommInitRank && CommDestroy && AllReduce; }
+};
+static Api &api() {
+  static Api a;
+  if (!a.handle) {
+    a.handle = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+    if (!a.handle) a.handle = dlopen("libnccl.so", RTLD_NOW | RTLD_GLOBAL);
+    if (a.handle) {
+      a.GetUniqueId = (GetUniqueId_t)dlsym(a.handle, "ncclGetUniqueId");
+      a.CommInitRank = (CommInitRank_t)dlsym(a.handle, "ncclCommInitRank");
+      a.CommDestroy = (CommDestroy_t)dlsym(a.handle, "ncclCommDestroy");
+      a.AllReduce = (AllReduce_t)dlsym(a.handle, "ncclAllReduce");
+      a.GetErrorString = (GetErrorString_t)dlsym(a.handle, "ncclGetErrorString");
+      a.CommGetAsyncError = (CommGetAsyncError_t)dlsym(a.handle, "ncclCommGetAsyncError");
+    }
+  }
+  return a;
+}
+}  // namespace nccl
+
+struct b200_model {
+  b200_ctx *ctx = nullptr;
+  b200_model_config cfg{};
+  b200_dtype dt = B200_F32;
+  size_t max_batch = 0;
+  bool with_opt = false;
+  // sizes
+  size_t H = 0, I = 0, L = 0, V = 0, nH = 0, nKV = 0, hd = 0, Q = 0, KV = 0, QKV = 0;
+  size_t layer_train = 0;   // trainable elements per layer: w_qkv, w_o, w_gate_up, w_down
+  size_t n_train = 0;       // emb + L*layer_train + out_proj
+  size_t n_total = 0;       // + norm weights (2 per layer + final)
+  // flat parameter storage in ENGINE order:
+  //   [emb V*H][layer l: w_qkv H*QKV | w_o Q*H | w_gate_up H*2I | w_down I*H][out_proj H*V][norms: (attn,ffn) per layer, final]
+  void *params = nullptr;    // compute dtype
+  float *master = nullptr;   // fp32 (aliases params in fp32 mode)
+  float *grads = nullptr;    // fp32, same order
+  float *adam_m = nullptr, *adam_v = nullptr;
+  size_t step_count = 0;
+  void *ones = nullptr;      // unit weight of the inner norm
+  float *cos_t = nullptr, *sin_t = nullptr;
+  // activations kept for backward, per layer (compute dtype)
+  std::vector<void *> hs;    // L+1 residual-stream states [M,H]
+  struct Act { void *a1, *a2, *qkv, *o, *h_mid, *ffn_in, *gate_up, *act; float *lse; };
+  std::vector<Act> acts;
+  // workspace
+  void *tmpH = nullptr, *g_act = nullptr, *g_gate_up = nullptr, *g_ffn_in = nullptr, *g_h_mid = nullptr, *g_o = nullptr,
+       *g_qkv = nullptr, *g_a2 = nullptr, *g_a1 = nullptr, *g_ping = nullptr, *g_pong = nullptr, *logits = nullptr,
+       *fh = nullptr;
+  int32_t *d_tokens = nullptr, *d_targets = nullptr;
+  float *d_loss = nullptr;
+  int32_t *pin_tokens = nullptr, *pin_targets = nullptr; float *pin_loss = nullptr;
+  std::vector<void *> allocs;
+  // data parallel
+  nccl::comm_t comm = nullptr;
+  int rank = 0, world = 1;
+  cudaStream_t comm_stream = nullptr;
+  cudaEvent_t ev_grad_ready = nullptr, ev_comm_done = nullptr;
+
+  size_t off_emb() const { return 0; }
+  size_t off_layer(size_t l) const { return V * H + l * layer_train; }
+  size_t off_qkv(size_t l) const { return off_layer(l); }
+  size_t off_o(size_t l) const { return off_layer(l) + H * QKV; }
+  size_t off_gate_up(size_t l) const { return off_o(l) + Q * H; }
+  size_t off_down(size_t l) const { return off_gate_up(l) + H * 2 * I; }
+  size_t off_out() const { return V * H + L * layer_train; }
+  size_t off_attn_norm(size_t l) const { return n_train + 2 * l * H; }
+  size_t off_ffn_norm(size_t l) const { return n_train + (2 * l + 1) * H; }
+  size_t off_final_norm() const { return n_train + 2 * L * H; }
+  void *P(size_t off) const { return (char *)params + off * dtype_size(dt); }
+  float *G(size_t off) const { return grads + off; }
+};
+
+namespace {
+int dalloc(b200_model *m, void **p, size_t bytes) {
+  int rc = b200_malloc(m->ctx, bytes, p);
+  if (rc == B200_OK) m->allocs.push_back(*p);
+  return rc;
+}
+#define TRY(x) do { int rc_ = (x); if (rc_ != B200_OK) return rc_; } while (0)
+
+AttnStrides token_major(const b200_model *m, size_t S) {
+  // fused rows [q (nH*hd) | k (nKV*hd) | v (nKV*hd)] per token; output rows [nH*hd]
+  AttnStrides st;
+  long long ld = (long long)m->QKV;
+  st.q_b = (long long)S * ld; st.q_h = (long long)m->hd; st.q_s = ld;
+  st.k_b = st.q_b; st.k_h = (long long)m->hd; st.k_s = ld;
+  st.v_b = st.q_b; st.v_h = (long long)m->hd; st.v_s = ld;
+  st.o_b = (long long)(S * m->Q); st.o_h = (long long)m->hd; st.o_s = (long long)m->Q;
+  return st;
+}
+}  // namespace
+
+extern "C" int b200_model_create(b200_ctx *ctx, const b200_model_config *cfg, b200_dtype dt, size_t max_batch,
+                                 int with_optimizer, b200_model **out) {
+  B200_REQUIRE(ctx, cfg && out && max_batch > 0, "model_create: bad arguments");
+  B200_REQUIRE(ctx, cfg->n_kv_heads > 0 && cfg->n_kv_heads <= cfg->n_heads && cfg->n_heads % cfg->n_kv_heads == 0,
+               "n_heads must be a multiple of n_kv_heads (cpp/src/Attention.cpp:45-50)");
+  B200_REQUIRE(ctx, cfg->head_dim % 2 == 0 && cfg->hidden_dim > 0 && cfg->vocab_size > 0 && cfg->max_seq_len > 0,
+               "model_create: bad dimensions");
+  b200_model *m = new b200_model();
+  m->ctx = ctx; m->cfg = *cfg; m->dt = dt; m->max_batch = max_batch; m->with_opt = with_optimizer != 0;
+  m->H = cfg->hidden_dim; m->I = cfg->intermediate_dim; m->L = cfg->n_layers; m->V = cfg->vocab_size;
+  m->nH = cfg->n_heads; m->nKV = cfg->n_kv_heads; m->hd = cfg->head_dim;
+  m->Q = m->nH * m->hd; m->KV = m->nKV * m->hd; m->QKV = m->Q + 2 * m->KV;
+  m->layer_train = m->H * m->QKV + m->Q * m->H + m->H * 2 * m->I + m->I * m->H;
+  m->n_train = 2 * m->V * m->H + m->L * m->layer_train;
+  m->n_total = m->n_train + (2 * m->L + 1) * m->H;
+  const size_t es = dtype_size(dt), M = max_batch * cfg->max_seq_len, H = m->H, I = m->I;
+  int rc = B200_OK;
+  auto A = [&](void **p, size_t bytes) { if (rc == B200_OK) rc = dalloc(m, p, bytes); };
+  A(&m->params, m->n_total * es);
+  if (dt == B200_BF16 && m->with_opt) A((void **)&m->master, m->n_total * 4);
+  A((void **)&m->grads, m->n_total * 4);
+  if (m->with_opt) { A((void **)&m->adam_m, m->n_train * 4); A((void **)&m->adam_v, m->n_train * 4); }
+  A(&m->ones, H * es);
+  A((void **)&m->cos_t, cfg->max_seq_len * (m->hd / 2) * 4);
+  A((void **)&m->sin_t, cfg->max_seq_len * (m->hd / 2) * 4);
+  m->hs.resize(m->L + 1, nullptr);
+  for (auto &p : m->hs) A(&p, M * H * es);
+  m->acts.resize(m->L);
+  for (auto &a : m->acts) {
+    A(&a.a1, M * H * es); A(&a.a2, M * H * es); A(&a.qkv, M * m->QKV * es); A(&a.o, M * m->Q * es);
+    A(&a.h_mid, M * H * es); A(&a.ffn_in, M * H * es); A(&a.gate_up, M * 2 * I * es); A(&a.act, M * I * es);
+    A((void **)&a.lse, max_batch * m->nH * cfg->max_seq_len * 4);
+  }
+  A(&m->tmpH, M * H * es); A(&m->g_act, M * I * es); A(&m->g_gate_up, M * 2 * I * es); A(&m->g_ffn_in, M * H * es);
+  A(&m->g_h_mid, M * H * es); A(&m->g_o, M * m->Q * es); A(&m->g_qkv, M * m->QKV * es); A(&m->g_a2, M * H * es);
+  A(&m->g_a1, M * H * es); A(&m->g_ping, M * H * es); A(&m->g_pong, M * H * es); A(&m->logits, M * m->V * es);
+  A(&m->fh, M * H * es);
+  A((void **)&m->d_tokens, M * 4); A((void **)&m->d_targets, M * 4); A((void **)&m->d_loss, 4);
+  if (rc == B200_OK && (cudaMallocHost(&m->pin_tokens, M * 4) != cudaSuccess || cudaMallocHost(&m->pin_targets, M * 4) != cudaSuccess ||
+                        cudaMallocHost(&m->pin_loss, 4) != cudaSuccess))
+    rc = b200_fail(ctx, B200_ERR_NOMEM, "pinned host allocation failed");
+  if (rc == B200_OK) rc = fill_const(ctx, m->ones, dt, H, 1.0f);
+  if (rc == B200_OK) rc = b200_rope_tables(ctx, m->cos_t, m->sin_t, cfg->max_seq_len, m->hd, cfg->rope_base);
+  if (rc == B200_OK) rc = b200_fill_zero(ctx, m->params, m->n_total * es);
+  if (rc == B200_OK) rc = b200_fill_zero(ctx, m->grads, m->n_total * 4);
+  if (rc == B200_OK && m->with_opt) { rc = b200_fill_zero(ctx, m->adam_m, m->n_train * 4); if (!rc) rc = b200_fill_zero(ctx, m->adam_v, m->n_train * 4); }
+  if (rc == B200_OK && !m->master && dt == B200_F32) m->master = (float *)m->params;
+  if (rc != B200_OK) { b200_model_destroy(m); return rc; }
+  *out = m;
+  return B200_OK;
+}
+
+extern "C" int b200_model_destroy(b200_model *m) {
+  if (!m) return B200_OK;
+  b200_dp_shutdown(m);
+  cudaStreamSynchronize(m->ctx->stream);
+  for (void *p : m->allocs) cudaFree(p);
+  if (m->pin_tokens) cudaFreeHost(m->pin_tokens);
+  if (m->pin_targets) cudaFreeHost(m->pin_targets);
+  if (m->pin_loss) cudaFreeHost(m->pin_loss);
+  delete m;
+  return B200_OK;
+}
+
+extern "C" size_t b200_model_param_count(const b200_model *m) { return m ? m->n_total : 0; }
+
+// ---- import / export in the reference's per-tensor order -----------------------------------
+namespace {
+struct Piece { size_t ref_off, rows, cols, eng_off, eng_ld; };
+// Maps every reference tensor onto its (possibly strided) place in the engine's fused storage.
+std::vector<Piece> layout_map(const b200_model *m) {
+  std::vector<Piece> v;
+  size_t r = 0;
+  const size_t H = m->H, I = m->I, Q = m->Q, KV = m->KV, QKV = m->QKV;
+  v.push_back({r, m->V, H, m->off_emb(), H}); r += m->V * H;
+  for (size_t l = 0; l < m->L; ++l) {
+    v.push_back({r, 1, H, m->off_attn_norm(l), H}); r += H;
+    v.push_back({r, H, Q, m->off_qkv(l), QKV}); r += H * Q;
+    v.push_back({r, H, KV, m->off_qkv(l) + Q, QKV}); r += H * KV;
+    v.push_back({r, H, KV, m->off_qkv(l) + Q + KV, QKV}); r += H * KV;
+    v.push_back({r, Q, H, m->off_o(l), H}); r += Q * H;
+    v.push_back({r, 1, H, m->off_ffn_norm(l), H}); r += H;
+    v.push_back({r, H, I, m->off_gate_up(l), 2 * I}); r += H * I;
+    v.push_back({r, H, I, m->off_gate_up(l) + I, 2 * I}); r += H * I;
+    v.push_back({r, I, H, m->off_down(l), H}); r += I * H;
+  }
+  v.push_back({r, 1, H, m->off_final_norm(), H}); r += H;
+  v.push_back({r, H, m->V, m->off_out(), m->V});
+  return v;
+}
+}  // namespace
+
+extern "C" int b200_model_load_params(b200_model *m, const float *host) {
+  if (!m) return B200_ERR_INVALID;
+  b200_ctx *ctx = m->ctx;
+  B200_REQUIRE(ctx, host, "model_load_params: null pointer");
+  auto map = layout_map(m);
+  size_t biggest = 0;
+  for (auto &p : map) biggest = p.rows * p.cols > biggest ? p.rows * p.cols : biggest;
+  float *stage = nullptr;
+  TRY(b200_malloc(ctx, biggest * 4, (void **)&stage));
+  int rc = B200_OK;
+  for (auto &p : map) {
+    rc = b200_memcpy_h2d(ctx, stage, host + p.ref_off, p.rows * p.cols * 4);
+    if (!rc) rc = convert2d(ctx, stage, B200_F32, m->P(p.eng_off), m->dt, p.rows, p.cols, p.cols, p.eng_ld);
+    if (!rc && m->master && (void *)m->master != m->params)
+      rc = convert2d(ctx, stage, B200_F32, m->master + p.eng_off, B200_F32, p.rows, p.cols, p.cols, p.eng_ld);
+    if (!rc) rc = b200_sync(ctx);     // stage is reused by the next tensor
+    if (rc) break;
+  }
+  b200_free(ctx, stage);
+  return rc;
+}
+
+static int export_flat(b200_model *m, const void *src, b200_dtype sdt, float *host) {
+  b200_ctx *ctx = m->ctx;
+  auto map = layout_map(m);
+  size_t biggest = 0;
+  for (auto &p : map) biggest = p.rows * p.cols > biggest ? p.rows * p.cols : biggest;
+  float *stage = nullptr;
+  TRY(b200_malloc(ctx, biggest * 4, (void **)&stage));
+  int rc = B200_OK;
+  for (auto &p : map) {
+    rc = convert2d(ctx, (const char *)src + p.eng_off * dtype_size(sdt), sdt, stage, B200_F32, p.rows, p.cols, p.eng_ld, p.cols);
+    if (!rc) rc = b200_memcpy_d2h(ctx, host + p.ref_off, stage, p.rows * p.cols * 4);
+    if (!rc) rc = b200_sync(ctx);
+    if (rc) break;
+  }
+  b200_free(ctx, stage);
+  return rc;
+}
+extern "C" int b200_model_read_params(b200_model *m, float *host) {
+  if (!m || !host) return B200_ERR_INVALID;
+  if (m->master) return export_flat(m, m->master, B200_F32, host);
+  return export_flat(m, m->params, m->dt, host);
+}
+extern "C" int b200_model_read_grads(b200_model *m, float *host) {
+  if (!m || !host) return B200_ERR_INVALID;
+  return export_flat(m, m->grads, B200_F32, host);
+}
+
+extern "C" int b200_model_init_synthetic(b200_model *m, uint64_t seed, float std) {
+  if (!m) return B200_ERR_INVALID;
+  b200_ctx *ctx = m->ctx;
+  // trainable tensors ~ N(0, std); norm weights 1 (cpp/src/RMSNorm.cpp:32)
+  if (m->master && (void *)m->master != m->params) {
+    TRY(b200_fill_normal(ctx, m->master, B200_F32, m->n_train, seed, std));
+    TRY(fill_const(ctx, m->master + m->n_train, B200_F32, m->n_total - m->n_train, 1.0f));
+    TRY(b200_convert(ctx, m->master, B200_F32, m->params, m->dt, m->n_total));
+  } else {
+    TRY(b200_fill_normal(ctx, m->params, m->dt, m->n_train, seed, std));
+    TRY(fill_const(ctx, m->P(m->n_train), m->dt, m->n_total - m->n_train, 1.0f));
+  }
+  return B200_OK;
+}
+
+// ---- one decoder layer ------------------------------------------------------------------
+// Forward, given the layer input h_in and its first norm output a1 already in acts[l].a1:
+// returns h_mid and ffn_out(tmpH) so that the caller fuses "h_out = h_mid + ffn_out" with the next norm.
+static int layer_forward_core(b200_model *m, size_t l, const void *h_in, size_t B, size_t S) {
+  b200_ctx *ctx = m->ctx;
+  const size_t M = B * S, H = m->H, I = m->I;
+  const float eps = m->cfg.rms_norm_eps;
+  b200_model::Act &a = m->acts[l];
+  const b200_dtype dt = m->dt;
+  // inner unit-weight norm (cpp/src/Attention.cpp:192-194)
+  TRY(b200_rms_norm_forward(ctx, a.a1, a.a2, m->ones, nullptr, eps, M, H, dt));
+  // Q|K|V in one GEMM on the fused weight
+  TRY(b200_gemm_ld(ctx, a.a2, m->P(m->off_qkv(l)), a.qkv, M, m->QKV, H, 0, 0, 0, dt, dt, H, m->QKV, m->QKV));
+  // RoPE on the q and k column blocks, in place (cpp/src/Attention.cpp:203)
+  const long long ld = (long long)m->QKV;
+  TRY(rope_strided(ctx, a.qkv, m->cos_t, m->sin_t, B, m->nH, S, m->hd, (long long)S * ld, (long long)m->hd, ld, dt, false));
+  TRY(rope_strided(ctx, (char *)a.qkv + m->Q * dtype_size(dt), m->cos_t, m->sin_t, B, m->nKV, S, m->hd, (long long)S * ld, (long long)m->hd, ld, dt, false));
+  AttnStrides st = token_major(m, S);
+  const char *qkv = (const char *)a.qkv;
+  TRY(attn_fwd_launch(ctx, qkv, qkv + m->Q * dtype_size(dt), qkv + (m->Q + m->KV) * dtype_size(dt), a.o, a.lse, B, m->nH,
+                      m->nKV, S, m->hd, st, dt));
+  TRY(b200_gemm_ld(ctx, a.o, m->P(m->off_o(l)), m->tmpH, M, H, m->Q, 0, 0, 0, dt, dt, m->Q, H, H));
+  // h_mid = h_in + attn_out ; ffn_in = rmsnorm(h_mid) * ffn_norm_w   (cpp/src/Transformer.cpp:178-179)
+  TRY(add_norm_oop(ctx, h_in, m->tmpH, a.h_mid, m->P(m->off_ffn_norm(l)), a.ffn_in, M, H, eps, dt));
+  TRY(b200_gemm_ld(ctx, a.ffn_in, m->P(m->off_gate_up(l)), a.gate_up, M, 2 * I, H, 0, 0, 0, dt, dt, H, 2 * I, 2 * I));
+  TRY(swiglu_fwd_strided(ctx, a.gate_up, (char *)a.gate_up + I * dtype_size(dt), a.act, M, I, 2 * I, I, dt));
+  TRY(b200_gemm_ld(ctx, a.act, m->P(m->off_down(l)), m->tmpH, M, H, I, 0, 0, 0, dt, dt, I, H, H));
+  return B200_OK;
+}
+
+// Backward of layer l: g = dL/dh_out -> g_in = dL/dh_in, weight grads into m->grads (overwritten).
+static int layer_backward_core(b200_model *m, size_t l, const void *g, void *g_in, size_t B, size_t S) {
+  b200_ctx *ctx = m->ctx;
+  const size_t M = B * S, H = m->H, I = m->I;
+  const float eps = m->cfg.rms_norm_eps;
+  b200_model::Act &a = m->acts[l];
+  const b200_dtype dt = m->dt;
+  const size_t es = dtype_size(dt);
+  // B. down projection (cpp/src/Transformer.cpp:382-401)
+  TRY(b200_gemm_ld(ctx, a.act, g, m->G(m->off_down(l)), I, H, M, 1, 0, 0, dt, B200_F32, I, H, H));
+  TRY(b200_gemm_ld(ctx, g, m->P(m->off_down(l)), m->g_act, M, I, H, 0, 1, 0, dt, dt, H, H, I));
+  // C. SwiGLU and gate/up projections (:405-439)
+  TRY(swiglu_bwd_strided(ctx, m->g_act, a.gate_up, (char *)a.gate_up + I * es, m->g_gate_up, (char *)m->g_gate_up + I * es, M, I, I, 2 * I, 2 * I, dt));
+  TRY(b200_gemm_ld(ctx, a.ffn_in, m->g_gate_up, m->G(m->off_gate_up(l)), H, 2 * I, M, 1, 0, 0, dt, B200_F32, H, 2 * I, 2 * I));
+  TRY(b200_gemm_ld(ctx, m->g_gate_up, m->P(m->off_gate_up(l)), m->g_ffn_in, M, H, 2 * I, 0, 1, 0, dt, dt, 2 * I, 2 * I, H));
+  // D. ffn norm + residual (:442-453)
+  TRY(b200_fused_backward_add_norm(ctx, m->g_ffn_in, a.h_mid, m->P(m->off_ffn_norm(l)), g, m->g_h_mid, M, H, eps, dt));
+  // E. attention (cpp/src/Attention.cpp:472-594)
+  TRY(b200_gemm_ld(ctx, a.o, m->g_h_mid, m->G(m->off_o(l)), m->Q, H, M, 1, 0, 0, dt, B200_F32, m->Q, H, H));
+  TRY(b200_gemm_ld(ctx, m->g_h_mid, m->P(m->off_o(l)), m->g_o, M, m->Q, H, 0, 1, 0, dt, dt, H, H, m->Q));
+  AttnStrides st = token_major(m, S);
+  const char *qkv = (const char *)a.qkv; char *gq = (char *)m->g_qkv;
+  TRY(attn_bwd_launch(ctx, qkv, qkv + m->Q * es, qkv + (m->Q + m->KV) * es, a.o, m->g_o, a.lse, gq, gq + m->Q * es,
+                      gq + (m->Q + m->KV) * es, B, m->nH, m->nKV, S, m->hd, st, st, dt));
+  const long long ld = (long long)m->QKV;
+  TRY(rope_strided(ctx, gq, m->cos_t, m->sin_t, B, m->nH, S, m->hd, (long long)S * ld, (long long)m->hd, ld, dt, true));
+  TRY(rope_strided(ctx, gq + m->Q * es, m->cos_t, m->sin_t, B, m->nKV, S, m->hd, (long long)S * ld, (long long)m->hd, ld, dt, true));
+  TRY(b200_gemm_ld(ctx, a.a2, m->g_qkv, m->G(m->off_qkv(l)), H, m->QKV, M, 1, 0, 0, dt, B200_F32, H, m->QKV, m->QKV));
+  TRY(b200_gemm_ld(ctx, m->g_qkv, m->P(m->off_qkv(l)), m->g_a2, M, H, m->QKV, 0, 1, 0, dt, dt, m->QKV, m->QKV, H));
+  TRY(b200_rms_norm_backward(ctx, m->g_a2, a.a1, m->ones, m->g_a1, nullptr, eps, M, H, dt));
+  // F. attn norm + residual (cpp/src/Transformer.cpp:460-471)
+  TRY(b200_fused_backward_add_norm(ctx, m->g_a1, m->hs[l], m->P(m->off_attn_norm(l)), m->g_h_mid, g_in, M, H, eps, dt));
+  return B200_OK;
+}
+
+static int check_shape(b200_model *m, size_t B, size_t S) {
+  B200_REQUIRE(m->ctx, B > 0 && B <= m->max_batch && S > 0 && S <= m->cfg.max_seq_len,
+               "batch/sequence exceed what the model was created for (cpp/src/Positional.cpp:90-94)");
+  return B200_OK;
+}
+
+static int forward_all(b200_model *m, const int32_t *tok, size_t B, size_t S) {
+  b200_ctx *ctx = m->ctx;
+  const size_t M = B * S, H = m->H;
+  const float eps = m->cfg.rms_norm_eps;
+  const b200_dtype dt = m->dt;
+  TRY(b200_embedding_forward(ctx, (const uint32_t *)tok, m->P(m->off_emb()), m->hs[0], M, H, m->V, dt));
+  if (m->L == 0) return b200_rms_norm_forward(ctx, m->hs[0], m->fh, m->P(m->off_final_norm()), nullptr, eps, M, H, dt);
+  TRY(b200_rms_norm_forward(ctx, m->hs[0], m->acts[0].a1, m->P(m->off_attn_norm(0)), nullptr, eps, M, H, dt));
+  for (size_t l = 0; l < m->L; ++l) {
+    TRY(layer_forward_core(m, l, m->hs[l], B, S));
+    // h_out = h_mid + ffn_out, fused with the norm that consumes it next
+    const void *w = (l + 1 < m->L) ? m->P(m->off_attn_norm(l + 1)) : m->P(m->off_final_norm());
+    void *y = (l + 1 < m->L) ? m->acts[l + 1].a1 : m->fh;
+    TRY(add_norm_oop(ctx, m->acts[l].h_mid, m->tmpH, m->hs[l + 1], w, y, M, H, eps, dt));
+  }
+  return B200_OK;
+}
+
+extern "C" int b200_model_forward(b200_model *m, const int32_t *tok, size_t B, size_t S, void *logits_out) {
+  if (!m) return B200_ERR_INVALID;
+  TRY(check_shape(m, B, S));
+  B200_REQUIRE(m->ctx, tok, "model_forward: null tokens");
+  TRY(forward_all(m, tok, B, S));
+  void *lg = logits_out ? logits_out : m->logits;
+  return b200_gemm_ld(m->ctx, m->fh, m->P(m->off_out()), lg, B * S, m->V, m->H, 0, 0, 0, m->dt, m->dt, m->H, m->V, m->V);
+}
+
+static int allreduce_async(b200_model *m, float *buf, size_t n) {
+  if (m->world <= 1 || !m->comm) return B200_OK;
+  b200_ctx *ctx = m->ctx;
+  B200_CUDA(ctx, cudaEventRecord(m->ev_grad_ready, ctx->stream));
+  B200_CUDA(ctx, cudaStreamWaitEvent(m->comm_stream, m->ev_grad_ready, 0));
+  int r = nccl::api().AllReduce(buf, buf, n, nccl::kFloat32, nccl::kAvg, m->comm, m->comm_stream);
+  if (r != 0) return b200_fail(ctx, B200_ERR_COMM, "ncclAllReduce failed: %s", nccl::api().GetErrorString ? nccl::api().GetErrorString(r) : "?");
+  return B200_OK;
+}
+static int allreduce_join(b200_model *m) {
+  if (m->world <= 1 || !m->comm) return B200_OK;
+  b200_ctx *ctx = m->ctx;
+  B200_CUDA(ctx, cudaEventRecord(m->ev_comm_done, m->comm_stream));
+  B200_CUDA(ctx, cudaStreamWaitEvent(ctx->stream, m->ev_comm_done, 0));
+  if (nccl::api().CommGetAsyncError) {
+    int aerr = 0;
+    if (nccl::api().CommGetAsyncError(m->comm, &aerr) == 0 && aerr != 0)
+      return b200_fail(ctx, B200_ERR_COMM, "NCCL asynchronous error %d", aerr);
+  }
+  return B200_OK;
+}
+
+extern "C" int b200_model_loss_and_grads(b200_model *m, const int32_t *tok, const int32_t *tgt, size_t B, size_t S,
+                                         float *dev_loss) {
+  if (!m) return B200_ERR_INVALID;
+  b200_ctx *ctx = m->ctx;
+  TRY(check_shape(m, B, S));
+  B200_REQUIRE(ctx, tok && tgt && dev_loss, "model_loss_and_grads: null pointer");
+  const size_t M = B * S, H = m->H, V = m->V;
+  const float eps = m->cfg.rms_norm_eps;
+  const b200_dtype dt = m->dt;
+  TRY(forward_all(m, tok, B, S));
+  TRY(b200_gemm_ld(ctx, m->fh, m->P(m->off_out()), m->logits, M, V, H, 0, 0, 0, dt, dt, H, V, V));
+  // loss + dlogits in place (cpp/src/Loss.cpp:77-134, 163-194)
+  TRY(b200_cross_entropy(ctx, m->logits, (const uint32_t *)tgt, dev_loss, m->logits, M, V, dt));
+  // output projection (cpp/src/Transformer.cpp:515-521, 607-627) and final norm (:632)
+  TRY(b200_gemm_ld(ctx, m->fh, m->logits, m->G(m->off_out()), H, V, M, 1, 0, 0, dt, B200_F32, H, V, V));
+  TRY(allreduce_async(m, m->G(m->off_out()), H * V));
+  TRY(b200_gemm_ld(ctx, m->logits, m->P(m->off_out()), m->tmpH, M, H, V, 0, 1, 0, dt, dt, V, V, H));
+  void *g = m->g_ping, *g_next = m->g_pong;
+  TRY(b200_rms_norm_backward(ctx, m->tmpH, m->hs[m->L], m->P(m->off_final_norm()), g, nullptr, eps, M, H, dt));
+  for (size_t l = m->L; l-- > 0;) {
+    TRY(layer_backward_core(m, l, g, g_next, B, S));
+    TRY(allreduce_async(m, m->G(m->off_layer(l)), m->layer_train));
+    void *t = g; g = g_next; g_next = t;
+  }
+  TRY(b200_embedding_backward(ctx, (const uint32_t *)tok, g, m->G(m->off_emb()), M, H, V, dt));
+  TRY(allreduce_async(m, m->G(m->off_emb()), V * H));
+  return allreduce_join(m);
+}
+
+extern "C" int b200_model_adamw_step(b200_model *m, float lr, float beta1, float beta2, float eps, float wd) {
+  if (!m) return B200_ERR_INVALID;
+  B200_REQUIRE(m->ctx, m->with_opt && m->master, "model was created without optimizer state");
+  m->step_count++;
+  b200_adamw_params p;
+  p.lr = lr; p.beta1 = beta1; p.beta2 = beta2; p.eps = eps; p.weight_decay = wd;
+  p.bias_correction1 = 1.0f - powf(beta1, (float)m->step_count);   // cpp/src/Optimizer.cpp:141-142
+  p.bias_correction2 = 1.0f - powf(beta2, (float)m->step_count);
+  void *shadow = ((void *)m->master != m->params) ? m->params : nullptr;
+  return b200_adamw_step(m->ctx, m->master, m->grads, m->adam_m, m->adam_v, shadow, m->n_train, &p);
+}
+
+extern "C" int b200_model_train_step(b200_model *m, const int32_t *tok, const int32_t *tgt, size_t B, size_t S,
+                                     float lr, float beta1, float beta2, float eps, float wd, float *dev_loss) {
+  TRY(b200_model_loss_and_grads(m, tok, tgt, B, S, dev_loss));
+  return b200_model_adamw_step(m, lr, beta1, beta2, eps, wd);
+}
+
+extern "C" int b200_model_train_step_host(b200_model *m, const int32_t *tok, const int32_t *tgt, size_t B, size_t S,
+                                          float lr, float beta1, float beta2, float eps, float wd, float *host_loss) {
+  if (!m) return B200_ERR_INVALID;
+  b200_ctx *ctx = m->ctx;
+  TRY(check_shape(m, B, S));
+  B200_REQUIRE(ctx, tok && tgt && host_loss, "model_train_step_host: null pointer");
+  const size_t M = B * S;
+  memcpy(m->pin_tokens, tok, M * 4);
+  memcpy(m->pin_targets, tgt, M * 4);
+  TRY(b200_memcpy_h2d(ctx, m->d_tokens, m->pin_tokens, M * 4));
+  TRY(b200_memcpy_h2d(ctx, m->d_targets, m->pin_targets, M * 4));
+  TRY(b200_model_train_step(m, m->d_tokens, m->d_targets, B, S, lr, beta1, beta2, eps, wd, m->d_loss));
+  TRY(b200_memcpy_d2h(ctx, m->pin_loss, m->d_loss, 4));
+  TRY(b200_sync(ctx));
+  *host_loss = *m->pin_loss;
+  return B200_OK;
+}
+
+extern "C" int b200_model_layer_forward(b200_model *m, size_t l, const void *h_in, void *h_out, size_t B, size_t S) {
+  if (!m) return B200_ERR_INVALID;
+  b200_ctx *ctx = m->ctx;
+  TRY(check_shape(m, B, S));
+  B200_REQUIRE(ctx, l < m->L && h_in && h_out, "model_layer_forward: bad arguments");
+  const size_t M = B * S, H = m->H;
+  TRY(b200_copy(ctx, m->hs[l], h_in, M * H * dtype_size(m->dt)));
+  TRY(b200_rms_norm_forward(ctx, m->hs[l], m->acts[l].a1, m->P(m->off_attn_norm(l)), nullptr, m->cfg.rms_norm_eps, M, H, m->dt));
+  TRY(layer_forward_core(m, l, m->hs[l], B, S));
+  TRY(b200_copy(ctx, h_out, m->acts[l].h_mid, M * H * dtype_size(m->dt)));
+  return b200_residual_add(ctx, h_out, m->tmpH, M * H, m->dt);
+}
+extern "C" int b200_model_layer_backward(b200_model *m, size_t l, const void *grad_out, void *grad_h_in, size_t B,
+                                         size_t S) {
+  if (!m) return B200_ERR_INVALID;
+  TRY(check_shape(m, B, S));
+  B200_REQUIRE(m->ctx, l < m->L && grad_out && grad_h_in, "model_layer_backward: bad arguments");
+  return layer_backward_core(m, l, grad_out, grad_h_in, B, S);
+}
+
+// ---- data parallel ------------------------------------------------------------------------
+extern "C" int b200_dp_unique_id(void *out128) {
+  if (!out128 || !nccl::api().ok()) return B200_ERR_COMM;
+  nccl::unique_id id;
+  if (nccl::api().GetUniqueId(&id) != 0) return B200_ERR_COMM;
+  memcpy(out128, &id, sizeof(id));
+  return B200_OK;
+}
+extern "C" int b200_dp_init(b200_model *m, const void *id128, int rank, int world) {
+  if (!m) return B200_ERR_INVALID;
+  b200_ctx *ctx = m->ctx;
+  B200_REQUIRE(ctx, id128 && world >= 1 && rank >= 0 && rank < world, "dp_init: bad arguments");
+  if (!nccl::api().ok()) return b200_fail(ctx, B200_ERR_COMM, "NCCL library not found (libnccl.so.2)");
+  nccl::unique_id id;
+  memcpy(&id, id128, sizeof(id));
+  int r = nccl::api().CommInitRank(&m->comm, world, id, rank);
+  if (r != 0) return b200_fail(ctx, B200_ERR_COMM, "ncclCommInitRank failed: %s", nccl::api().GetErrorString ? nccl::api().GetErrorString(r) : "?");
+  m->rank = rank; m->world = world;
+  B200_CUDA(ctx, cudaStreamCreateWithFlags(&m->comm_stream, cudaStreamNonBlocking));
+  B200_CUDA(ctx, cudaEventCreateWithFlags(&m->ev_grad_ready, cudaEventDisableTiming));
+  B200_CUDA(ctx, cudaEventCreateWithFlags(&m->ev_comm_done, cudaEventDisableTiming));
+  return B200_OK;
+}
+extern "C" int b200_dp_shutdown(b200_model *m) {
+  if (!m || !m->comm) return B200_OK;
+  cudaStreamSynchronize(m->comm_stream);
+  nccl::api().CommDestroy(m->comm);
+  m->comm = nullptr; m->world = 1;
+  cudaEventDestroy(m->ev_grad_ready); cudaEventDestroy(m->ev_comm_done);
+  cudaStreamDestroy(m->comm_stream);
+  return B200_OK;
+}

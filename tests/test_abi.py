@@ -1,0 +1,54 @@
+"""CPU-side checks of the drop-in boundary: the CUDA extension is built in-tree, loads,
+and exports every entry point that include/b200_bridge.h declares (no compute calls)."""
+import ctypes
+import importlib
+import os
+import re
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+bridge = importlib.import_module("large-language-model_b200.bridge")
+
+
+def header_symbols():
+    text = open(os.path.join(ROOT, "include", "b200_bridge.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(b200_[a-z0-9_]+)\s*\(", text)))
+
+
+@pytest.fixture(scope="module")
+def lib():
+    import __graft_entry__ as ge
+    ge.build_cuda()
+    return ctypes.CDLL(bridge.LIB_PATH)
+
+
+def test_library_exports_every_declared_symbol(lib):
+    syms = header_symbols()
+    assert len(syms) >= 55
+    missing = [s for s in syms if not hasattr(lib, s)]
+    assert not missing, missing
+
+
+def test_python_binding_covers_the_header():
+    assert sorted(bridge.EXPORTED_SYMBOLS) == header_symbols()
+
+
+def test_no_device_means_a_loud_failure(lib):
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present")
+    assert bridge.load_library().b200_is_available() == 0
+    with pytest.raises(bridge.B200Error):
+        bridge.Context(0)
+
+
+def test_product_package_never_touches_the_cpu_checker():
+    pkg = os.path.join(ROOT, "large-language-model_b200")
+    for dirpath, _, files in os.walk(pkg):
+        for f in files:
+            if f.endswith((".py", ".cu", ".cuh", ".cpp", ".h")):
+                src = open(os.path.join(dirpath, f)).read()
+                assert "oracle" not in src.replace("oracle/", "oracle/") or "import oracle" not in src and "from oracle" not in src, f
+                assert "liboracle" not in src and "orc_" not in src, f

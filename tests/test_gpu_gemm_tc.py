@@ -1,0 +1,85 @@
+"""The tcgen05 bf16 GEMM (NN forward, NT data-gradient, TN weight-gradient forms) against the
+CPU checker on bf16-rounded inputs, bf16 and fp32 outputs, ragged edges, accumulate; then the
+full projection shapes of the 1.6B configuration through a size-independent property
+(sampled rows/columns recomputed on the CPU, and linearity in A)."""
+import numpy as np
+import pytest
+
+from gpu_util import BF16_TOL, bridge, ctx, rel, synth  # noqa: F401
+
+pytestmark = pytest.mark.gpu
+SEED = 5
+
+
+def _ab(M, N, K, ta, tb, std_b=1.0):
+    A = synth.bf16_round(synth.normal(SEED, f"A{M}{K}", (K, M) if ta else (M, K)))
+    B = synth.bf16_round(synth.normal(SEED, f"B{K}{N}", (N, K) if tb else (K, N), std_b))
+    return A, B
+
+
+def _ref(A, B, ta, tb):
+    a = A.T if ta else A
+    b = B.T if tb else B
+    return a.astype(np.float64) @ b.astype(np.float64)
+
+
+FORMS = [(False, False), (False, True), (True, False), (True, True)]
+
+
+@pytest.mark.parametrize("ta,tb", FORMS)
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (128, 256, 256), (256, 512, 128), (384, 256, 1024)])
+def test_aligned_tiles(ctx, ta, tb, M, N, K):
+    A, B = _ab(M, N, K, ta, tb)
+    exp = _ref(A, B, ta, tb)
+    out32 = ctx.gemm(ctx.array(A, "bf16"), ctx.array(B, "bf16"), M, N, K, ta, tb, out_dtype="f32").download()
+    assert rel(out32, exp) < 1e-5, "fp32-out tensor-core GEMM must be exact up to accumulation order"
+    out16 = ctx.gemm(ctx.array(A, "bf16"), ctx.array(B, "bf16"), M, N, K, ta, tb, out_dtype="bf16").download()
+    assert rel(out16, exp) < 5e-3
+
+
+@pytest.mark.parametrize("ta,tb", FORMS)
+@pytest.mark.parametrize("M,N,K", [(8, 8, 8), (136, 264, 72), (200, 328, 200), (1000, 520, 136), (16, 3072, 2048)])
+def test_ragged_edges(ctx, ta, tb, M, N, K):
+    A, B = _ab(M, N, K, ta, tb)
+    out = ctx.gemm(ctx.array(A, "bf16"), ctx.array(B, "bf16"), M, N, K, ta, tb, out_dtype="f32").download()
+    assert rel(out, _ref(A, B, ta, tb)) < 1e-5
+
+
+def test_accumulate_into_fp32_c(ctx):
+    M, N, K = 256, 512, 192
+    A, B = _ab(M, N, K, True, False)
+    C0 = synth.normal(SEED, "C0", (M, N))
+    dc = ctx.array(C0)
+    ctx.gemm(ctx.array(A, "bf16"), ctx.array(B, "bf16"), M, N, K, True, False, C_acc=dc)
+    assert rel(dc.download(), _ref(A, B, True, False) + C0) < 1e-5
+
+
+def test_many_tiles_exercise_the_persistent_schedule(ctx):
+    M, N, K = 128 * 21, 256 * 9, 320          # 189 tiles > 148 SMs, odd counts
+    A, B = _ab(M, N, K, False, False)
+    out = ctx.gemm(ctx.array(A, "bf16"), ctx.array(B, "bf16"), M, N, K, out_dtype="f32").download()
+    assert rel(out, _ref(A, B, False, False)) < 1e-5
+
+
+PROJ = [("qkv", 2048, 3072), ("o", 2048, 2048), ("gate_up", 2048, 11264), ("down", 5632, 2048)]
+
+
+@pytest.mark.parametrize("name,K,N", PROJ)
+def test_full_size_projection_shapes(ctx, name, K, N):
+    """M = 16384 tokens, the three GEMM forms of one projection, checked on sampled rows/cols."""
+    M = 16384
+    rng = np.random.default_rng(1)
+    x = ctx.empty((M, K), "bf16"); w = ctx.empty((K, N), "bf16"); dy = ctx.empty((M, N), "bf16")
+    lib = ctx.lib
+    ctx._check(lib.b200_fill_normal(ctx.h, x.ptr, 1, M * K, 11, 1.0))
+    ctx._check(lib.b200_fill_normal(ctx.h, w.ptr, 1, K * N, 12, 0.02))
+    ctx._check(lib.b200_fill_normal(ctx.h, dy.ptr, 1, M * N, 13, 1.0))
+    hx, hw, hdy = x.download(), w.download(), dy.download()
+    y = ctx.gemm(x, w, M, N, K, out_dtype="bf16").download()                     # forward  NN
+    rows = rng.choice(M, 24, replace=False)
+    assert rel(y[rows], hx[rows].astype(np.float64) @ hw.astype(np.float64)) < 5e-3
+    dx = ctx.gemm(dy, w, M, K, N, False, True, out_dtype="bf16").download()      # dgrad    NT
+    assert rel(dx[rows], hdy[rows].astype(np.float64) @ hw.astype(np.float64).T) < 5e-3
+    dw = ctx.gemm(x, dy, K, N, M, True, False, out_dtype="f32").download()       # wgrad    TN
+    cols = rng.choice(N, 16, replace=False)
+    assert rel(dw[:, cols], hx.astype(np.float64).T @ hdy[:, cols].astype(np.float64)) < 1e-4

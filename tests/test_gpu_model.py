@@ -1,0 +1,165 @@
+"""Decoder layer and whole-model parity of the device-resident engine against the CPU checker
+and the committed reference fixtures: the single-layer benchmark configuration in fp32
+(rel-err <= 1e-4 on every output and gradient), bf16 (<= 2e-2), AdamW steps, and training."""
+import os
+
+import numpy as np
+import pytest
+
+from gpu_util import BF16_TOL, FP32_TOL, bridge, ctx, rel, synth  # noqa: F401
+from oracle import oracle
+
+pytestmark = pytest.mark.gpu
+GOLD = np.load(os.path.join(os.path.dirname(__file__), "golden", "reference_cpu_ops.npz"))
+SEED = 20240
+TOY = dict(B=2, S=8, H=32, I=48, nH=4, nKV=2, hd=8, V=64, L=2)
+C1 = dict(B=2, S=128, H=256, I=688, nH=8, nKV=2, hd=32, V=4096, L=1)
+
+
+def inputs(cfg, seed=SEED):
+    params = synth.model_params(seed, cfg)
+    tokens = synth.token_ids(seed, "tokens", (cfg.B, cfg.S + 1), cfg.V)
+    return params, np.ascontiguousarray(tokens[:, :-1]), np.ascontiguousarray(tokens[:, 1:])
+
+
+def trainable_mask(cfg):
+    mask = np.ones(cfg.model_params, bool)
+    for l in range(cfg.L):
+        base = cfg.V * cfg.H + l * cfg.layer_params
+        for k, (off, shp) in cfg.layer_slices().items():
+            if k.endswith("norm_w"):
+                mask[base + off: base + off + cfg.H] = False
+    e = cfg.V * cfg.H + cfg.L * cfg.layer_params
+    mask[e:e + cfg.H] = False
+    return mask
+
+
+def digest(a, n=256):
+    a = np.asarray(a, np.float32).ravel()
+    idx = np.linspace(0, a.size - 1, n).astype(np.int64)
+    return np.concatenate([[np.sqrt(np.sum(a.astype(np.float64) ** 2)), a.astype(np.float64).sum()], a[idx].astype(np.float64)])
+
+
+@pytest.mark.parametrize("cfgd", [TOY, C1], ids=["toy", "single_layer_benchmark_config"])
+def test_fp32_model_loss_logits_and_every_gradient(ctx, orc, cfgd):
+    cfg = oracle.Config(**cfgd)
+    params, tok, tgt = inputs(cfg)
+    loss_ref, grads_ref, logits_ref = orc.model_loss_and_grads(cfg, tok, tgt, params, want_logits=True)
+    model = bridge.Model(ctx, cfg, "f32")
+    model.load_params(params)
+    np.testing.assert_array_equal(model.read_params(), params)              # import/export is lossless
+    logits = model.forward(ctx.array(tok, "i32"), cfg.B, cfg.S).download()
+    assert rel(logits, logits_ref) < FP32_TOL
+    loss = model.loss_and_grads_host(tok, tgt)
+    assert abs(loss - loss_ref) < 1e-5 * max(1.0, abs(loss_ref))
+    grads = model.read_grads()
+    mask = trainable_mask(cfg)
+    lp, e = cfg.layer_params, cfg.V * cfg.H
+    assert rel(grads[:e], grads_ref[:e]) < FP32_TOL                        # embedding
+    assert rel(grads[-cfg.H * cfg.V:], grads_ref[-cfg.H * cfg.V:]) < FP32_TOL   # output projection
+    for l in range(cfg.L):
+        for k, (off, shp) in cfg.layer_slices().items():
+            if k.endswith("norm_w"):
+                continue
+            n = int(np.prod(shp))
+            sl = slice(e + l * lp + off, e + l * lp + off + n)
+            assert rel(grads[sl], grads_ref[sl]) < FP32_TOL, (l, k)
+    assert not grads[~mask].any()           # norm weights are not trained (cpp/src/Trainer.cpp:195-205)
+    if cfgd is C1:                          # and against the reference's own CPU ops (committed digests)
+        assert abs(loss - float(GOLD["c1_model_loss"])) < 1e-4
+        d = digest(grads[:e]); g = GOLD["c1_model_g_emb"]
+        assert abs(d[0] - g[0]) < 1e-4 * g[0] and rel(d[2:], g[2:]) < 1e-3
+        d = digest(logits); g = GOLD["c1_model_logits"]
+        assert abs(d[0] - g[0]) < 1e-4 * g[0] and rel(d[2:], g[2:]) < 1e-4
+    model.close()
+
+
+@pytest.mark.parametrize("cfgd", [TOY, C1], ids=["toy", "single_layer_benchmark_config"])
+def test_fp32_single_layer_forward_backward(ctx, orc, cfgd):
+    cfg = oracle.Config(**{**cfgd, "L": 1})
+    params, _, _ = inputs(cfg)
+    lp = params[cfg.V * cfg.H: cfg.V * cfg.H + cfg.layer_params]
+    tag = "toy" if cfgd is TOY else "c1"
+    x = synth.normal(SEED, tag + ".x", (cfg.B, cfg.S, cfg.H))
+    g = synth.normal(SEED, tag + ".gout", (cfg.B, cfg.S, cfg.H))
+    model = bridge.Model(ctx, cfg, "f32")
+    model.load_params(params)
+    out = model.layer_forward(0, ctx.array(x), cfg.B, cfg.S).download()
+    assert rel(out, orc.layer_forward(cfg, x, lp)) < FP32_TOL
+    gh = model.layer_backward(0, ctx.array(g), cfg.B, cfg.S).download()
+    egh, egl = orc.layer_backward(cfg, g, x, lp)
+    assert rel(gh, egh) < FP32_TOL
+    grads = model.read_grads()[cfg.V * cfg.H: cfg.V * cfg.H + cfg.layer_params]
+    for k, (off, shp) in cfg.layer_slices().items():
+        if not k.endswith("norm_w"):
+            n = int(np.prod(shp))
+            assert rel(grads[off:off + n], egl[off:off + n]) < FP32_TOL, k
+    if cfgd is C1:
+        d, gd = digest(out), GOLD["c1_layer_out"]
+        assert abs(d[0] - gd[0]) < 1e-4 * gd[0] and rel(d[2:], gd[2:]) < 1e-4
+        d, gd = digest(gh), GOLD["c1_layer_gh"]
+        assert abs(d[0] - gd[0]) < 1e-4 * gd[0] and rel(d[2:], gd[2:]) < 1e-4
+    model.close()
+
+
+@pytest.mark.parametrize("cfgd", [dict(B=2, S=128, H=256, I=688, nH=8, nKV=2, hd=32, V=4096, L=2),
+                                  dict(B=2, S=256, H=512, I=1024, nH=4, nKV=2, hd=128, V=2048, L=2)],
+                         ids=["hd32", "hd128"])
+def test_bf16_model_against_fp32_checker(ctx, orc, cfgd):
+    cfg = oracle.Config(**cfgd)
+    params, tok, tgt = inputs(cfg, seed=9)
+    params = synth.bf16_round(params)
+    loss_ref, grads_ref, logits_ref = orc.model_loss_and_grads(cfg, tok, tgt, params, want_logits=True)
+    model = bridge.Model(ctx, cfg, "bf16")
+    model.load_params(params)
+    logits = model.forward(ctx.array(tok, "i32"), cfg.B, cfg.S).download()
+    assert rel(logits, logits_ref) < BF16_TOL
+    loss = model.loss_and_grads_host(tok, tgt)
+    assert abs(loss - loss_ref) < 2e-3 * abs(loss_ref)
+    grads = model.read_grads()
+    lp, e = cfg.layer_params, cfg.V * cfg.H
+    assert rel(grads[:e], grads_ref[:e]) < BF16_TOL
+    assert rel(grads[-cfg.H * cfg.V:], grads_ref[-cfg.H * cfg.V:]) < BF16_TOL
+    for l in range(cfg.L):
+        for k, (off, shp) in cfg.layer_slices().items():
+            if k.endswith("norm_w"):
+                continue
+            n = int(np.prod(shp))
+            sl = slice(e + l * lp + off, e + l * lp + off + n)
+            assert rel(grads[sl], grads_ref[sl]) < BF16_TOL, (l, k, rel(grads[sl], grads_ref[sl]))
+    model.close()
+
+
+def test_adamw_training_steps_match_the_checker_and_reduce_the_loss(ctx, orc):
+    cfg = oracle.Config(B=2, S=16, H=64, I=96, nH=4, nKV=2, hd=16, V=96, L=2)
+    params, tok, tgt = inputs(cfg, seed=3)
+    model = bridge.Model(ctx, cfg, "f32")
+    model.load_params(params)
+    p = params.copy()
+    m, v = np.zeros_like(p), np.zeros_like(p)
+    mask = trainable_mask(cfg)
+    losses = []
+    for step in range(1, 4):
+        loss = model.train_step_host(tok, tgt, lr=1e-2, beta1=0.9, beta2=0.95, eps=1e-8, wd=0.1)
+        l_ref, g_ref, _ = orc.model_loss_and_grads(cfg, tok, tgt, p)
+        assert abs(loss - l_ref) < 1e-4 * max(1, abs(l_ref))
+        pn, mn, vn = orc.adamw_step(p, g_ref, m, v, 1e-2, 0.9, 0.95, 1e-8, 0.1, step)
+        p = np.where(mask, pn, p); m = np.where(mask, mn, m); v = np.where(mask, vn, v)
+        losses.append(loss)
+    assert rel(model.read_params(), p) < 1e-4
+    for _ in range(40):       # overfit check of cpp/tests/test_trainer.cpp:179-252
+        loss = model.train_step_host(tok, tgt, lr=1e-2)
+    assert loss < 0.5 * losses[0]
+    model.close()
+
+
+def test_shape_errors_are_reported_not_ignored(ctx):
+    cfg = oracle.Config(**TOY)
+    model = bridge.Model(ctx, cfg, "f32")
+    tok = np.zeros((cfg.B, cfg.S * 2), np.int32)
+    with pytest.raises(bridge.B200Error):          # longer than max_seq_len (cpp/src/Positional.cpp:90-94)
+        model.train_step_host(tok, tok)
+    bad = np.full((cfg.B, cfg.S), cfg.V + 5, np.int32)
+    with pytest.raises(bridge.B200Error):          # token id out of range (cpp/src/Transformer.cpp:127-129)
+        model.loss_and_grads_host(bad, np.zeros_like(bad))
+    model.close()
