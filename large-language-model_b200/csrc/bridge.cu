@@ -182,7 +182,7 @@ int attn_fwd_launch(b200_ctx *ctx, const void *Q, const void *K, const void *V, 
                     size_t nH, size_t nKV, size_t S, size_t hd, const AttnStrides &st, b200_dtype dt) {
   B200_REQUIRE(ctx, Q && K && V && O, "attention forward: null pointer");
   B200_REQUIRE(ctx, nKV > 0 && nH % nKV == 0, "attention: n_heads must be a multiple of n_kv (cpp/src/Attention.cpp:48-50)");
-  if (lse && attn_tc_supported(B, nH, nKV, S, hd, st, dt, Q, K, V, O))
+  if (attn_tc_supported(B, nH, nKV, S, hd, st, dt, Q, K, V, O))
     return attn_fwd_tc_launch(ctx, Q, K, V, O, lse, B, nH, nKV, S, hd, st);
   return attn_fwd_simt_launch(ctx, Q, K, V, O, lse, B, nH, nKV, S, hd, st, dt);
 }
