@@ -60,6 +60,13 @@ int b200_sync(b200_ctx *ctx);
 /* Number of kernels this library has launched on the context since creation. */
 uint64_t b200_launch_count(const b200_ctx *ctx);
 
+/* Per-launch device timing of the tensor-core GEMM with CUDA events on the launching
+ * stream (the reference keeps wall-clock counters accum_gpu_time_ms / count_gpu_calls,
+ * MetalBridge.hpp:141-145).  _read synchronises, returns the totals since the last read
+ * and clears them. */
+int b200_profile_gemm(b200_ctx *ctx, int enable);
+int b200_profile_gemm_read(b200_ctx *ctx, double *total_ms, double *total_flops, uint64_t *launches);
+
 /* ---- device memory (the reference wraps host pages zero-copy; a discrete GPU needs mirrors) */
 int b200_malloc(b200_ctx *ctx, size_t bytes, void **dptr);
 int b200_free(b200_ctx *ctx, void *dptr);

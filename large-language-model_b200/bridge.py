@@ -32,6 +32,14 @@ class ModelConfig(C.Structure):
                                    "n_kv_heads", "head_dim", "max_seq_len")] + [("rope_base", _f), ("rms_norm_eps", _f)]
 
 
+class Shape:
+    """Problem shape for Model (names follow the reference's ModelConfig plus batch/sequence)."""
+
+    def __init__(self, B, S, H, I, nH, nKV, hd, V, L=1, eps=1e-5, rope_base=10000.0):
+        self.B, self.S, self.H, self.I, self.nH, self.nKV, self.hd, self.V, self.L = B, S, H, I, nH, nKV, hd, V, L
+        self.eps, self.rope_base = eps, rope_base
+
+
 class AdamWParams(C.Structure):
     _fields_ = [(n, _f) for n in ("lr", "beta1", "beta2", "eps", "weight_decay", "bias_correction1",
                                   "bias_correction2")]
@@ -46,6 +54,8 @@ _SIGS = {
     "b200_set_stream": (_i, [_vp, _vp]),
     "b200_sync": (_i, [_vp]),
     "b200_launch_count": (C.c_uint64, [_vp]),
+    "b200_profile_gemm": (_i, [_vp, _i]),
+    "b200_profile_gemm_read": (_i, [_vp, C.POINTER(C.c_double), C.POINTER(C.c_double), C.POINTER(C.c_uint64)]),
     "b200_malloc": (_i, [_vp, _sz, C.POINTER(_vp)]),
     "b200_free": (_i, [_vp, _vp]),
     "b200_memcpy_h2d": (_i, [_vp, _vp, _vp, _sz]),
@@ -209,6 +219,15 @@ class Context:
 
     def launch_count(self) -> int:
         return int(self.lib.b200_launch_count(self.h))
+
+    def profile_gemm(self, enable: bool):
+        self._check(self.lib.b200_profile_gemm(self.h, int(enable)))
+
+    def profile_gemm_read(self):
+        """(total ms, total flops, launches) of the tensor-core GEMM since the last read."""
+        ms, fl, n = C.c_double(), C.c_double(), C.c_uint64()
+        self._check(self.lib.b200_profile_gemm_read(self.h, C.byref(ms), C.byref(fl), C.byref(n)))
+        return ms.value, fl.value, int(n.value)
 
     def empty(self, shape, dtype="f32") -> DeviceArray:
         return DeviceArray(self, shape, dtype)

@@ -83,6 +83,8 @@ extern "C" int b200_destroy(b200_ctx *ctx) {
   cudaSetDevice(ctx->device);
   cudaStreamSynchronize(ctx->stream);
   if (ctx->scratch) cudaFree(ctx->scratch);
+  for (auto &t : ctx->timed) { cudaEventDestroy(t.start); cudaEventDestroy(t.stop); }
+  for (auto e : ctx->event_pool) cudaEventDestroy(e);
   cudaFree(ctx->dev_status);
   cudaFreeHost(ctx->host_status);
   cudaStreamDestroy(ctx->own_stream);
@@ -109,6 +111,25 @@ extern "C" int b200_sync(b200_ctx *ctx) {
     if (st == 2) return b200_fail(ctx, B200_ERR_INVALID, "token id out of range in embedding lookup");
     return b200_fail(ctx, B200_ERR_DEVICE_WAIT, "a device-side wait gave up (code %d)", st);
   }
+  return B200_OK;
+}
+
+extern "C" int b200_profile_gemm(b200_ctx *ctx, int enable) {
+  if (!ctx) return B200_ERR_INVALID;
+  ctx->time_gemm = enable != 0;
+  return B200_OK;
+}
+extern "C" int b200_profile_gemm_read(b200_ctx *ctx, double *total_ms, double *total_flops, uint64_t *launches) {
+  if (!ctx || !total_ms || !total_flops || !launches) return B200_ERR_INVALID;
+  B200_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  *total_ms = 0; *total_flops = 0; *launches = ctx->timed.size();
+  for (auto &t : ctx->timed) {
+    float ms = 0.f;
+    cudaEventElapsedTime(&ms, t.start, t.stop);
+    *total_ms += ms; *total_flops += t.flops;
+    ctx->event_pool.push_back(t.start); ctx->event_pool.push_back(t.stop);
+  }
+  ctx->timed.clear();
   return B200_OK;
 }
 

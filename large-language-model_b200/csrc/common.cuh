@@ -7,6 +7,7 @@
 #include <cstdio>
 #include <cstring>
 #include <string>
+#include <vector>
 
 #include "../../include/b200_bridge.h"
 
@@ -25,6 +26,11 @@ struct b200_ctx {
   // workspace for split reductions etc. (grown on demand, never shrunk)
   void *scratch = nullptr;
   size_t scratch_bytes = 0;
+  // optional per-launch timing of the tensor-core GEMM (CUDA events on the launching stream)
+  bool time_gemm = false;
+  struct Timed { cudaEvent_t start, stop; double flops; };
+  std::vector<Timed> timed;
+  std::vector<cudaEvent_t> event_pool;
 };
 
 int b200_fail(b200_ctx *ctx, int code, const char *fmt, ...);

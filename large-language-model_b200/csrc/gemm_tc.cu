@@ -221,8 +221,15 @@ int launch_variant(b200_ctx *ctx, const CUtensorMap &ma, const CUtensorMap &mb, 
   }
   int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   int grid = tiles < ctx->sm_count ? tiles : ctx->sm_count;
+  b200_ctx::Timed tm{};
+  if (ctx->time_gemm) {
+    auto ev = [&]() { cudaEvent_t e; if (ctx->event_pool.empty()) cudaEventCreate(&e); else { e = ctx->event_pool.back(); ctx->event_pool.pop_back(); } return e; };
+    tm.start = ev(); tm.stop = ev(); tm.flops = 2.0 * M * N * K;
+    cudaEventRecord(tm.start, ctx->stream);
+  }
   kern<<<grid, THREADS, SMEM_BYTES, ctx->stream>>>(ma, mb, (TO *)C, M, N, K, ldc, ctx->dev_status, g_mn_lbo, g_mn_sbo, g_mn_kadv);
   B200_LAUNCHED(ctx);
+  if (ctx->time_gemm) { cudaEventRecord(tm.stop, ctx->stream); ctx->timed.push_back(tm); }
   return B200_OK;
 }
 
