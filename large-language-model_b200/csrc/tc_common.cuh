@@ -172,3 +172,5 @@ int tc_make_map_3d(CUtensorMap *map, const void *base, uint64_t d0, uint64_t d1,
                    uint64_t stride2_bytes, uint32_t b0, uint32_t b1, uint32_t b2);
 int tc_make_map_4d(CUtensorMap *map, const void *base, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t d3,
                    uint64_t stride1_bytes, uint64_t stride2_bytes, uint64_t stride3_bytes, uint32_t box0, uint32_t box1);
+int tc_make_map_f32_3d(CUtensorMap *map, const void *base, uint64_t d0, uint64_t d1, uint64_t d2,
+                       uint64_t stride1_bytes, uint64_t stride2_bytes, uint32_t box0, uint32_t box1);
