@@ -200,10 +200,17 @@ static int norm_grid(b200_ctx *ctx, size_t rows) {
   return (int)(rows < cap ? (rows ? rows : 1) : cap);
 }
 
+// warp-per-row kernels (norm_warp.cu): 1 = launched, 0 = shape does not fit, < 0 = error
+template <class T>
+int rms_fwd_warp(b200_ctx *, const void *, void *, const void *, const void *, void *, float *, float, size_t, size_t, bool);
+template <class T>
+int rms_bwd_warp(b200_ctx *, const void *, const void *, const void *, const void *, void *, float *, float, size_t, size_t, bool);
+
 template <class T>
 static int rms_fwd_t(b200_ctx *ctx, const void *x, void *h, const void *r, const void *w, void *y, float *rstd,
                      float eps, size_t rows, size_t D, bool add) {   // h: where x + r is stored (may be x itself)
   constexpr int N = Vec16<T>::N;
+  if (int rc = rms_fwd_warp<T>(ctx, x, h, r, w, y, rstd, eps, rows, D, add)) return rc < 0 ? rc : B200_OK;
   int grid = norm_grid(ctx, rows);
   bool vec = (D % N == 0) && (((uintptr_t)x | (uintptr_t)h | (uintptr_t)r | (uintptr_t)w | (uintptr_t)y) % 16 == 0);
   if (vec) {
@@ -221,6 +228,7 @@ template <class T>
 static int rms_bwd_t(b200_ctx *ctx, const void *g, const void *x, const void *w, const void *rg, void *dx, float *dw,
                      float eps, size_t rows, size_t D, bool add) {
   constexpr int N = Vec16<T>::N;
+  if (int rc = rms_bwd_warp<T>(ctx, g, x, w, rg, dx, dw, eps, rows, D, add)) return rc < 0 ? rc : B200_OK;
   int grid = norm_grid(ctx, rows);
   bool vec = (D % N == 0) && (D / N <= (size_t)NORM_VPT * NORM_THREADS) &&
              (((uintptr_t)g | (uintptr_t)x | (uintptr_t)w | (uintptr_t)rg | (uintptr_t)dx) % 16 == 0);

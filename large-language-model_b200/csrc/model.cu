@@ -302,8 +302,7 @@ static int layer_forward_core(b200_model *m, size_t l, const void *h_in, size_t 
   TRY(b200_gemm_ld(ctx, a.a2, m->P(m->off_qkv(l)), a.qkv, M, m->QKV, H, 0, 0, 0, dt, dt, H, m->QKV, m->QKV));
   // RoPE on the q and k column blocks, in place (cpp/src/Attention.cpp:203)
   const long long ld = (long long)m->QKV;
-  TRY(rope_strided(ctx, a.qkv, m->cos_t, m->sin_t, B, m->nH, S, m->hd, (long long)S * ld, (long long)m->hd, ld, dt, false));
-  TRY(rope_strided(ctx, (char *)a.qkv + m->Q * dtype_size(dt), m->cos_t, m->sin_t, B, m->nKV, S, m->hd, (long long)S * ld, (long long)m->hd, ld, dt, false));
+  TRY(rope_strided(ctx, a.qkv, m->cos_t, m->sin_t, B, m->nH + m->nKV, S, m->hd, (long long)S * ld, (long long)m->hd, ld, dt, false));
   AttnStrides st = token_major(m, S);
   const char *qkv = (const char *)a.qkv;
   TRY(attn_fwd_launch(ctx, qkv, qkv + m->Q * dtype_size(dt), qkv + (m->Q + m->KV) * dtype_size(dt), a.o, a.lse, B, m->nH,
@@ -342,8 +341,7 @@ static int layer_backward_core(b200_model *m, size_t l, const void *g, void *g_i
   TRY(attn_bwd_launch(ctx, qkv, qkv + m->Q * es, qkv + (m->Q + m->KV) * es, a.o, m->g_o, a.lse, gq, gq + m->Q * es,
                       gq + (m->Q + m->KV) * es, B, m->nH, m->nKV, S, m->hd, st, st, dt));
   const long long ld = (long long)m->QKV;
-  TRY(rope_strided(ctx, gq, m->cos_t, m->sin_t, B, m->nH, S, m->hd, (long long)S * ld, (long long)m->hd, ld, dt, true));
-  TRY(rope_strided(ctx, gq + m->Q * es, m->cos_t, m->sin_t, B, m->nKV, S, m->hd, (long long)S * ld, (long long)m->hd, ld, dt, true));
+  TRY(rope_strided(ctx, gq, m->cos_t, m->sin_t, B, m->nH + m->nKV, S, m->hd, (long long)S * ld, (long long)m->hd, ld, dt, true));
   TRY(b200_gemm_ld(ctx, a.a2, m->g_qkv, m->G(m->off_qkv(l)), H, m->QKV, M, 1, 0, 0, dt, B200_F32, H, m->QKV, m->QKV));
   TRY(b200_gemm_ld(ctx, m->g_qkv, m->P(m->off_qkv(l)), m->g_a2, M, H, m->QKV, 0, 1, 0, dt, dt, m->QKV, m->QKV, H));
   TRY(b200_rms_norm_backward(ctx, m->g_a2, a.a1, m->ones, m->g_a1, nullptr, eps, M, H, dt));

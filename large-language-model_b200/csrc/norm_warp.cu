@@ -1,0 +1,184 @@
+// RMSNorm forward / backward, one WARP per row: the row lives in registers (VPL 16-byte vectors per
+// lane), reductions are warp shuffles only (no block barriers), and every lane keeps VPL independent
+// 16-byte loads per tensor in flight, which is what saturates HBM for the 2048-wide rows of the
+// 1.6B configuration.  Same maths as the block-per-row kernels in elementwise.cu
+// (cpp/src/gpu_kernel/rms_norm_forward.metal:29-60, fused_add_norm.metal:25-72,
+//  cpp/src/RMSNorm.cpp:126-160, fused_backward_add_norm.metal:19-84).
+#include "common.cuh"
+
+namespace {
+constexpr int WARPS_PER_CTA = 8;
+
+template <class T, int VPL, bool ADD>
+__global__ void __launch_bounds__(WARPS_PER_CTA * 32)
+rms_fwd_warp_kernel(const T *x, T *h_out, const T *__restrict__ r, const T *__restrict__ w, T *__restrict__ y,
+                    float *__restrict__ rstd_out, float eps, size_t rows, int D) {
+  constexpr int N = Vec16<T>::N;
+  const int lane = threadIdx.x & 31;
+  const size_t warp_global = (size_t)blockIdx.x * WARPS_PER_CTA + (threadIdx.x >> 5);
+  const size_t n_warps = (size_t)gridDim.x * WARPS_PER_CTA;
+  for (size_t row = warp_global; row < rows; row += n_warps) {
+    const size_t base = row * (size_t)D;
+    float v[VPL][N];
+    Vec16<T> a[VPL], b[VPL];
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) a[i].load(x + base + (lane + 32 * i) * N);
+    if (ADD) {
+#pragma unroll
+      for (int i = 0; i < VPL; ++i) b[i].load(r + base + (lane + 32 * i) * N);
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+      a[i].unpack(v[i]);
+      if (ADD) {
+        float rb[N];
+        b[i].unpack(rb);
+#pragma unroll
+        for (int j = 0; j < N; ++j) v[i][j] += rb[j];
+        Vec16<T> o; o.pack(v[i]); o.store(h_out + base + (lane + 32 * i) * N); o.unpack(v[i]);   // normalise what is stored
+      }
+#pragma unroll
+      for (int j = 0; j < N; ++j) ss += v[i][j] * v[i][j];
+    }
+    ss = warp_sum(ss);
+    const float rstd = rsqrtf(ss / (float)D + eps);
+    if (rstd_out && lane == 0) rstd_out[row] = rstd;
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+      Vec16<T> wv; float wf[N], o[N];
+      wv.load(w + (lane + 32 * i) * N); wv.unpack(wf);
+#pragma unroll
+      for (int j = 0; j < N; ++j) o[j] = v[i][j] * rstd * wf[j];
+      Vec16<T> ov; ov.pack(o); ov.store(y + base + (lane + 32 * i) * N);
+    }
+  }
+}
+
+template <class T, int VPL, bool ADD, bool DW>
+__global__ void __launch_bounds__(WARPS_PER_CTA * 32)
+rms_bwd_warp_kernel(const T *__restrict__ g, const T *__restrict__ x, const T *__restrict__ w,
+                    const T *__restrict__ res_grad, T *__restrict__ dx, float *__restrict__ dw, float eps,
+                    size_t rows, int D) {
+  constexpr int N = Vec16<T>::N;
+  const int lane = threadIdx.x & 31;
+  const size_t warp_global = (size_t)blockIdx.x * WARPS_PER_CTA + (threadIdx.x >> 5);
+  const size_t n_warps = (size_t)gridDim.x * WARPS_PER_CTA;
+  float dw_acc[DW ? VPL : 1][N];
+  if (DW) {
+#pragma unroll
+    for (int i = 0; i < VPL; ++i)
+#pragma unroll
+      for (int j = 0; j < N; ++j) dw_acc[i][j] = 0.f;
+  }
+  for (size_t row = warp_global; row < rows; row += n_warps) {
+    const size_t base = row * (size_t)D;
+    Vec16<T> xa[VPL], ga[VPL], ra[VPL];
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) { xa[i].load(x + base + (lane + 32 * i) * N); ga[i].load(g + base + (lane + 32 * i) * N); }
+    if (ADD) {
+#pragma unroll
+      for (int i = 0; i < VPL; ++i) ra[i].load(res_grad + base + (lane + 32 * i) * N);
+    }
+    float xv[VPL][N], gw[VPL][N];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+      xa[i].unpack(xv[i]);
+#pragma unroll
+      for (int j = 0; j < N; ++j) ss += xv[i][j] * xv[i][j];
+    }
+    ss = warp_sum(ss);
+    const float rstd = rsqrtf(ss / (float)D + eps);
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+      Vec16<T> wv; float wf[N], gf[N];
+      wv.load(w + (lane + 32 * i) * N); wv.unpack(wf);
+      ga[i].unpack(gf);
+#pragma unroll
+      for (int j = 0; j < N; ++j) {
+        const float xhat = xv[i][j] * rstd;
+        if (DW) dw_acc[i][j] += gf[j] * xhat;
+        gw[i][j] = gf[j] * wf[j];
+        s += gw[i][j] * xhat;
+      }
+    }
+    s = warp_sum(s) / (float)D;
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+      float o[N];
+      if (ADD) ra[i].unpack(o);
+#pragma unroll
+      for (int j = 0; j < N; ++j) {
+        const float d = rstd * (gw[i][j] - xv[i][j] * rstd * s);
+        o[j] = ADD ? o[j] + d : d;
+      }
+      Vec16<T> ov; ov.pack(o); ov.store(dx + base + (lane + 32 * i) * N);
+    }
+  }
+  if (DW) {
+#pragma unroll
+    for (int i = 0; i < VPL; ++i)
+#pragma unroll
+      for (int j = 0; j < N; ++j) atomicAdd(dw + (lane + 32 * i) * N + j, dw_acc[i][j]);
+  }
+}
+
+int warp_grid(b200_ctx *ctx, size_t rows) {
+  size_t blocks = (rows + WARPS_PER_CTA - 1) / WARPS_PER_CTA, cap = (size_t)ctx->sm_count * 4;
+  return (int)(blocks < cap ? (blocks ? blocks : 1) : cap);
+}
+bool aligned16(std::initializer_list<const void *> ps) {
+  for (auto p : ps) if ((uintptr_t)p % 16) return false;
+  return true;
+}
+}  // namespace
+
+// Returns 1 when the warp-per-row kernel was launched, 0 when the shape does not fit it, <0 on error.
+template <class T>
+int rms_fwd_warp(b200_ctx *ctx, const void *x, void *h, const void *r, const void *w, void *y, float *rstd, float eps,
+                 size_t rows, size_t D, bool add) {
+  constexpr int N = Vec16<T>::N;
+  if (D % (32 * N) || !aligned16({x, h, r, w, y})) return 0;
+  const int vpl = (int)(D / (32 * N));
+  const int grid = warp_grid(ctx, rows);
+#define FW(V, A) rms_fwd_warp_kernel<T, V, A><<<grid, WARPS_PER_CTA * 32, 0, ctx->stream>>>((const T *)x, (T *)h, (const T *)r, (const T *)w, (T *)y, rstd, eps, rows, (int)D)
+  switch (vpl) {
+    case 1: if (add) FW(1, true); else FW(1, false); break;
+    case 2: if (add) FW(2, true); else FW(2, false); break;
+    case 4: if (add) FW(4, true); else FW(4, false); break;
+    case 8: if (add) FW(8, true); else FW(8, false); break;
+    default: return 0;
+  }
+#undef FW
+  ctx->launches++;
+  if (cudaGetLastError() != cudaSuccess) return b200_fail(ctx, B200_ERR_CUDA, "rms_norm forward launch failed");
+  return 1;
+}
+template <class T>
+int rms_bwd_warp(b200_ctx *ctx, const void *g, const void *x, const void *w, const void *rg, void *dx, float *dw,
+                 float eps, size_t rows, size_t D, bool add) {
+  constexpr int N = Vec16<T>::N;
+  if (D % (32 * N) || !aligned16({g, x, w, rg, dx})) return 0;
+  const int vpl = (int)(D / (32 * N));
+  const int grid = warp_grid(ctx, rows);
+#define BW(V, A, W_) rms_bwd_warp_kernel<T, V, A, W_><<<grid, WARPS_PER_CTA * 32, 0, ctx->stream>>>((const T *)g, (const T *)x, (const T *)w, (const T *)rg, (T *)dx, dw, eps, rows, (int)D)
+#define BWV(V) do { if (add) { if (dw) BW(V, true, true); else BW(V, true, false); } else { if (dw) BW(V, false, true); else BW(V, false, false); } } while (0)
+  switch (vpl) {
+    case 1: BWV(1); break;
+    case 2: BWV(2); break;
+    case 4: BWV(4); break;
+    case 8: BWV(8); break;
+    default: return 0;
+  }
+#undef BWV
+#undef BW
+  ctx->launches++;
+  if (cudaGetLastError() != cudaSuccess) return b200_fail(ctx, B200_ERR_CUDA, "rms_norm backward launch failed");
+  return 1;
+}
+template int rms_fwd_warp<float>(b200_ctx *, const void *, void *, const void *, const void *, void *, float *, float, size_t, size_t, bool);
+template int rms_fwd_warp<bf16>(b200_ctx *, const void *, void *, const void *, const void *, void *, float *, float, size_t, size_t, bool);
+template int rms_bwd_warp<float>(b200_ctx *, const void *, const void *, const void *, const void *, void *, float *, float, size_t, size_t, bool);
+template int rms_bwd_warp<bf16>(b200_ctx *, const void *, const void *, const void *, const void *, void *, float *, float, size_t, size_t, bool);
