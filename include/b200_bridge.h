@@ -14,7 +14,7 @@
  *     stream; the host-pointer behaviour of the reference interface (caller
  *     passes host buffers, results are visible after end_scope) is provided by
  *     the b200_host_* calls at the end and by the C++ `namespace metal_bridge`
- *     adaptor built on them (csrc/metal_bridge_shim.cpp).
+ *     adaptor (large-language-model_b200/adaptor/metal_bridge_b200.cpp).
  *
  * All matrices are row-major.  Plain C: no C++ or torch types cross this
  * boundary.  Functions are not thread-safe per context (the reference

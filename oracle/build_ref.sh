@@ -52,3 +52,15 @@ $CXX_BIN -std=c++20 -O2 -fopenmp -fPIC -shared -fvisibility=hidden -ffp-contract
   -I"$HERE/shim" -I"$REF/cpp/include" \
   "$SRC"/*.cpp "$HERE/shim/bridge_cpu_stub.cpp" "$HERE/ref_driver.cpp" -o "$LIB" -lpthread
 echo "built $LIB"
+# Drop-in check (alias-fixed variant only): the same reference sources and driver, linked against the
+# B200 backend's `namespace metal_bridge` adaptor instead of the CPU stub.  With GPU_ENABLED=1 every op of
+# the reference engine then runs on the CUDA kernels through host pointers (tests/test_gpu_dropin.py).
+PKGDIR="$HERE/../large-language-model_b200"
+if [ "$ALIAS_FIX" = "1" ] && [ -f "$PKGDIR/libb200bridge.so" ]; then
+  $CXX_BIN -std=c++20 -O2 -fopenmp -fPIC -shared -fvisibility=hidden -ffp-contract=off \
+    -include chrono -include string -include numeric -include cstring -include thread \
+    -I"$HERE/shim" -I"$REF/cpp/include" -I"$HERE/../include" \
+    "$SRC"/*.cpp "$PKGDIR/adaptor/metal_bridge_b200.cpp" "$HERE/ref_driver.cpp" \
+    -o "$OUT/libref_on_b200.so" -L"$PKGDIR" -lb200bridge -Wl,-rpath,'$ORIGIN/../../large-language-model_b200' -lpthread
+  echo "built $OUT/libref_on_b200.so"
+fi
