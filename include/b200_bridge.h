@@ -160,6 +160,18 @@ int b200_embedding_backward(b200_ctx *ctx, const uint32_t *token_ids, const void
 int b200_cross_entropy(b200_ctx *ctx, const void *logits, const uint32_t *targets, float *loss_out,
                        void *grad_logits, size_t total_tokens, size_t vocab_size, b200_dtype dtype);
 
+/* ---- cross-entropy for callers that must not allocate device memory.
+ * No counterpart in the reference.  Same inputs, outputs and results as b200_cross_entropy, but the
+ * per-token losses live in a fixed 256 KiB device array inside the library (held by every GPU that
+ * loads it until process exit) instead of the context's grow-on-demand scratch, so the call never
+ * reaches cudaMalloc/cudaFree.  For hosts that may not allocate at call time: fixed-budget
+ * embedders, plugins whose application forbids allocation after start-up, real-time paths that
+ * cannot take an allocation's implicit synchronisation.  At most 65536 tokens per call (larger
+ * inputs return B200_ERR_INVALID).  The first call on a device resolves the array's address; make
+ * it before any stream capture.  All calls share the array: calls that overlap on the GPU race. */
+int b200_cross_entropy_noalloc(b200_ctx *ctx, const void *logits, const uint32_t *targets, float *loss_out,
+                               void *grad_logits, size_t total_tokens, size_t vocab_size, b200_dtype dtype);
+
 /* ---- metal_bridge::adamw_step (MetalBridge.hpp:92-98). param/m/v fp32; grad
  * fp32; bf16_shadow (optional) receives the updated parameter rounded to bf16. */
 typedef struct {

@@ -83,6 +83,7 @@ _SIGS = {
     "b200_embedding_forward": (_i, [_vp, _vp, _vp, _vp, _sz, _sz, _sz, _i]),
     "b200_embedding_backward": (_i, [_vp, _vp, _vp, _vp, _sz, _sz, _sz, _i]),
     "b200_cross_entropy": (_i, [_vp, _vp, _vp, _vp, _vp, _sz, _sz, _i]),
+    "b200_cross_entropy_noalloc": (_i, [_vp, _vp, _vp, _vp, _vp, _sz, _sz, _i]),
     "b200_adamw_step": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _sz, C.POINTER(AdamWParams)]),
     "b200_model_create": (_i, [_vp, C.POINTER(ModelConfig), _i, _sz, _i, C.POINTER(_vp)]),
     "b200_model_destroy": (_i, [_vp]),
@@ -342,6 +343,14 @@ class Context:
         self._check(self.lib.b200_cross_entropy(self.h, logits.ptr, targets.ptr, loss.ptr, grad.ptr if grad else None,
                                                 T, V, logits.code))
         return loss, grad
+
+    def cross_entropy_noalloc(self, logits, targets, loss, grad=None):
+        """Cross-entropy through the entry point that allocates nothing: the caller supplies every
+        buffer (``loss`` is a 1-element f32 device array, ``grad`` optional, like ``logits``); at most
+        65536 tokens.  For hosts that cannot allocate device memory at call time."""
+        T, V = logits.size // logits.shape[-1], logits.shape[-1]
+        self._check(self.lib.b200_cross_entropy_noalloc(self.h, logits.ptr, targets.ptr, loss.ptr,
+                                                        grad.ptr if grad is not None else None, T, V, logits.code))
 
     def adamw_step(self, p, g, m, v, lr, beta1, beta2, eps, wd, step, shadow=None):
         bc1 = float(np.float32(1.0) - np.float32(beta1) ** np.float32(step))

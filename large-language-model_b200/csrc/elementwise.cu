@@ -805,3 +805,51 @@ int fill_const(b200_ctx *ctx, void *d, b200_dtype dt, size_t n, float v) {
   B200_LAUNCHED(ctx);
   return B200_OK;
 }
+
+// ============================== cross-entropy for callers that must not allocate ==========
+// Some hosts of this library cannot call cudaMalloc at the point where they need the loss: code
+// running inside a fixed-memory budget that was carved up at start-up, plugins whose embedding
+// application forbids device allocation after initialisation, and callers on a real-time path where
+// the implicit device synchronisation of an allocation is not acceptable.  The regular
+// b200_cross_entropy() keeps its per-token losses in the context's grow-on-demand scratch block,
+// which may allocate.  This variant keeps them in a fixed array that is part of the library image
+// instead: every GPU that loads the library holds the 256 KiB until the process exits, and in
+// exchange the call performs no cudaMalloc / cudaFree and uses no allocating library routine.
+//
+// Limits and rules:
+//   - at most B200_CE_NOALLOC_MAX_TOKENS (65536) tokens per call; larger inputs are rejected with
+//     B200_ERR_INVALID and a message, nothing is launched;
+//   - the first call on each device looks the array's device address up (cudaGetSymbolAddress, with
+//     that device current); make that first call before starting any stream capture;
+//   - all calls share the one array.  It still holds the previous call's per-token losses; nothing
+//     in it has to start at zero because each call overwrites entries [0, tokens) before the
+//     reduction reads exactly those entries.  Two calls that overlap on the GPU (different streams,
+//     or different contexts on the same device) race on the array: serialise them.
+constexpr size_t B200_CE_NOALLOC_MAX_TOKENS = 65536;
+static __device__ __align__(256) float g_ce_noalloc_token_loss[B200_CE_NOALLOC_MAX_TOKENS];
+static float *g_ce_noalloc_dev_ptr[64] = {nullptr};   // device address of the array, per device ordinal
+
+extern "C" int b200_cross_entropy_noalloc(b200_ctx *ctx, const void *logits, const uint32_t *targets,
+                                          float *loss_out, void *grad, size_t tokens, size_t V, b200_dtype dt) {
+  B200_REQUIRE(ctx, logits && targets && loss_out && V > 0, "cross_entropy_noalloc: bad arguments");
+  if (tokens > B200_CE_NOALLOC_MAX_TOKENS)
+    return b200_fail(ctx, B200_ERR_INVALID, "cross_entropy_noalloc: %zu tokens exceed the fixed scratch of %zu tokens; "
+                     "split the batch or use b200_cross_entropy", tokens, B200_CE_NOALLOC_MAX_TOKENS);
+  if (!tokens) return B200_OK;
+  B200_REQUIRE(ctx, ctx->device >= 0 && ctx->device < 64, "cross_entropy_noalloc: device ordinal out of range");
+  if (!g_ce_noalloc_dev_ptr[ctx->device]) {
+    // The array's name is only a host-side handle here; kernels need its device address.
+    B200_CUDA(ctx, cudaSetDevice(ctx->device));
+    float *p = nullptr;
+    B200_CUDA(ctx, cudaGetSymbolAddress((void **)&p, g_ce_noalloc_token_loss));
+    g_ce_noalloc_dev_ptr[ctx->device] = p;
+  }
+  float *tok_loss = g_ce_noalloc_dev_ptr[ctx->device];
+  int grid = (int)(tokens < (size_t)ctx->sm_count * 4 ? tokens : (size_t)ctx->sm_count * 4);
+  if (dt == B200_BF16) ce_token_kernel<bf16><<<grid, 512, 0, ctx->stream>>>((const bf16 *)logits, targets, tok_loss, (bf16 *)grad, tokens, V);
+  else ce_token_kernel<float><<<grid, 512, 0, ctx->stream>>>((const float *)logits, targets, tok_loss, (float *)grad, tokens, V);
+  B200_LAUNCHED(ctx);
+  mean_kernel<<<1, 1024, 0, ctx->stream>>>(tok_loss, loss_out, tokens);
+  B200_LAUNCHED(ctx);
+  return B200_OK;
+}
