@@ -1,0 +1,101 @@
+"""Worker for the multi-rank tests (launched with torch.distributed.run, one process per rank).
+
+mode "cpu": world_size gloo ranks on CPU.  Each rank takes its slice of a seeded global batch, computes
+  loss and gradients with the CPU checker, and the ranks average them (the CPU model of the engine's
+  NCCL exchange).  Rank 0 checks that the result equals the checker run on the whole batch, i.e. that
+  batch sharding + gradient averaging is exactly the single-device step.
+mode "gpu": one rank per GPU.  Each rank runs the device-resident engine on its slice with the NCCL
+  gradient exchange enabled, then one AdamW step; rank 0 compares gradients, loss and updated weights
+  with a single-device run of the engine on the whole batch.
+Writes "OK" or the failure to the file given as argv[2].
+"""
+import importlib
+import os
+import sys
+import traceback
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+synth = importlib.import_module("large-language-model_b200.synth")
+dp = importlib.import_module("large-language-model_b200.dp")
+
+
+def rel(a, b):
+    a, b = np.asarray(a, np.float64).ravel(), np.asarray(b, np.float64).ravel()
+    return float(np.linalg.norm(a - b) / (np.linalg.norm(b) + 1e-30))
+
+
+def main():
+    mode, out_path = sys.argv[1], sys.argv[2]
+    from oracle import oracle
+    rank, world = dp.init_control_plane("gloo")
+    msg = "OK"
+    try:
+        per = 2
+        cfg_all = oracle.Config(B=per * world, S=16, H=64, I=96, nH=4, nKV=2, hd=16, V=128, L=2)
+        cfg_one = oracle.Config(B=per, S=16, H=64, I=96, nH=4, nKV=2, hd=16, V=128, L=2)
+        params = synth.model_params(5, cfg_all)
+        tok = synth.token_ids(5, "tokens", (cfg_all.B, cfg_all.S + 1), cfg_all.V)
+        mine = dp.shard_batch(tok, rank, world)
+        t, y = np.ascontiguousarray(mine[:, :-1]), np.ascontiguousarray(mine[:, 1:])
+        ta, ya = np.ascontiguousarray(tok[:, :-1]), np.ascontiguousarray(tok[:, 1:])
+        payload = dp.broadcast_bytes(b"id-from-rank-0" if rank == 0 else None)
+        assert payload == b"id-from-rank-0"
+        assert dp.max_over_ranks([float(rank)])[0] == float(world - 1)
+        if mode == "cpu":
+            orc = oracle.Oracle()
+            loss, grads, _ = orc.model_loss_and_grads(cfg_one, t, y, params)
+            g_avg = dp.average_over_ranks(grads)
+            l_avg = dp.average_over_ranks(np.array([loss]))[0]
+            if rank == 0:
+                loss_all, grads_all, _ = orc.model_loss_and_grads(cfg_all, ta, ya, params)
+                assert abs(l_avg - loss_all) < 1e-5, (l_avg, loss_all)
+                assert rel(g_avg, grads_all) < 1e-5, rel(g_avg, grads_all)
+        else:
+            import torch
+            bridge = importlib.import_module("large-language-model_b200.bridge")
+            local = int(os.environ.get("LOCAL_RANK", "0"))
+            torch.cuda.set_device(local)
+            ctx = bridge.Context(local)
+            model = bridge.Model(ctx, cfg_one, "f32")
+            model.load_params(params)
+            uid = dp.broadcast_bytes(bridge.dp_unique_id() if rank == 0 else None)
+            model.dp_init(uid, rank, world)
+            loss = model.loss_and_grads_host(t, y)
+            grads = model.read_grads()
+            model.adamw_step(1e-2)
+            new_params = model.read_params()
+            l_avg = dp.average_over_ranks(np.array([loss]))[0]
+            model.close(); ctx.close()
+            if rank == 0:
+                ctx1 = bridge.Context(local)
+                single = bridge.Model(ctx1, cfg_all, "f32")
+                single.load_params(params)
+                loss_all = single.loss_and_grads_host(ta, ya)
+                grads_all = single.read_grads()
+                single.adamw_step(1e-2)
+                params_all = single.read_params()
+                single.close(); ctx1.close()
+                assert abs(l_avg - loss_all) < 1e-5, (l_avg, loss_all)
+                assert rel(grads, grads_all) < 1e-4, rel(grads, grads_all)
+                assert rel(new_params, params_all) < 1e-5, rel(new_params, params_all)
+    except Exception:      # noqa: BLE001 - reported to the parent test
+        msg = traceback.format_exc()
+    import torch.distributed as dist
+    flags = [None] * world
+    if dist.is_initialized():
+        dist.all_gather_object(flags, msg)
+    else:
+        flags = [msg]
+    if rank == 0:
+        bad = [m for m in flags if m != "OK"]
+        with open(out_path, "w") as f:
+            f.write("OK" if not bad else "\n".join(bad))
+    if dist.is_initialized():
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
