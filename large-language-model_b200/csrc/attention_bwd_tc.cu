@@ -42,7 +42,8 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
   BwdShared *sh = (BwdShared *)(sdS + 32768);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_t = (S + TQ - 1) / TQ;
-  const int j = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+  // x = (batch, kv head) fastest, y = key tile: the heaviest key tiles (small j) are dispatched first
+  const int j = blockIdx.y, kvh = blockIdx.x % nKV, b = blockIdx.x / nKV;
   const int G = nH / nKV;
   const int n_steps = G * (n_t - j);                  // (head in group) x (query tiles j..n_t-1)
   volatile int *abort_flag = &sh->abort_flag;
@@ -295,7 +296,7 @@ int bwd_launch_t(b200_ctx *ctx, const void *Q, const void *K, const void *V, con
   constexpr int smem = 4 * 128 * HD * 2 + 2 * 32768 + 1024 + (int)sizeof(BwdShared);
   static bool attr = false;
   if (!attr) { B200_CUDA(ctx, cudaFuncSetAttribute(attn_bwd_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)); attr = true; }
-  dim3 grid((unsigned)((S + TK - 1) / TK), (unsigned)nKV, (unsigned)B);
+  dim3 grid((unsigned)(nKV * B), (unsigned)((S + TK - 1) / TK), 1);
   attn_bwd_tc_kernel<HD><<<grid, THREADS, smem, ctx->stream>>>(mq, mk, mv, mdo, mdq, lse, Dsum, (bf16 *)dK, (bf16 *)dV, (int)nH, (int)nKV, (int)S,
                                                               gst.k_b, gst.k_h, gst.k_s, gst.v_b, gst.v_h, gst.v_s, 1.0f / sqrtf((float)HD),
                                                               ctx->dev_status);

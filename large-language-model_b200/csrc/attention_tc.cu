@@ -21,7 +21,7 @@ using namespace attn;
 namespace {
 
 struct FwdShared {
-  uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], p_full, o_full, o_consumed, pair[4];
+  uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], p_full[2], o_full[2], o_consumed[2], pair[4];
   uint32_t tmem_base;
   int abort_flag;
   float xchg[2][2][128];   // [tile parity][column half][row]: row maxima, then row sums
@@ -34,14 +34,22 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                    int nH, int nKV, int S, long long o_b, long long o_h, long long o_s, float scale, int *status) {
   constexpr int TILE_BYTES = 128 * HD * 2;
   constexpr int OC = HD / 2;                            // output columns per thread
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  // Q | K x2 | V x2 | P x2 fill the 227 KiB of shared memory at head_dim 128, so there is no room for an
+  // alignment pad: the dynamic segment is declared 1024-byte aligned and checked below.
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t *smem = smem_raw;
   uint8_t *sQ = smem, *sK = sQ + TILE_BYTES, *sV = sK + 2 * TILE_BYTES, *sP = sV + 2 * TILE_BYTES;
-  FwdShared *sh = (FwdShared *)(sP + 32768);
+  FwdShared *sh = (FwdShared *)(sP + 2 * 32768);
+  if (tc::smem_u32(smem) & 1023u) {           // swizzled tiles need 1024-byte alignment: refuse rather than corrupt
+    if (threadIdx.x == 0) atomicCAS(status, 0, 299);
+    return;
+  }
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_qt = (S + TQ - 1) / TQ;
-  const int qi = n_qt - 1 - (int)blockIdx.x;          // heavy (late) tiles first
-  const int h = blockIdx.y, b = blockIdx.z, kvh = h / (nH / nKV);
+  // grid: x = head (fastest), y = query tile, z = batch... launch order is linear in (x, y, z): all heads and
+  // batches of the heaviest (last) query tile are dispatched first, the lightest tiles fill the tail
+  const int qi = n_qt - 1 - (int)blockIdx.y;
+  const int h = blockIdx.x % nH, b = blockIdx.x / nH, kvh = h / (nH / nKV);
   const int n_kt = qi + 1;                            // causal: key tiles 0..qi
   volatile int *abort_flag = &sh->abort_flag;
 
@@ -51,9 +59,9 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       tc::mbar_init(&sh->k_full[i], 1); tc::mbar_init(&sh->k_empty[i], 1);
       tc::mbar_init(&sh->v_full[i], 1); tc::mbar_init(&sh->v_empty[i], 1);
       tc::mbar_init(&sh->s_full[i], 1);
+      tc::mbar_init(&sh->p_full[i], COMPUTE_WARPS); tc::mbar_init(&sh->o_full[i], 1); tc::mbar_init(&sh->o_consumed[i], COMPUTE_WARPS);
     }
     for (int i = 0; i < 4; ++i) tc::mbar_init(&sh->pair[i], 64);   // the two warps that share a row quarter
-    tc::mbar_init(&sh->p_full, COMPUTE_WARPS); tc::mbar_init(&sh->o_full, 1); tc::mbar_init(&sh->o_consumed, COMPUTE_WARPS);
     sh->abort_flag = 0;
     tc::fence_barrier_init();
     tc::fence_proxy_async();
@@ -103,15 +111,16 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         // scores of the next tile go into the other buffer (its previous reader finished before p_full(j-1))
         if (j + 1 < n_kt) { if (!issue_s(j + 1)) break; }
         const int s = j & 1; const uint32_t ph = (j >> 1) & 1;
-        if (!tc::mbar_wait(&sh->p_full, j & 1, status, abort_flag, 205)) break;
+        if (!tc::mbar_wait(&sh->p_full[s], ph, status, abort_flag, 205)) break;
         if (!tc::mbar_wait(&sh->v_full[s], ph, status, abort_flag, 206)) break;
-        if (j > 0 && !tc::mbar_wait(&sh->o_consumed, (j - 1) & 1, status, abort_flag, 207)) break;
+        // the output buffer of tile j was last used by tile j-2
+        if (j > 1 && !tc::mbar_wait(&sh->o_consumed[s], ((j - 2) >> 1) & 1, status, abort_flag, 207)) break;
         tc::tc_fence_after();
-        const uint32_t v_addr = tc::smem_u32(sV + s * TILE_BYTES);
+        const uint32_t v_addr = tc::smem_u32(sV + s * TILE_BYTES), pj_addr = p_addr + s * 32768;
 #pragma unroll
         for (int k = 0; k < TK / 16; ++k)
-          tc::umma_ss(tmem_o, desc_kmajor(p_addr, k), desc_mnmajor(v_addr, k), idesc_o, k ? 1u : 0u);
-        tc::umma_commit(&sh->o_full);
+          tc::umma_ss(tmem_o + s * 128, desc_kmajor(pj_addr, k), desc_mnmajor(v_addr, k), idesc_o, k ? 1u : 0u);
+        tc::umma_commit(&sh->o_full[s]);
         tc::umma_commit(&sh->v_empty[s]);
       }
     }
@@ -122,7 +131,7 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
     const int q_idx = qi * TQ + r;
     const int q_eff = min(q_idx, S - 1);               // rows past the end behave like the last row (never stored)
     const float sl2 = scale * LOG2E;
-    float m = -INFINITY, l = 0.f;
+    float m = -INFINITY, l = 0.f, alpha_prev = 0.f;
     float o[OC];
 #pragma unroll
     for (int i = 0; i < OC; ++i) o[i] = 0.f;
@@ -164,26 +173,43 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         }
         uint4 w;
         w.x = pack_bf16(p[0], p[1]); w.y = pack_bf16(p[2], p[3]); w.z = pack_bf16(p[4], p[5]); w.w = pack_bf16(p[6], p[7]);
-        *reinterpret_cast<uint4 *>(sP + swz_unit(r, half * 8 + u)) = w;
+        *reinterpret_cast<uint4 *>(sP + s * 32768 + swz_unit(r, half * 8 + u)) = w;
       }
       l = l * alpha + rowsum;
       m = m_new;
       tc::fence_proxy_async();
       tc::tc_fence_before();
       __syncwarp();
-      if (lane == 0) tc::mbar_arrive(&sh->p_full);
-      // O_t = P V of this tile: this thread's half of the head_dim
-      if (!tc::mbar_wait(&sh->o_full, j & 1, status, abort_flag, 209)) { ok = false; break; }
+      if (lane == 0) tc::mbar_arrive(&sh->p_full[s]);
+      // Software pipeline: while the tensor cores compute O_t(j) = P(j) V(j), fold in the PREVIOUS tile's
+      // O_t(j-1) (its rescale factor alpha(j-1) was kept), then go straight on to the scores of tile j+1.
+      if (j > 0) {
+        const int sp = (j - 1) & 1;
+        if (!tc::mbar_wait(&sh->o_full[sp], ((j - 1) >> 1) & 1, status, abort_flag, 209)) { ok = false; break; }
+        tc::tc_fence_after();
+        uint32_t ov[OC];
+#pragma unroll
+        for (int c = 0; c < OC / 32; ++c) tc::tmem_ld_32x32(tmem_o + sp * 128 + lane_base + half * OC + c * 32, ov + c * 32);
+        tc::tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < OC; ++i) o[i] = o[i] * alpha_prev + __uint_as_float(ov[i]);
+        tc::tc_fence_before();
+        __syncwarp();
+        if (lane == 0) tc::mbar_arrive(&sh->o_consumed[sp]);
+      }
+      alpha_prev = alpha;
+    }
+    if (ok) {   // drain: the last tile's product
+      const int sp = (n_kt - 1) & 1;
+      ok = tc::mbar_wait(&sh->o_full[sp], ((n_kt - 1) >> 1) & 1, status, abort_flag, 212);
       tc::tc_fence_after();
       uint32_t ov[OC];
 #pragma unroll
-      for (int c = 0; c < OC / 32; ++c) tc::tmem_ld_32x32(tmem_o + lane_base + half * OC + c * 32, ov + c * 32);
+      for (int c = 0; c < OC / 32; ++c) tc::tmem_ld_32x32(tmem_o + sp * 128 + lane_base + half * OC + c * 32, ov + c * 32);
       tc::tmem_ld_wait();
 #pragma unroll
-      for (int i = 0; i < OC; ++i) o[i] = o[i] * alpha + __uint_as_float(ov[i]);
+      for (int i = 0; i < OC; ++i) o[i] = o[i] * alpha_prev + __uint_as_float(ov[i]);
       tc::tc_fence_before();
-      __syncwarp();
-      if (lane == 0) tc::mbar_arrive(&sh->o_consumed);
     }
     if (ok) {
       // combine the two column halves' row sums
@@ -221,10 +247,11 @@ int fwd_launch_t(b200_ctx *ctx, const void *Q, const void *K, const void *V, voi
   if (make_map_4d(&mq, Q, HD, S, nH, B, st.q_s, st.q_h, st.q_b) || make_map_4d(&mk, K, HD, S, nKV, B, st.k_s, st.k_h, st.k_b) ||
       make_map_4d(&mv, V, HD, S, nKV, B, st.v_s, st.v_h, st.v_b))
     return b200_fail(ctx, B200_ERR_CUDA, "cuTensorMapEncodeTiled failed for attention operands");
-  constexpr int smem = 5 * 128 * HD * 2 + 32768 + 1024 + (int)sizeof(FwdShared);
+  constexpr int smem = 5 * 128 * HD * 2 + 2 * 32768 + (int)sizeof(FwdShared);
+  static_assert(smem <= 232448, "forward attention tiles exceed the 227 KiB of shared memory per CTA");
   static bool attr = false;
   if (!attr) { B200_CUDA(ctx, cudaFuncSetAttribute(attn_fwd_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)); attr = true; }
-  dim3 grid((unsigned)((S + TQ - 1) / TQ), (unsigned)nH, (unsigned)B);
+  dim3 grid((unsigned)(nH * B), (unsigned)((S + TQ - 1) / TQ), 1);
   attn_fwd_tc_kernel<HD><<<grid, THREADS, smem, ctx->stream>>>(mq, mk, mv, (bf16 *)O, lse, (int)nH, (int)nKV, (int)S, st.o_b, st.o_h,
                                                               st.o_s, 1.0f / sqrtf((float)HD), ctx->dev_status);
   B200_LAUNCHED(ctx);
@@ -235,7 +262,7 @@ int fwd_launch_t(b200_ctx *ctx, const void *Q, const void *K, const void *V, voi
 bool attn_tc_supported(size_t B, size_t nH, size_t nKV, size_t S, size_t hd, const AttnStrides &st, b200_dtype dt,
                        const void *Q, const void *K, const void *V, const void *O) {
   if (dt != B200_BF16 || (hd != 64 && hd != 128) || B == 0 || S == 0 || nKV == 0 || nH % nKV) return false;
-  if (B > 65535 || nH > 65535) return false;
+  if (nH * B > 0x7fffffffull || (S + TQ - 1) / TQ > 65535) return false;
   return layout_ok(Q, st.q_b, st.q_h, st.q_s) && layout_ok(K, st.k_b, st.k_h, st.k_s) &&
          layout_ok(V, st.v_b, st.v_h, st.v_s) && layout_ok(O, st.o_b, st.o_h, st.o_s);
 }
