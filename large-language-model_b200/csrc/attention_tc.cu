@@ -148,20 +148,26 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       tc::tmem_ld_32x32(ts, v);
       tc::tmem_ld_32x32(ts + 32, v + 32);
       tc::tmem_ld_wait();
-      float mx = -INFINITY;
+      float mx8[8];                                   // independent partial maxima: no 64-long dependency chain
+#pragma unroll
+      for (int a = 0; a < 8; ++a) mx8[a] = -INFINITY;
 #pragma unroll
       for (int i = 0; i < 64; ++i) {
         float x = __uint_as_float(v[i]);
         if (diag && (kc0 + i > q_eff)) x = -INFINITY;
-        mx = fmaxf(mx, x);
+        mx8[i & 7] = fmaxf(mx8[i & 7], x);
       }
+      float mx = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])), fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
+      // the row's other 64 columns belong to the partner warp: exchange the two partial maxima
       sh->xchg[j & 1][half][r] = mx;
       tc::mbar_arrive(&sh->pair[quarter]);
       if (!tc::mbar_wait(&sh->pair[quarter], j & 1, status, abort_flag, 210)) { ok = false; break; }
       mx = fmaxf(mx, sh->xchg[j & 1][half ^ 1][r]);
       const float m_new = fmaxf(m, mx * sl2);
       const float alpha = fast_exp2(m - m_new);
-      float rowsum = 0.f;
+      float rs8[8];                                   // independent partial sums: no 64-long dependency chain
+#pragma unroll
+      for (int a = 0; a < 8; ++a) rs8[a] = 0.f;
 #pragma unroll
       for (int u = 0; u < 8; ++u) {
         float p[8];
@@ -169,12 +175,13 @@ attn_fwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         for (int i = 0; i < 8; ++i) {
           float e = fast_exp2(__uint_as_float(v[u * 8 + i]) * sl2 - m_new);
           if (diag && (kc0 + u * 8 + i > q_eff)) e = 0.f;
-          p[i] = e; rowsum += e;
+          p[i] = e; rs8[i] += e;
         }
         uint4 w;
         w.x = pack_bf16(p[0], p[1]); w.y = pack_bf16(p[2], p[3]); w.z = pack_bf16(p[4], p[5]); w.w = pack_bf16(p[6], p[7]);
         *reinterpret_cast<uint4 *>(sP + s * 32768 + swz_unit(r, half * 8 + u)) = w;
       }
+      const float rowsum = ((rs8[0] + rs8[1]) + (rs8[2] + rs8[3])) + ((rs8[4] + rs8[5]) + (rs8[6] + rs8[7]));
       l = l * alpha + rowsum;
       m = m_new;
       tc::fence_proxy_async();
