@@ -32,7 +32,7 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
                    const __grid_constant__ CUtensorMap map_dq, const float *__restrict__ lse,
                    const float *__restrict__ Dsum, bf16 *__restrict__ dK, bf16 *__restrict__ dV, int nH, int nKV, int S,
                    long long dk_b, long long dk_h, long long dk_s, long long dv_b, long long dv_h, long long dv_s,
-                   float scale, int *status) {
+                   float scale, int *status, const float *__restrict__ rope_cos, const float *__restrict__ rope_sin) {
   constexpr int TILE_BYTES = 128 * HD * 2;
   constexpr int CH = HD / 64;                          // 32-column chunks of the head_dim per thread
   extern __shared__ uint8_t smem_raw[];
@@ -211,6 +211,16 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
         tc::tmem_ld_32x32(t_dv + lane_base + col, g);
         tc::tmem_ld_wait();
         if (key < S) {
+          if (rope_cos != nullptr) {
+            // gradient of the rotary embedding (inverse rotation, cpp/src/Positional.cpp:207-231) on dK, position = key
+            const float *cp = rope_cos + (size_t)key * (HD / 2) + (col >> 1), *sp = rope_sin + (size_t)key * (HD / 2) + (col >> 1);
+#pragma unroll
+            for (int p2 = 0; p2 < 16; ++p2) {
+              const float x0 = __uint_as_float(a[2 * p2]), x1 = __uint_as_float(a[2 * p2 + 1]), cc = __ldg(cp + p2), ss = __ldg(sp + p2);
+              a[2 * p2] = __float_as_uint(x0 * cc + x1 * ss);
+              a[2 * p2 + 1] = __float_as_uint(-x0 * ss + x1 * cc);
+            }
+          }
 #pragma unroll
           for (int u = 0; u < 4; ++u) {
             uint4 w;
@@ -258,13 +268,21 @@ __global__ void attn_dsum_kernel(const bf16 *__restrict__ O, const bf16 *__restr
 }
 // fp32 [B,nH,S,hd] accumulator -> strided bf16 dQ
 __global__ void attn_dq_store_kernel(const float *__restrict__ acc, bf16 *__restrict__ dQ, int B, int nH, int S,
-                                     int hd, long long q_b, long long q_h, long long q_s) {
+                                     int hd, long long q_b, long long q_h, long long q_s,
+                                     const float *__restrict__ rope_cos, const float *__restrict__ rope_sin) {
   const size_t total = (size_t)B * nH * S * (hd / 8);
   for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
     const int u = (int)(idx % (hd / 8)); size_t r = idx / (hd / 8);
     const int s = (int)(r % S); r /= S;
     const int h = (int)(r % nH), b = (int)(r / nH);
-    const float4 x = *reinterpret_cast<const float4 *>(acc + idx * 8), y = *reinterpret_cast<const float4 *>(acc + idx * 8 + 4);
+    float4 x = *reinterpret_cast<const float4 *>(acc + idx * 8), y = *reinterpret_cast<const float4 *>(acc + idx * 8 + 4);
+    if (rope_cos != nullptr) {   // gradient of the rotary embedding on dQ: inverse rotation at position s
+      const float4 c = *reinterpret_cast<const float4 *>(rope_cos + (size_t)s * (hd / 2) + u * 4);
+      const float4 n = *reinterpret_cast<const float4 *>(rope_sin + (size_t)s * (hd / 2) + u * 4);
+      float4 a = x, d = y;
+      x.x = a.x * c.x + a.y * n.x; x.y = -a.x * n.x + a.y * c.x; x.z = a.z * c.y + a.w * n.y; x.w = -a.z * n.y + a.w * c.y;
+      y.x = d.x * c.z + d.y * n.z; y.y = -d.x * n.z + d.y * c.z; y.z = d.z * c.w + d.w * n.w; y.w = -d.z * n.w + d.w * c.w;
+    }
     uint4 w;
     w.x = pack_bf16(x.x, x.y); w.y = pack_bf16(x.z, x.w); w.z = pack_bf16(y.x, y.y); w.w = pack_bf16(y.z, y.w);
     *reinterpret_cast<uint4 *>(dQ + b * q_b + h * q_h + (long long)s * q_s + u * 8) = w;
@@ -274,7 +292,7 @@ __global__ void attn_dq_store_kernel(const float *__restrict__ acc, bf16 *__rest
 template <int HD>
 int bwd_launch_t(b200_ctx *ctx, const void *Q, const void *K, const void *V, const void *O, const void *dO,
                  const float *lse, void *dQ, void *dK, void *dV, size_t B, size_t nH, size_t nKV, size_t S,
-                 const AttnStrides &st, const AttnStrides &gst) {
+                 const AttnStrides &st, const AttnStrides &gst, const float *rope_cos, const float *rope_sin) {
   const size_t rows = B * nH * S;
   // scratch: D [rows] fp32, dQ accumulator [rows, HD] fp32 (zeroed here, added to by TMA reduce)
   const size_t d_elems = ((rows + 63) / 64) * 64;
@@ -299,11 +317,11 @@ int bwd_launch_t(b200_ctx *ctx, const void *Q, const void *K, const void *V, con
   dim3 grid((unsigned)(nKV * B), (unsigned)((S + TK - 1) / TK), 1);
   attn_bwd_tc_kernel<HD><<<grid, THREADS, smem, ctx->stream>>>(mq, mk, mv, mdo, mdq, lse, Dsum, (bf16 *)dK, (bf16 *)dV, (int)nH, (int)nKV, (int)S,
                                                               gst.k_b, gst.k_h, gst.k_s, gst.v_b, gst.v_h, gst.v_s, 1.0f / sqrtf((float)HD),
-                                                              ctx->dev_status);
+                                                              ctx->dev_status, rope_cos, rope_sin);
   B200_LAUNCHED(ctx);
   {
     size_t items = rows * (HD / 8), blocks = (items + 255) / 256, cap = (size_t)ctx->sm_count * 16;
-    attn_dq_store_kernel<<<(int)(blocks < cap ? blocks : cap), 256, 0, ctx->stream>>>(dQacc, (bf16 *)dQ, (int)B, (int)nH, (int)S, HD, gst.q_b, gst.q_h, gst.q_s);
+    attn_dq_store_kernel<<<(int)(blocks < cap ? blocks : cap), 256, 0, ctx->stream>>>(dQacc, (bf16 *)dQ, (int)B, (int)nH, (int)S, HD, gst.q_b, gst.q_h, gst.q_s, rope_cos, rope_sin);
     B200_LAUNCHED(ctx);
   }
   return B200_OK;
@@ -312,7 +330,8 @@ int bwd_launch_t(b200_ctx *ctx, const void *Q, const void *K, const void *V, con
 
 int attn_bwd_tc_launch(b200_ctx *ctx, const void *Q, const void *K, const void *V, const void *O, const void *dO,
                        const float *lse, void *dQ, void *dK, void *dV, size_t B, size_t nH, size_t nKV, size_t S,
-                       size_t hd, const AttnStrides &st, const AttnStrides &gst) {
-  return hd == 128 ? bwd_launch_t<128>(ctx, Q, K, V, O, dO, lse, dQ, dK, dV, B, nH, nKV, S, st, gst)
-                   : bwd_launch_t<64>(ctx, Q, K, V, O, dO, lse, dQ, dK, dV, B, nH, nKV, S, st, gst);
+                       size_t hd, const AttnStrides &st, const AttnStrides &gst, const float *rope_cos,
+                       const float *rope_sin) {
+  return hd == 128 ? bwd_launch_t<128>(ctx, Q, K, V, O, dO, lse, dQ, dK, dV, B, nH, nKV, S, st, gst, rope_cos, rope_sin)
+                   : bwd_launch_t<64>(ctx, Q, K, V, O, dO, lse, dQ, dK, dV, B, nH, nKV, S, st, gst, rope_cos, rope_sin);
 }

@@ -16,7 +16,7 @@ int attn_fwd_tc_launch(b200_ctx *, const void *, const void *, const void *, voi
                        size_t, size_t, const AttnStrides &);
 int attn_bwd_tc_launch(b200_ctx *, const void *, const void *, const void *, const void *, const void *,
                        const float *, void *, void *, void *, size_t, size_t, size_t, size_t, size_t,
-                       const AttnStrides &, const AttnStrides &);
+                       const AttnStrides &, const AttnStrides &, const float *, const float *);
 int swiglu_fwd_strided(b200_ctx *, const void *, const void *, void *, size_t, size_t, size_t, size_t, b200_dtype);
 
 int b200_fail(b200_ctx *ctx, int code, const char *fmt, ...) {
@@ -169,8 +169,12 @@ extern "C" int b200_copy(b200_ctx *ctx, void *dst, const void *src, size_t n) {
 
 // ------------------------------------------------------------------ GEMM --
 int b200_gemm_ld(b200_ctx *ctx, const void *A, const void *B, void *C, size_t M, size_t N, size_t K, int ta, int tb,
-                 int acc, b200_dtype in_dt, b200_dtype out_dt, size_t lda, size_t ldb, size_t ldc) {
+                 int acc, b200_dtype in_dt, b200_dtype out_dt, size_t lda, size_t ldb, size_t ldc,
+                 const GemmEpilogue *epi) {
   B200_REQUIRE(ctx, A && B && C, "gemm: null pointer");
+  B200_REQUIRE(ctx, !epi || (in_dt == B200_BF16 && out_dt == B200_BF16 && !acc && K > 0 &&
+                             gemm_tc_supported(A, B, C, M, N, K, lda, ldb, ldc, out_dt)),
+               "gemm: a fused epilogue needs the tensor-core path");
   if (M == 0 || N == 0) return B200_OK;
   if (K == 0) {
     if (!acc) {
@@ -180,7 +184,7 @@ int b200_gemm_ld(b200_ctx *ctx, const void *A, const void *B, void *C, size_t M,
     return B200_OK;
   }
   if (in_dt == B200_BF16 && !(acc && out_dt == B200_BF16) && gemm_tc_supported(A, B, C, M, N, K, lda, ldb, ldc, out_dt))
-    return gemm_tc_launch(ctx, A, B, C, M, N, K, ta, tb, acc, out_dt, lda, ldb, ldc);
+    return gemm_tc_launch(ctx, A, B, C, M, N, K, ta, tb, acc, out_dt, lda, ldb, ldc, epi);
   return gemm_simt_launch(ctx, A, B, C, M, N, K, ta, tb, acc, in_dt, out_dt, lda, ldb, ldc);
 }
 
@@ -209,15 +213,23 @@ int attn_fwd_launch(b200_ctx *ctx, const void *Q, const void *K, const void *V, 
 }
 int attn_bwd_launch(b200_ctx *ctx, const void *Q, const void *K, const void *V, const void *O, const void *dO,
                     const float *lse, void *dQ, void *dK, void *dV, size_t B, size_t nH, size_t nKV, size_t S,
-                    size_t hd, const AttnStrides &st, const AttnStrides &gst, b200_dtype dt) {
+                    size_t hd, const AttnStrides &st, const AttnStrides &gst, b200_dtype dt, const float *rope_cos,
+                    const float *rope_sin) {
   B200_REQUIRE(ctx, Q && K && V && O && dO && lse && dQ && dK && dV, "attention backward: null pointer");
   B200_REQUIRE(ctx, nKV > 0 && nH % nKV == 0, "attention: n_heads must be a multiple of n_kv");
   if (attn_tc_supported(B, nH, nKV, S, hd, st, dt, Q, K, V, O) &&
       attn_tc_supported(B, nH, nKV, S, hd, gst, dt, dQ, dK, dV, dO))
-    return attn_bwd_tc_launch(ctx, Q, K, V, O, dO, lse, dQ, dK, dV, B, nH, nKV, S, hd, st, gst);
+    return attn_bwd_tc_launch(ctx, Q, K, V, O, dO, lse, dQ, dK, dV, B, nH, nKV, S, hd, st, gst, rope_cos, rope_sin);
+  B200_REQUIRE(ctx, !rope_cos && !rope_sin, "attention backward: fused rotary gradient needs the tensor-core path");
   float *scr = (float *)b200_scratch(ctx, 2 * B * nKV * S * hd * sizeof(float));
   if (!scr) return B200_ERR_NOMEM;
   return attn_bwd_simt_launch(ctx, Q, K, V, O, dO, lse, dQ, dK, dV, scr, B, nH, nKV, S, hd, st, gst, dt);
+}
+
+bool attn_bwd_fuses_rope(size_t B, size_t nH, size_t nKV, size_t S, size_t hd, const AttnStrides &st,
+                         const AttnStrides &gst, b200_dtype dt, const void *Q, const void *K, const void *V,
+                         const void *O, const void *dO, const void *dQ, const void *dK, const void *dV) {
+  return attn_tc_supported(B, nH, nKV, S, hd, st, dt, Q, K, V, O) && attn_tc_supported(B, nH, nKV, S, hd, gst, dt, dQ, dK, dV, dO);
 }
 
 static AttnStrides ref_layout(size_t nH, size_t nKV, size_t S, size_t hd) {

@@ -119,13 +119,21 @@ __device__ __forceinline__ float block_max(float v, float *red) {
 // ---- internal launchers shared between translation units -------------------
 int gemm_simt_launch(b200_ctx *ctx, const void *A, const void *B, void *C, size_t M, size_t N, size_t K, int ta,
                      int tb, int acc, b200_dtype in_dt, b200_dtype out_dt, size_t lda, size_t ldb, size_t ldc);
+// Optional fused epilogue of the tensor-core GEMM (bf16 output): rotary position embedding applied to the
+// fp32 accumulators of columns [0, cols) before rounding -- row r is token position r % S, column c is
+// element c % hd of its head; interleaved pairs, tables [S, hd/2] (cpp/src/Positional.cpp:120-147).
+struct GemmEpilogue {
+  const float *cos_t = nullptr, *sin_t = nullptr;
+  int S = 0, hd = 0, cols = 0;
+};
 int gemm_tc_launch(b200_ctx *ctx, const void *A, const void *B, void *C, size_t M, size_t N, size_t K, int ta, int tb,
-                   int acc, b200_dtype out_dt, size_t lda, size_t ldb, size_t ldc);
+                   int acc, b200_dtype out_dt, size_t lda, size_t ldb, size_t ldc, const GemmEpilogue *epi = nullptr);
 bool gemm_tc_supported(const void *A, const void *B, const void *C, size_t M, size_t N, size_t K, size_t lda,
                        size_t ldb, size_t ldc, b200_dtype out_dt);
 // Strided general form used by the engine (leading dimensions in elements).
 int b200_gemm_ld(b200_ctx *ctx, const void *A, const void *B, void *C, size_t M, size_t N, size_t K, int ta, int tb,
-                 int acc, b200_dtype in_dt, b200_dtype out_dt, size_t lda, size_t ldb, size_t ldc);
+                 int acc, b200_dtype in_dt, b200_dtype out_dt, size_t lda, size_t ldb, size_t ldc,
+                 const GemmEpilogue *epi = nullptr);
 
 // Attention on strided head layouts (element strides; head_dim contiguous).
 struct AttnStrides {
@@ -138,4 +146,9 @@ int attn_fwd_launch(b200_ctx *ctx, const void *Q, const void *K, const void *V, 
                     size_t nH, size_t nKV, size_t S, size_t hd, const AttnStrides &st, b200_dtype dt);
 int attn_bwd_launch(b200_ctx *ctx, const void *Q, const void *K, const void *V, const void *O, const void *dO,
                     const float *lse, void *dQ, void *dK, void *dV, size_t B, size_t nH, size_t nKV, size_t S,
-                    size_t hd, const AttnStrides &st, const AttnStrides &gst, b200_dtype dt);
+                    size_t hd, const AttnStrides &st, const AttnStrides &gst, b200_dtype dt,
+                    const float *rope_cos = nullptr, const float *rope_sin = nullptr);
+// true when attn_bwd_launch can apply the inverse rotary embedding to dQ and dK itself (tensor-core path)
+bool attn_bwd_fuses_rope(size_t B, size_t nH, size_t nKV, size_t S, size_t hd, const AttnStrides &st,
+                         const AttnStrides &gst, b200_dtype dt, const void *Q, const void *K, const void *V,
+                         const void *O, const void *dO, const void *dQ, const void *dK, const void *dV);

@@ -38,7 +38,7 @@ template <bool A_MN, bool B_MN, class TO, bool ACC>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                TO *__restrict__ C, int M, int N, int K, size_t ldc, int *status, uint32_t mn_lbo, uint32_t mn_sbo,
-               uint32_t mn_kadv) {
+               uint32_t mn_kadv, GemmEpilogue epi) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t *sA = smem, *sB = smem + STAGES * A_STAGE_BYTES;
@@ -149,6 +149,23 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         if (row < M && col < N) {
           if (col + 32 <= N) {
             if constexpr (sizeof(TO) == 2) {
+              if (epi.cos_t != nullptr && col < epi.cols) {
+                // fused rotary embedding on the fp32 accumulators: 16 interleaved pairs of this 32-column chunk
+                const int half = epi.hd >> 1;
+                const size_t tab = (size_t)(row % epi.S) * half + ((col % epi.hd) >> 1);
+                const float4 *c4 = reinterpret_cast<const float4 *>(epi.cos_t + tab), *s4 = reinterpret_cast<const float4 *>(epi.sin_t + tab);
+#pragma unroll
+                for (int g = 0; g < 4; ++g) {
+                  const float4 cc = __ldg(c4 + g), ss = __ldg(s4 + g);
+                  const float cv[4] = {cc.x, cc.y, cc.z, cc.w}, sv[4] = {ss.x, ss.y, ss.z, ss.w};
+#pragma unroll
+                  for (int j = 0; j < 4; ++j) {
+                    const float x0 = __uint_as_float(r[g * 8 + 2 * j]), x1 = __uint_as_float(r[g * 8 + 2 * j + 1]);
+                    r[g * 8 + 2 * j] = __float_as_uint(x0 * cv[j] - x1 * sv[j]);
+                    r[g * 8 + 2 * j + 1] = __float_as_uint(x0 * sv[j] + x1 * cv[j]);
+                  }
+                }
+              }
 #pragma unroll
               for (int v = 0; v < 4; ++v) {
                 uint4 o;
@@ -212,7 +229,7 @@ void load_encode() {
 
 template <bool A_MN, bool B_MN, class TO, bool ACC>
 int launch_variant(b200_ctx *ctx, const CUtensorMap &ma, const CUtensorMap &mb, void *C, int M, int N, int K,
-                   size_t ldc) {
+                   size_t ldc, const GemmEpilogue &epi) {
   auto kern = gemm_tc_kernel<A_MN, B_MN, TO, ACC>;
   static bool attr_set = false;
   if (!attr_set) {
@@ -227,7 +244,7 @@ int launch_variant(b200_ctx *ctx, const CUtensorMap &ma, const CUtensorMap &mb, 
     tm.start = ev(); tm.stop = ev(); tm.flops = 2.0 * M * N * K;
     cudaEventRecord(tm.start, ctx->stream);
   }
-  kern<<<grid, THREADS, SMEM_BYTES, ctx->stream>>>(ma, mb, (TO *)C, M, N, K, ldc, ctx->dev_status, g_mn_lbo, g_mn_sbo, g_mn_kadv);
+  kern<<<grid, THREADS, SMEM_BYTES, ctx->stream>>>(ma, mb, (TO *)C, M, N, K, ldc, ctx->dev_status, g_mn_lbo, g_mn_sbo, g_mn_kadv, epi);
   B200_LAUNCHED(ctx);
   if (ctx->time_gemm) { cudaEventRecord(tm.stop, ctx->stream); ctx->timed.push_back(tm); }
   return B200_OK;
@@ -235,10 +252,10 @@ int launch_variant(b200_ctx *ctx, const CUtensorMap &ma, const CUtensorMap &mb, 
 
 template <bool A_MN, bool B_MN>
 int launch_out(b200_ctx *ctx, const CUtensorMap &ma, const CUtensorMap &mb, void *C, int M, int N, int K, size_t ldc,
-               b200_dtype out_dt, int acc) {
-  if (out_dt == B200_BF16) return launch_variant<A_MN, B_MN, bf16, false>(ctx, ma, mb, C, M, N, K, ldc);
-  if (acc) return launch_variant<A_MN, B_MN, float, true>(ctx, ma, mb, C, M, N, K, ldc);
-  return launch_variant<A_MN, B_MN, float, false>(ctx, ma, mb, C, M, N, K, ldc);
+               b200_dtype out_dt, int acc, const GemmEpilogue &epi) {
+  if (out_dt == B200_BF16) return launch_variant<A_MN, B_MN, bf16, false>(ctx, ma, mb, C, M, N, K, ldc, epi);
+  if (acc) return launch_variant<A_MN, B_MN, float, true>(ctx, ma, mb, C, M, N, K, ldc, epi);
+  return launch_variant<A_MN, B_MN, float, false>(ctx, ma, mb, C, M, N, K, ldc, epi);
 }
 
 }  // namespace
@@ -312,8 +329,14 @@ bool gemm_tc_supported(const void *A, const void *B, const void *C, size_t M, si
 }
 
 int gemm_tc_launch(b200_ctx *ctx, const void *A, const void *B, void *C, size_t M, size_t N, size_t K, int ta, int tb,
-                   int acc, b200_dtype out_dt, size_t lda, size_t ldb, size_t ldc) {
+                   int acc, b200_dtype out_dt, size_t lda, size_t ldb, size_t ldc, const GemmEpilogue *epi_in) {
   B200_REQUIRE(ctx, !(acc && out_dt == B200_BF16), "gemm: accumulate needs an fp32 C on the tensor-core path");
+  GemmEpilogue epi;
+  if (epi_in) {
+    epi = *epi_in;
+    B200_REQUIRE(ctx, out_dt == B200_BF16 && epi.cos_t && epi.sin_t && epi.S > 0 && epi.hd % 32 == 0 && epi.cols % 32 == 0 &&
+                 ((uintptr_t)epi.cos_t | (uintptr_t)epi.sin_t) % 16 == 0, "gemm: unsupported fused rotary epilogue");
+  }
   CUtensorMap ma, mb;
   int r;
   // A: stored [M,K] (K inner) or, transposed, [K,M] (M inner)
@@ -326,8 +349,8 @@ int gemm_tc_launch(b200_ctx *ctx, const void *A, const void *B, void *C, size_t 
   if (r) return b200_fail(ctx, B200_ERR_CUDA, "cuTensorMapEncodeTiled(B) failed: %d", r);
   const bool a_mn = ta != 0, b_mn = tb == 0;
   int m = (int)M, n = (int)N, k = (int)K;
-  if (a_mn && b_mn) return launch_out<true, true>(ctx, ma, mb, C, m, n, k, ldc, out_dt, acc);
-  if (a_mn && !b_mn) return launch_out<true, false>(ctx, ma, mb, C, m, n, k, ldc, out_dt, acc);
-  if (!a_mn && b_mn) return launch_out<false, true>(ctx, ma, mb, C, m, n, k, ldc, out_dt, acc);
-  return launch_out<false, false>(ctx, ma, mb, C, m, n, k, ldc, out_dt, acc);
+  if (a_mn && b_mn) return launch_out<true, true>(ctx, ma, mb, C, m, n, k, ldc, out_dt, acc, epi);
+  if (a_mn && !b_mn) return launch_out<true, false>(ctx, ma, mb, C, m, n, k, ldc, out_dt, acc, epi);
+  if (!a_mn && b_mn) return launch_out<false, true>(ctx, ma, mb, C, m, n, k, ldc, out_dt, acc, epi);
+  return launch_out<false, false>(ctx, ma, mb, C, m, n, k, ldc, out_dt, acc, epi);
 }

@@ -299,10 +299,19 @@ static int layer_forward_core(b200_model *m, size_t l, const void *h_in, size_t 
   // inner unit-weight norm (cpp/src/Attention.cpp:192-194)
   TRY(b200_rms_norm_forward(ctx, a.a1, a.a2, m->ones, nullptr, eps, M, H, dt));
   // Q|K|V in one GEMM on the fused weight
-  TRY(b200_gemm_ld(ctx, a.a2, m->P(m->off_qkv(l)), a.qkv, M, m->QKV, H, 0, 0, 0, dt, dt, H, m->QKV, m->QKV));
-  // RoPE on the q and k column blocks, in place (cpp/src/Attention.cpp:203)
+  // RoPE on the q and k column blocks (cpp/src/Attention.cpp:203): in the GEMM epilogue on the tensor-core
+  // path (applied to the fp32 accumulators), else as its own in-place pass
   const long long ld = (long long)m->QKV;
-  TRY(rope_strided(ctx, a.qkv, m->cos_t, m->sin_t, B, m->nH + m->nKV, S, m->hd, (long long)S * ld, (long long)m->hd, ld, dt, false));
+  const bool rope_in_gemm = dt == B200_BF16 && m->hd % 32 == 0 &&
+                            gemm_tc_supported(a.a2, m->P(m->off_qkv(l)), a.qkv, M, m->QKV, H, H, m->QKV, m->QKV, dt);
+  if (rope_in_gemm) {
+    GemmEpilogue epi;
+    epi.cos_t = m->cos_t; epi.sin_t = m->sin_t; epi.S = (int)S; epi.hd = (int)m->hd; epi.cols = (int)(m->Q + m->KV);
+    TRY(b200_gemm_ld(ctx, a.a2, m->P(m->off_qkv(l)), a.qkv, M, m->QKV, H, 0, 0, 0, dt, dt, H, m->QKV, m->QKV, &epi));
+  } else {
+    TRY(b200_gemm_ld(ctx, a.a2, m->P(m->off_qkv(l)), a.qkv, M, m->QKV, H, 0, 0, 0, dt, dt, H, m->QKV, m->QKV));
+    TRY(rope_strided(ctx, a.qkv, m->cos_t, m->sin_t, B, m->nH + m->nKV, S, m->hd, (long long)S * ld, (long long)m->hd, ld, dt, false));
+  }
   AttnStrides st = token_major(m, S);
   const char *qkv = (const char *)a.qkv;
   TRY(attn_fwd_launch(ctx, qkv, qkv + m->Q * dtype_size(dt), qkv + (m->Q + m->KV) * dtype_size(dt), a.o, a.lse, B, m->nH,
@@ -338,10 +347,16 @@ static int layer_backward_core(b200_model *m, size_t l, const void *g, void *g_i
   TRY(b200_gemm_ld(ctx, m->g_h_mid, m->P(m->off_o(l)), m->g_o, M, m->Q, H, 0, 1, 0, dt, dt, H, H, m->Q));
   AttnStrides st = token_major(m, S);
   const char *qkv = (const char *)a.qkv; char *gq = (char *)m->g_qkv;
+  // the gradient of RoPE (inverse rotation of dQ and dK) is applied inside the tensor-core attention backward
+  // where that path runs, else as its own in-place pass (cpp/src/Attention.cpp:544)
+  const bool rope_in_attn = attn_bwd_fuses_rope(B, m->nH, m->nKV, S, m->hd, st, st, dt, qkv, qkv + m->Q * es, qkv + (m->Q + m->KV) * es,
+                                                a.o, m->g_o, gq, gq + m->Q * es, gq + (m->Q + m->KV) * es);
   TRY(attn_bwd_launch(ctx, qkv, qkv + m->Q * es, qkv + (m->Q + m->KV) * es, a.o, m->g_o, a.lse, gq, gq + m->Q * es,
-                      gq + (m->Q + m->KV) * es, B, m->nH, m->nKV, S, m->hd, st, st, dt));
+                      gq + (m->Q + m->KV) * es, B, m->nH, m->nKV, S, m->hd, st, st, dt, rope_in_attn ? m->cos_t : nullptr,
+                      rope_in_attn ? m->sin_t : nullptr));
   const long long ld = (long long)m->QKV;
-  TRY(rope_strided(ctx, gq, m->cos_t, m->sin_t, B, m->nH + m->nKV, S, m->hd, (long long)S * ld, (long long)m->hd, ld, dt, true));
+  if (!rope_in_attn)
+    TRY(rope_strided(ctx, gq, m->cos_t, m->sin_t, B, m->nH + m->nKV, S, m->hd, (long long)S * ld, (long long)m->hd, ld, dt, true));
   TRY(b200_gemm_ld(ctx, a.a2, m->g_qkv, m->G(m->off_qkv(l)), H, m->QKV, M, 1, 0, 0, dt, B200_F32, H, m->QKV, m->QKV));
   TRY(b200_gemm_ld(ctx, m->g_qkv, m->P(m->off_qkv(l)), m->g_a2, M, H, m->QKV, 0, 1, 0, dt, dt, m->QKV, m->QKV, H));
   TRY(b200_rms_norm_backward(ctx, m->g_a2, a.a1, m->ones, m->g_a1, nullptr, eps, M, H, dt));
