@@ -114,6 +114,12 @@ extern "C" int b200_sync(b200_ctx *ctx) {
   return B200_OK;
 }
 
+// Bring-up / A-B hook (not part of the public header): 0 forces the single-CTA tensor-core GEMM.
+extern "C" int b200_internal_set_gemm_2cta(b200_ctx *ctx, int enable) {
+  if (!ctx) return B200_ERR_INVALID;
+  ctx->gemm_2cta = enable != 0;
+  return B200_OK;
+}
 extern "C" int b200_profile_gemm(b200_ctx *ctx, int enable) {
   if (!ctx) return B200_ERR_INVALID;
   ctx->time_gemm = enable != 0;
@@ -184,7 +190,13 @@ int b200_gemm_ld(b200_ctx *ctx, const void *A, const void *B, void *C, size_t M,
     return B200_OK;
   }
   if (in_dt == B200_BF16 && !(acc && out_dt == B200_BF16) && gemm_tc_supported(A, B, C, M, N, K, lda, ldb, ldc, out_dt))
+  {
+    // two-CTA kernel when there are enough 256x256 tile pairs to fill the SM pairs; else 128x256 tiles
+    const size_t pairs = ((M + 255) / 256) * ((N + 255) / 256);
+    if (ctx->gemm_2cta && pairs >= (size_t)ctx->sm_count / 4)
+      return gemm_tc2_launch(ctx, A, B, C, M, N, K, ta, tb, acc, out_dt, lda, ldb, ldc, epi);
     return gemm_tc_launch(ctx, A, B, C, M, N, K, ta, tb, acc, out_dt, lda, ldb, ldc, epi);
+  }
   return gemm_simt_launch(ctx, A, B, C, M, N, K, ta, tb, acc, in_dt, out_dt, lda, ldb, ldc);
 }
 

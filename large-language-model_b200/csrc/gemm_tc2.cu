@@ -1,0 +1,326 @@
+// Two-CTA form of the bf16 tensor-core GEMM (tcgen05 cta_group::2): a cluster of two CTAs on one
+// SM pair computes a 256x256 output tile.  Each CTA stages its own 128 rows of A and only HALF of the
+// B tile (128 of the 256 columns); the pair's tensor cores read both halves, so the shared-memory
+// fill per SM drops from 48 KiB to 32 KiB per 64-deep K slice (the single-CTA kernel is bound by that
+// fill bandwidth) and the ring deepens from 4 to 6 stages.
+//   both CTAs:  warp 0 = TMA producer (loads signal the LEADER's "full" barrier),
+//               warps 2..5 = epilogue of the CTA's own 128 accumulator rows
+//   leader CTA: warp 1 lane 0 issues tcgen05.mma.cta_group::2 (M = 256) and commits completion to the
+//               "empty" / "accumulator full" barriers of both CTAs
+// Same operand handling as gemm_tc.cu (K-major / MN-major through descriptors, ragged edges by TMA
+// zero fill), same optional rotary epilogue.  No load uses multicast; the only cross-CTA traffic is
+// mbarrier arrivals and the tensor cores reading the peer's B half.
+#include "common.cuh"
+#include "tc_common.cuh"
+
+namespace {
+
+constexpr int BM = 128, BN = 256, BK = 64, STAGES = 6;
+constexpr int A_STAGE_BYTES = BM * BK * 2;        // 16 KiB: this CTA's 128 rows
+constexpr int B_STAGE_BYTES = (BN / 2) * BK * 2;  // 16 KiB: this CTA's half of the 256 columns
+constexpr int CHUNK_BYTES = 64 * BK * 2;
+constexpr int SMEM_BYTES = STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + 1024 + 256;
+constexpr int THREADS = 192;
+constexpr int GROUP_M = 8;                        // 256-row tile pairs per rasterisation group
+constexpr uint32_t LEADER_MASK = 0xFEFFFFFFu;     // clears the CTA-rank bit of a shared::cluster address (rank 0)
+constexpr uint32_t PEER_BIT = 0x01000000u;        // rank 1 of the pair
+
+struct SharedTail {
+  uint64_t full[STAGES], empty[STAGES], acc_full[2], acc_empty[2];
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+__device__ __forceinline__ uint32_t cluster_ctarank() { uint32_t r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
+__device__ __forceinline__ void cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(addr) : "memory");
+}
+__device__ __forceinline__ void tma_load_2d_2sm(void *dst, const CUtensorMap *map, int c0, int c1, uint32_t leader_bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(tc::smem_u32(dst)), "l"(map), "r"(leader_bar), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void umma_ss_2sm(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t acc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(acc)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit_2sm(uint32_t bar_addr) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_addr) : "memory");
+}
+// completion of everything issued so far -> the same barrier in both CTAs of the pair
+__device__ __forceinline__ void umma_commit_both(uint64_t *bar) {
+  const uint32_t a = tc::smem_u32(bar) & LEADER_MASK;
+  umma_commit_2sm(a);
+  umma_commit_2sm(a | PEER_BIT);
+}
+__device__ __forceinline__ void tmem_alloc_2sm(uint32_t *dst, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tc::smem_u32(dst)), "r"(ncols) : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_2sm(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+
+// One 32-column chunk of one accumulator row -> global memory (optional rotary embedding, accumulate).
+template <class TO, bool ACC>
+__device__ __forceinline__ void store_chunk(uint32_t (&r)[32], TO *crow, int row, int col, int N, const GemmEpilogue &epi) {
+  if (col + 32 <= N) {
+    if constexpr (sizeof(TO) == 2) {
+      if (epi.cos_t != nullptr && col < epi.cols) {
+        const int half = epi.hd >> 1;
+        const size_t tab = (size_t)(row % epi.S) * half + ((col % epi.hd) >> 1);
+        const float4 *c4 = reinterpret_cast<const float4 *>(epi.cos_t + tab), *s4 = reinterpret_cast<const float4 *>(epi.sin_t + tab);
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          const float4 cc = __ldg(c4 + g), ss = __ldg(s4 + g);
+          const float cv[4] = {cc.x, cc.y, cc.z, cc.w}, sv[4] = {ss.x, ss.y, ss.z, ss.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float x0 = __uint_as_float(r[g * 8 + 2 * j]), x1 = __uint_as_float(r[g * 8 + 2 * j + 1]);
+            r[g * 8 + 2 * j] = __float_as_uint(x0 * cv[j] - x1 * sv[j]);
+            r[g * 8 + 2 * j + 1] = __float_as_uint(x0 * sv[j] + x1 * cv[j]);
+          }
+        }
+      }
+#pragma unroll
+      for (int v = 0; v < 4; ++v) {
+        uint4 o;
+        uint32_t *po = &o.x;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[v * 8 + 2 * j]), __uint_as_float(r[v * 8 + 2 * j + 1]));
+          po[j] = *reinterpret_cast<uint32_t *>(&h);
+        }
+        *reinterpret_cast<uint4 *>(crow + col + v * 8) = o;
+      }
+    } else {
+#pragma unroll
+      for (int v = 0; v < 8; ++v) {
+        float4 o = make_float4(__uint_as_float(r[v * 4]), __uint_as_float(r[v * 4 + 1]), __uint_as_float(r[v * 4 + 2]), __uint_as_float(r[v * 4 + 3]));
+        if (ACC) {
+          float4 p = *reinterpret_cast<const float4 *>(crow + col + v * 4);
+          o.x += p.x; o.y += p.y; o.z += p.z; o.w += p.w;
+        }
+        *reinterpret_cast<float4 *>(crow + col + v * 4) = o;
+      }
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      if (col + j < N) {
+        float v = __uint_as_float(r[j]);
+        if (ACC) v += to_f(crow[col + j]);
+        crow[col + j] = from_f<TO>(v);
+      }
+    }
+  }
+}
+
+template <bool A_MN, bool B_MN, class TO, bool ACC>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                TO *__restrict__ C, int M, int N, int K, size_t ldc, int *status, GemmEpilogue epi) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t *sA = smem, *sB = smem + STAGES * A_STAGE_BYTES;
+  SharedTail *sh = (SharedTail *)(smem + STAGES * (A_STAGE_BYTES + B_STAGE_BYTES));
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+  const int cluster_id = blockIdx.x >> 1, n_clusters = gridDim.x >> 1;
+  const int tiles_m = (M + 2 * BM - 1) / (2 * BM), tiles_n = (N + BN - 1) / BN, total = tiles_m * tiles_n;
+  const int num_kb = (K + BK - 1) / BK;
+  volatile int *abort_flag = &sh->abort_flag;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < STAGES; ++i) { tc::mbar_init(&sh->full[i], 1); tc::mbar_init(&sh->empty[i], 1); }
+    for (int i = 0; i < 2; ++i) { tc::mbar_init(&sh->acc_full[i], 1); tc::mbar_init(&sh->acc_empty[i], 8); }
+    sh->abort_flag = 0;
+    tc::fence_barrier_init();
+    tc::fence_proxy_async();
+    tc::tma_prefetch_desc(&map_a);
+    tc::tma_prefetch_desc(&map_b);
+  }
+  if (warp == 1) tmem_alloc_2sm(&sh->tmem_base, 512);
+  tc::tc_fence_before();
+  __syncthreads();
+  cluster_sync();                      // the peer's barriers are initialised before anything arrives on them
+  tc::tc_fence_after();
+  const uint32_t tmem_base = sh->tmem_base;
+
+  auto tile_coords = [&](int t, int &tm, int &tn) {
+    int per_group = GROUP_M * tiles_n;
+    int g = t / per_group, r = t % per_group;
+    int gm = min(GROUP_M, tiles_m - g * GROUP_M);
+    tm = g * GROUP_M + r % gm;
+    tn = r / gm;
+  };
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0; uint32_t phase = 0;
+      bool ok = true;
+      for (int t = cluster_id; t < total && ok; t += n_clusters) {
+        int tm, tn; tile_coords(t, tm, tn);
+        const int m0 = tm * 2 * BM + (int)rank * BM;            // this CTA's rows
+        const int n0 = tn * BN + (int)rank * (BN / 2);          // this CTA's half of the B columns
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!tc::mbar_wait(&sh->empty[stage], phase ^ 1, status, abort_flag, 111)) { ok = false; break; }
+          const uint32_t full_leader = tc::smem_u32(&sh->full[stage]) & LEADER_MASK;
+          if (leader) tc::mbar_expect_tx(&sh->full[stage], 2 * (A_STAGE_BYTES + B_STAGE_BYTES));
+          uint8_t *a = sA + stage * A_STAGE_BYTES, *b = sB + stage * B_STAGE_BYTES;
+          if (A_MN) {
+#pragma unroll
+            for (int c = 0; c < BM / 64; ++c) tma_load_2d_2sm(a + c * CHUNK_BYTES, &map_a, m0 + c * 64, kb * BK, full_leader);
+          } else {
+            tma_load_2d_2sm(a, &map_a, kb * BK, m0, full_leader);
+          }
+          if (B_MN) {
+#pragma unroll
+            for (int c = 0; c < BN / 128; ++c) tma_load_2d_2sm(b + c * CHUNK_BYTES, &map_b, n0 + c * 64, kb * BK, full_leader);
+          } else {
+            tma_load_2d_2sm(b, &map_b, kb * BK, n0, full_leader);
+          }
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+      if (!ok) { long long t0 = clock64(); while (clock64() - t0 < 2000000ll) {} }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && leader) {
+      constexpr uint32_t idesc = tc::make_idesc_bf16(2 * BM, BN, A_MN, B_MN);
+      int stage = 0; uint32_t phase = 0; int acc = 0; uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int t = cluster_id; t < total && ok; t += n_clusters) {
+        if (!tc::mbar_wait(&sh->acc_empty[acc], acc_phase ^ 1, status, abort_flag, 112)) { ok = false; break; }
+        tc::tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!tc::mbar_wait(&sh->full[stage], phase, status, abort_flag, 113)) { ok = false; break; }
+          tc::tc_fence_after();
+          const uint32_t a_addr = tc::smem_u32(sA + stage * A_STAGE_BYTES), b_addr = tc::smem_u32(sB + stage * B_STAGE_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            uint64_t da = A_MN ? tc::make_smem_desc(a_addr + k * 2048, CHUNK_BYTES, 1024) : tc::make_smem_desc(a_addr + k * 32, 16, 1024);
+            uint64_t db = B_MN ? tc::make_smem_desc(b_addr + k * 2048, CHUNK_BYTES, 1024) : tc::make_smem_desc(b_addr + k * 32, 16, 1024);
+            umma_ss_2sm(d_tmem, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit_both(&sh->empty[stage]);
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        umma_commit_both(&sh->acc_full[acc]);
+        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      }
+    }
+  } else {
+    const int q = warp & 3;
+    int acc = 0; uint32_t acc_phase = 0;
+    bool ok = true;
+    for (int t = cluster_id; t < total && ok; t += n_clusters) {
+      int tm, tn; tile_coords(t, tm, tn);
+      if (!tc::mbar_wait(&sh->acc_full[acc], acc_phase, status, abort_flag, 114)) { ok = false; break; }
+      tc::tc_fence_after();
+      const int row = tm * 2 * BM + (int)rank * BM + q * 32 + lane;
+      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN;
+      TO *crow = C + (size_t)row * ldc;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tc::tmem_ld_32x32(taddr + c * 32, r);
+        tc::tmem_ld_wait();
+        const int col = tn * BN + c * 32;
+        if (row < M && col < N) store_chunk<TO, ACC>(r, crow, row, col, N, epi);
+      }
+      tc::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(tc::smem_u32(&sh->acc_empty[acc]) & LEADER_MASK);   // the leader issues the MMAs
+      if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+    }
+  }
+  tc::tc_fence_before();
+  __syncthreads();
+  cluster_sync();                      // neither CTA leaves while the pair may still touch its shared / tensor memory
+  if (warp == 1) {
+    __syncwarp();
+    tc::tc_fence_after();
+    tmem_dealloc_2sm(tmem_base, 512);
+  }
+}
+
+template <bool A_MN, bool B_MN, class TO, bool ACC>
+int launch_variant(b200_ctx *ctx, const CUtensorMap &ma, const CUtensorMap &mb, void *C, int M, int N, int K,
+                   size_t ldc, const GemmEpilogue &epi) {
+  auto kern = gemm_tc2_kernel<A_MN, B_MN, TO, ACC>;
+  static bool attr_set = false;
+  static int max_clusters = 0;
+  cudaLaunchConfig_t cfg = {};
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+  cfg.blockDim = dim3(THREADS); cfg.dynamicSmemBytes = SMEM_BYTES; cfg.stream = ctx->stream; cfg.attrs = attr; cfg.numAttrs = 1;
+  if (!attr_set) {
+    B200_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    cfg.gridDim = dim3(ctx->sm_count & ~1);
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n <= 0) { cudaGetLastError(); n = ctx->sm_count / 2; }
+    max_clusters = n;
+    attr_set = true;
+  }
+  const int pairs = ((M + 2 * BM - 1) / (2 * BM)) * ((N + BN - 1) / BN);
+  const int clusters = pairs < max_clusters ? pairs : max_clusters;
+  cfg.gridDim = dim3(2 * clusters);
+  b200_ctx::Timed tm{};
+  if (ctx->time_gemm) {
+    auto ev = [&]() { cudaEvent_t e; if (ctx->event_pool.empty()) cudaEventCreate(&e); else { e = ctx->event_pool.back(); ctx->event_pool.pop_back(); } return e; };
+    tm.start = ev(); tm.stop = ev(); tm.flops = 2.0 * M * N * K;
+    cudaEventRecord(tm.start, ctx->stream);
+  }
+  B200_CUDA(ctx, cudaLaunchKernelEx(&cfg, kern, ma, mb, (TO *)C, M, N, K, ldc, ctx->dev_status, epi));
+  ctx->launches++;
+  if (ctx->time_gemm) { cudaEventRecord(tm.stop, ctx->stream); ctx->timed.push_back(tm); }
+  return B200_OK;
+}
+
+template <bool A_MN, bool B_MN>
+int launch_out(b200_ctx *ctx, const CUtensorMap &ma, const CUtensorMap &mb, void *C, int M, int N, int K, size_t ldc,
+               b200_dtype out_dt, int acc, const GemmEpilogue &epi) {
+  if (out_dt == B200_BF16) return launch_variant<A_MN, B_MN, bf16, false>(ctx, ma, mb, C, M, N, K, ldc, epi);
+  if (acc) return launch_variant<A_MN, B_MN, float, true>(ctx, ma, mb, C, M, N, K, ldc, epi);
+  return launch_variant<A_MN, B_MN, float, false>(ctx, ma, mb, C, M, N, K, ldc, epi);
+}
+}  // namespace
+
+// Same contract as gemm_tc_launch (gemm_tc.cu); worthwhile when there are enough 256x256 tile pairs.
+int gemm_tc2_launch(b200_ctx *ctx, const void *A, const void *B, void *C, size_t M, size_t N, size_t K, int ta, int tb,
+                    int acc, b200_dtype out_dt, size_t lda, size_t ldb, size_t ldc, const GemmEpilogue *epi_in) {
+  B200_REQUIRE(ctx, !(acc && out_dt == B200_BF16), "gemm: accumulate needs an fp32 C on the tensor-core path");
+  GemmEpilogue epi;
+  if (epi_in) {
+    epi = *epi_in;
+    B200_REQUIRE(ctx, out_dt == B200_BF16 && epi.cos_t && epi.sin_t && epi.S > 0 && epi.hd % 32 == 0 && epi.cols % 32 == 0 &&
+                 ((uintptr_t)epi.cos_t | (uintptr_t)epi.sin_t) % 16 == 0, "gemm: unsupported fused rotary epilogue");
+  }
+  CUtensorMap ma, mb;
+  int r;
+  if (!ta) r = tc_make_map_2d(&ma, A, K, M, lda * 2, BK, BM);
+  else r = tc_make_map_2d(&ma, A, M, K, lda * 2, 64, BK);
+  if (r) return b200_fail(ctx, B200_ERR_CUDA, "cuTensorMapEncodeTiled(A) failed: %d", r);
+  if (!tb) r = tc_make_map_2d(&mb, B, N, K, ldb * 2, 64, BK);
+  else r = tc_make_map_2d(&mb, B, K, N, ldb * 2, BK, BN / 2);
+  if (r) return b200_fail(ctx, B200_ERR_CUDA, "cuTensorMapEncodeTiled(B) failed: %d", r);
+  const bool a_mn = ta != 0, b_mn = tb == 0;
+  int m = (int)M, n = (int)N, k = (int)K;
+  if (a_mn && b_mn) return launch_out<true, true>(ctx, ma, mb, C, m, n, k, ldc, out_dt, acc, epi);
+  if (a_mn && !b_mn) return launch_out<true, false>(ctx, ma, mb, C, m, n, k, ldc, out_dt, acc, epi);
+  if (!a_mn && b_mn) return launch_out<false, true>(ctx, ma, mb, C, m, n, k, ldc, out_dt, acc, epi);
+  return launch_out<false, false>(ctx, ma, mb, C, m, n, k, ldc, out_dt, acc, epi);
+}

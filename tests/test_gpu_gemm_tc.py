@@ -26,6 +26,16 @@ def _ref(A, B, ta, tb):
 FORMS = [(False, False), (False, True), (True, False), (True, True)]
 
 
+@pytest.fixture(params=[1, 0], ids=["two_cta", "one_cta"], autouse=True)
+def gemm_kernel_choice(ctx, request):
+    """Every test runs with the two-CTA (cta_group::2) kernel enabled for large shapes and with the
+    single-CTA kernel forced (internal A/B hook of the library)."""
+    ctx.lib.b200_internal_set_gemm_2cta.argtypes = [bridge._vp, bridge._i]
+    ctx.lib.b200_internal_set_gemm_2cta(ctx.h, request.param)
+    yield
+    ctx.lib.b200_internal_set_gemm_2cta(ctx.h, 1)
+
+
 @pytest.mark.parametrize("ta,tb", FORMS)
 @pytest.mark.parametrize("M,N,K", [(128, 256, 64), (128, 256, 256), (256, 512, 128), (384, 256, 1024)])
 def test_aligned_tiles(ctx, ta, tb, M, N, K):
@@ -38,7 +48,7 @@ def test_aligned_tiles(ctx, ta, tb, M, N, K):
 
 
 @pytest.mark.parametrize("ta,tb", FORMS)
-@pytest.mark.parametrize("M,N,K", [(8, 8, 8), (136, 264, 72), (200, 328, 200), (1000, 520, 136), (16, 3072, 2048)])
+@pytest.mark.parametrize("M,N,K", [(8, 8, 8), (136, 264, 72), (200, 328, 200), (1000, 520, 136), (16, 3072, 2048), (2500, 2200, 200), (3000, 9000, 72)])
 def test_ragged_edges(ctx, ta, tb, M, N, K):
     A, B = _ab(M, N, K, ta, tb)
     out = ctx.gemm(ctx.array(A, "bf16"), ctx.array(B, "bf16"), M, N, K, ta, tb, out_dtype="f32").download()
