@@ -70,8 +70,13 @@ __device__ __forceinline__ void tmem_dealloc_2sm(uint32_t taddr, uint32_t ncols)
 }
 
 // One 32-column chunk of one accumulator row -> global memory (optional rotary embedding, accumulate).
+__device__ __forceinline__ void red_add_v4(float *p, float a, float b, float c, float d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+// `red`: this tile is one K-split of several -> add into C with vector reductions instead of storing.
 template <class TO, bool ACC>
-__device__ __forceinline__ void store_chunk(uint32_t (&r)[32], TO *crow, int row, int col, int N, const GemmEpilogue &epi) {
+__device__ __forceinline__ void store_chunk(uint32_t (&r)[32], TO *crow, int row, int col, int N, const GemmEpilogue &epi,
+                                            bool red) {
   if (col + 32 <= N) {
     if constexpr (sizeof(TO) == 2) {
       if (epi.cos_t != nullptr && col < epi.cols) {
@@ -105,6 +110,7 @@ __device__ __forceinline__ void store_chunk(uint32_t (&r)[32], TO *crow, int row
 #pragma unroll
       for (int v = 0; v < 8; ++v) {
         float4 o = make_float4(__uint_as_float(r[v * 4]), __uint_as_float(r[v * 4 + 1]), __uint_as_float(r[v * 4 + 2]), __uint_as_float(r[v * 4 + 3]));
+        if (red) { red_add_v4(reinterpret_cast<float *>(crow + col + v * 4), o.x, o.y, o.z, o.w); continue; }
         if (ACC) {
           float4 p = *reinterpret_cast<const float4 *>(crow + col + v * 4);
           o.x += p.x; o.y += p.y; o.z += p.z; o.w += p.w;
@@ -117,6 +123,9 @@ __device__ __forceinline__ void store_chunk(uint32_t (&r)[32], TO *crow, int row
     for (int j = 0; j < 32; ++j) {
       if (col + j < N) {
         float v = __uint_as_float(r[j]);
+        if constexpr (sizeof(TO) == 4) {
+          if (red) { atomicAdd(reinterpret_cast<float *>(crow + col + j), v); continue; }
+        }
         if (ACC) v += to_f(crow[col + j]);
         crow[col + j] = from_f<TO>(v);
       }
@@ -127,7 +136,7 @@ __device__ __forceinline__ void store_chunk(uint32_t (&r)[32], TO *crow, int row
 template <bool A_MN, bool B_MN, class TO, bool ACC>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                TO *__restrict__ C, int M, int N, int K, size_t ldc, int *status, GemmEpilogue epi) {
+                TO *__restrict__ C, int M, int N, int K, size_t ldc, int *status, GemmEpilogue epi, int splits) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t *sA = smem, *sB = smem + STAGES * A_STAGE_BYTES;
@@ -138,6 +147,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   const int cluster_id = blockIdx.x >> 1, n_clusters = gridDim.x >> 1;
   const int tiles_m = (M + 2 * BM - 1) / (2 * BM), tiles_n = (N + BN - 1) / BN, total = tiles_m * tiles_n;
   const int num_kb = (K + BK - 1) / BK;
+  const int items = total * splits;                 // work item = (tile pair, K split); all tiles of split 0 first
   volatile int *abort_flag = &sh->abort_flag;
 
   if (threadIdx.x == 0) {
@@ -168,11 +178,12 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     if (lane == 0) {
       int stage = 0; uint32_t phase = 0;
       bool ok = true;
-      for (int t = cluster_id; t < total && ok; t += n_clusters) {
-        int tm, tn; tile_coords(t, tm, tn);
+      for (int it = cluster_id; it < items && ok; it += n_clusters) {
+        int tm, tn; tile_coords(it % total, tm, tn);
+        const int sp = it / total, kb0 = sp * num_kb / splits, kb1 = (sp + 1) * num_kb / splits;
         const int m0 = tm * 2 * BM + (int)rank * BM;            // this CTA's rows
         const int n0 = tn * BN + (int)rank * (BN / 2);          // this CTA's half of the B columns
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!tc::mbar_wait(&sh->empty[stage], phase ^ 1, status, abort_flag, 111)) { ok = false; break; }
           const uint32_t full_leader = tc::smem_u32(&sh->full[stage]) & LEADER_MASK;
           if (leader) tc::mbar_expect_tx(&sh->full[stage], 2 * (A_STAGE_BYTES + B_STAGE_BYTES));
@@ -199,11 +210,12 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       constexpr uint32_t idesc = tc::make_idesc_bf16(2 * BM, BN, A_MN, B_MN);
       int stage = 0; uint32_t phase = 0; int acc = 0; uint32_t acc_phase = 0;
       bool ok = true;
-      for (int t = cluster_id; t < total && ok; t += n_clusters) {
+      for (int it = cluster_id; it < items && ok; it += n_clusters) {
+        const int sp = it / total, kb0 = sp * num_kb / splits, kb1 = (sp + 1) * num_kb / splits;
         if (!tc::mbar_wait(&sh->acc_empty[acc], acc_phase ^ 1, status, abort_flag, 112)) { ok = false; break; }
         tc::tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!tc::mbar_wait(&sh->full[stage], phase, status, abort_flag, 113)) { ok = false; break; }
           tc::tc_fence_after();
           const uint32_t a_addr = tc::smem_u32(sA + stage * A_STAGE_BYTES), b_addr = tc::smem_u32(sB + stage * B_STAGE_BYTES);
@@ -211,7 +223,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           for (int k = 0; k < BK / 16; ++k) {
             uint64_t da = A_MN ? tc::make_smem_desc(a_addr + k * 2048, CHUNK_BYTES, 1024) : tc::make_smem_desc(a_addr + k * 32, 16, 1024);
             uint64_t db = B_MN ? tc::make_smem_desc(b_addr + k * 2048, CHUNK_BYTES, 1024) : tc::make_smem_desc(b_addr + k * 32, 16, 1024);
-            umma_ss_2sm(d_tmem, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+            umma_ss_2sm(d_tmem, da, db, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
           }
           umma_commit_both(&sh->empty[stage]);
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
@@ -225,8 +237,8 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     const int q = warp & 3;
     int acc = 0; uint32_t acc_phase = 0;
     bool ok = true;
-    for (int t = cluster_id; t < total && ok; t += n_clusters) {
-      int tm, tn; tile_coords(t, tm, tn);
+    for (int it = cluster_id; it < items && ok; it += n_clusters) {
+      int tm, tn; tile_coords(it % total, tm, tn);
       if (!tc::mbar_wait(&sh->acc_full[acc], acc_phase, status, abort_flag, 114)) { ok = false; break; }
       tc::tc_fence_after();
       const int row = tm * 2 * BM + (int)rank * BM + q * 32 + lane;
@@ -238,7 +250,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         tc::tmem_ld_32x32(taddr + c * 32, r);
         tc::tmem_ld_wait();
         const int col = tn * BN + c * 32;
-        if (row < M && col < N) store_chunk<TO, ACC>(r, crow, row, col, N, epi);
+        if (row < M && col < N) store_chunk<TO, ACC>(r, crow, row, col, N, epi, splits > 1);
       }
       tc::tc_fence_before();
       __syncwarp();
@@ -276,7 +288,19 @@ int launch_variant(b200_ctx *ctx, const CUtensorMap &ma, const CUtensorMap &mb, 
     attr_set = true;
   }
   const int pairs = ((M + 2 * BM - 1) / (2 * BM)) * ((N + BN - 1) / BN);
-  const int clusters = pairs < max_clusters ? pairs : max_clusters;
+  // Split K (fp32 output only: partial tiles are added with vector reductions) when whole tile pairs fill the
+  // SM pairs badly -- the weight-gradient GEMMs have few tiles and a 16384-deep K.
+  int splits = 1;
+  if (sizeof(TO) == 4 && ldc == (size_t)N) {
+    const int num_kb = (K + BK - 1) / BK;
+    auto eff = [&](int s) { int items = pairs * s; int waves = (items + max_clusters - 1) / max_clusters; return (double)items / ((double)waves * max_clusters); };
+    double best = eff(1);
+    for (int s = 2; s <= 4; ++s)
+      if (num_kb / s >= 16 && eff(s) > best + 0.08) { best = eff(s); splits = s; }
+    if (splits > 1 && !ACC) B200_CUDA(ctx, cudaMemsetAsync(C, 0, (size_t)M * N * sizeof(float), ctx->stream));
+  }
+  const int items = pairs * splits;
+  const int clusters = items < max_clusters ? items : max_clusters;
   cfg.gridDim = dim3(2 * clusters);
   b200_ctx::Timed tm{};
   if (ctx->time_gemm) {
@@ -284,7 +308,7 @@ int launch_variant(b200_ctx *ctx, const CUtensorMap &ma, const CUtensorMap &mb, 
     tm.start = ev(); tm.stop = ev(); tm.flops = 2.0 * M * N * K;
     cudaEventRecord(tm.start, ctx->stream);
   }
-  B200_CUDA(ctx, cudaLaunchKernelEx(&cfg, kern, ma, mb, (TO *)C, M, N, K, ldc, ctx->dev_status, epi));
+  B200_CUDA(ctx, cudaLaunchKernelEx(&cfg, kern, ma, mb, (TO *)C, M, N, K, ldc, ctx->dev_status, epi, splits));
   ctx->launches++;
   if (ctx->time_gemm) { cudaEventRecord(tm.stop, ctx->stream); ctx->timed.push_back(tm); }
   return B200_OK;
