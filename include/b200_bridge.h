@@ -227,6 +227,39 @@ int b200_model_layer_forward(b200_model *m, size_t layer, const void *h_in, void
 int b200_model_layer_backward(b200_model *m, size_t layer, const void *grad_out, void *grad_h_in, size_t batch,
                               size_t seq_len);
 
+/* ---- autoregressive decode with a KV cache.
+ * The reference C++ engine threads a KVCache through its signatures but never uses it
+ * (cpp/include/TransformerConfig.hpp:121-124, cpp/src/Attention.cpp:171-284) and generates by re-running
+ * the full context per token in Python (python/pipeline/inference/sampler.py:115-148).  Here the
+ * prompt is run once (prefill fills per-layer K/V caches), then each step runs one token per sequence.
+ * Sampling rules follow sampler.py:43-108 (repetition penalty over the last 128 ids, top-k, top-p,
+ * temperature; temperature 0 = greedy argmax, lowest id on ties). */
+typedef struct {
+  float temperature, top_p, repetition_penalty;
+  int top_k;                       /* 0 disables */
+  uint64_t seed;                   /* counter-based: token t of sequence b depends only on (seed, t, b) */
+  int n_whitespace_ids;            /* ids never penalised (sampler.py:27-28), at most 8 */
+  int whitespace_ids[8];
+} b200_sampler_config;
+/* One sampling step for `batch` rows of device logits [batch, vocab] (vocab <= 32768).  history is a device
+ * int32 [batch, hist_ld] array whose first hist_len entries per row are the ids seen so far; with append != 0
+ * the drawn id is also stored at history[b, hist_len].  out_threshold / out_kept (optional, device) receive
+ * the logit threshold and the number of surviving ids per row, for checking the filters. */
+int b200_sample(b200_ctx *ctx, const void *logits, b200_dtype dtype, size_t batch, size_t vocab, int32_t *history,
+                size_t hist_len, size_t hist_ld, int append, const b200_sampler_config *cfg, uint64_t step,
+                int32_t *out_tokens, float *out_threshold, int32_t *out_kept);
+/* Allocates K/V caches for `batch` sequences of up to max_total_len positions (<= max_seq_len of the model). */
+int b200_model_decode_begin(b200_model *m, size_t batch, size_t max_total_len);
+/* Runs the prompt [batch, prompt_len] (device ids), fills the caches, writes the logits of the last prompt
+ * position to logits_last (device, compute dtype, [batch, vocab]). */
+int b200_model_prefill(b200_model *m, const int32_t *dev_tokens, size_t batch, size_t prompt_len, void *logits_last);
+/* One token per sequence at position `pos` (= number of positions already in the cache): logits [batch, vocab]. */
+int b200_model_decode_step(b200_model *m, const int32_t *dev_tokens, size_t batch, size_t pos, void *logits);
+/* Whole generation from HOST buffers: prompt [batch, prompt_len] in, [batch, new_tokens] ids out.
+ * decode_ms (optional) receives the device time of the new_tokens-1 decode steps (prefill excluded). */
+int b200_model_generate(b200_model *m, const int32_t *host_prompt, size_t batch, size_t prompt_len, size_t new_tokens,
+                        const b200_sampler_config *cfg, int32_t *host_out, float *prefill_ms, float *decode_ms);
+
 /* ---- data parallel (no counterpart in the reference, which is single-device):
  * replicas all-reduce (average) fp32 gradient buckets with NCCL on a side
  * stream as soon as each layer's weight gradients are enqueued. */

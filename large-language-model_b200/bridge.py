@@ -40,6 +40,17 @@ class Shape:
         self.eps, self.rope_base = eps, rope_base
 
 
+class SamplerConfig(C.Structure):
+    """Decode hyper-parameters (python/pipeline/inference/sampler.py:18-28 of the reference)."""
+    _fields_ = [("temperature", _f), ("top_p", _f), ("repetition_penalty", _f), ("top_k", _i), ("seed", C.c_uint64),
+                ("n_whitespace_ids", _i), ("whitespace_ids", _i * 8)]
+
+    @classmethod
+    def make(cls, temperature=0.0, top_p=1.0, repetition_penalty=1.0, top_k=0, seed=0, whitespace_ids=()):
+        ws = (list(whitespace_ids) + [-1] * 8)[:8]
+        return cls(temperature, top_p, repetition_penalty, top_k, seed, min(len(whitespace_ids), 8), (_i * 8)(*ws))
+
+
 class AdamWParams(C.Structure):
     _fields_ = [(n, _f) for n in ("lr", "beta1", "beta2", "eps", "weight_decay", "bias_correction1",
                                   "bias_correction2")]
@@ -99,6 +110,11 @@ _SIGS = {
     "b200_model_train_step": (_i, [_vp, _vp, _vp, _sz, _sz, _f, _f, _f, _f, _f, _vp]),
     "b200_model_layer_forward": (_i, [_vp, _sz, _vp, _vp, _sz, _sz]),
     "b200_model_layer_backward": (_i, [_vp, _sz, _vp, _vp, _sz, _sz]),
+    "b200_sample": (_i, [_vp, _vp, _i, _sz, _sz, _vp, _sz, _sz, _i, C.POINTER(SamplerConfig), C.c_uint64, _vp, _vp, _vp]),
+    "b200_model_decode_begin": (_i, [_vp, _sz, _sz]),
+    "b200_model_prefill": (_i, [_vp, _vp, _sz, _sz, _vp]),
+    "b200_model_decode_step": (_i, [_vp, _vp, _sz, _sz, _vp]),
+    "b200_model_generate": (_i, [_vp, _vp, _sz, _sz, _sz, C.POINTER(SamplerConfig), _vp, C.POINTER(_f), C.POINTER(_f)]),
     "b200_dp_unique_id": (_i, [_vp]),
     "b200_dp_init": (_i, [_vp, _vp, _i, _i]),
     "b200_dp_shutdown": (_i, [_vp]),
@@ -352,6 +368,15 @@ class Context:
         self._check(self.lib.b200_cross_entropy_noalloc(self.h, logits.ptr, targets.ptr, loss.ptr,
                                                         grad.ptr if grad is not None else None, T, V, logits.code))
 
+    def sample(self, logits, history, hist_len, sampler: "SamplerConfig", step=0, append=False):
+        """One sampling step; returns (tokens, threshold, kept) device arrays."""
+        B, V = logits.shape
+        tok, thr, kept = self.empty((B,), "i32"), self.empty((B,), "f32"), self.empty((B,), "i32")
+        self._check(self.lib.b200_sample(self.h, logits.ptr, logits.code, B, V, history.ptr if history is not None else None,
+                                         hist_len, history.shape[1] if history is not None else 0, int(append),
+                                         C.byref(sampler), step, tok.ptr, thr.ptr, kept.ptr))
+        return tok, thr, kept
+
     def adamw_step(self, p, g, m, v, lr, beta1, beta2, eps, wd, step, shadow=None):
         bc1 = float(np.float32(1.0) - np.float32(beta1) ** np.float32(step))
         bc2 = float(np.float32(1.0) - np.float32(beta2) ** np.float32(step))
@@ -479,6 +504,30 @@ class Model:
         out = self.ctx.empty(grad_out.shape, grad_out.dtype)
         self.ctx._check(self.ctx.lib.b200_model_layer_backward(self.h, layer, grad_out.ptr, out.ptr, B, S))
         return out
+
+    # ---- decode -------------------------------------------------------------
+    def decode_begin(self, batch: int, max_total_len: int):
+        self.ctx._check(self.ctx.lib.b200_model_decode_begin(self.h, batch, max_total_len))
+
+    def prefill(self, tokens_dev: DeviceArray, B: int, P: int) -> DeviceArray:
+        logits = self.ctx.empty((B, self.cfg.V), self.dtype)
+        self.ctx._check(self.ctx.lib.b200_model_prefill(self.h, tokens_dev.ptr, B, P, logits.ptr))
+        return logits
+
+    def decode_step(self, tokens_dev: DeviceArray, B: int, pos: int) -> DeviceArray:
+        logits = self.ctx.empty((B, self.cfg.V), self.dtype)
+        self.ctx._check(self.ctx.lib.b200_model_decode_step(self.h, tokens_dev.ptr, B, pos, logits.ptr))
+        return logits
+
+    def generate(self, prompt: np.ndarray, new_tokens: int, sampler: "SamplerConfig"):
+        """prompt [B, P] host ids -> ([B, new_tokens] ids, prefill ms, decode ms)."""
+        prompt = np.ascontiguousarray(prompt, np.int32)
+        B, P = prompt.shape
+        out = np.empty((B, new_tokens), np.int32)
+        pm, dm = _f(0.0), _f(0.0)
+        self.ctx._check(self.ctx.lib.b200_model_generate(self.h, _np_ptr(prompt), B, P, new_tokens, C.byref(sampler),
+                                                         _np_ptr(out), C.byref(pm), C.byref(dm)))
+        return out, float(pm.value), float(dm.value)
 
     def dp_init(self, unique_id: bytes, rank: int, world: int):
         buf = C.create_string_buffer(unique_id, 128)

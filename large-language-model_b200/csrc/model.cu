@@ -91,6 +91,11 @@ struct b200_model {
   float *d_loss = nullptr;
   int32_t *pin_tokens = nullptr, *pin_targets = nullptr; float *pin_loss = nullptr;
   std::vector<void *> allocs;
+  // decode: per-layer K/V caches [cache_batch, cache_len, KV] (keys stored after RoPE), generation buffers
+  std::vector<void *> k_cache, v_cache;
+  size_t cache_batch = 0, cache_len = 0;
+  void *dec_logits = nullptr, *dec_h = nullptr;      // [cache_batch, V], [cache_batch, H]
+  int32_t *dec_history = nullptr, *dec_next = nullptr;
   // data parallel
   nccl::comm_t comm = nullptr;
   int rank = 0, world = 1;
@@ -536,4 +541,130 @@ extern "C" int b200_dp_shutdown(b200_model *m) {
   cudaEventDestroy(m->ev_grad_ready); cudaEventDestroy(m->ev_comm_done);
   cudaStreamDestroy(m->comm_stream);
   return B200_OK;
+}
+
+// ---- autoregressive decode ------------------------------------------------------------------
+int kv_append(b200_ctx *, const void *, void *, void *, size_t, size_t, size_t, size_t, size_t, size_t, size_t, b200_dtype);
+int attn_decode(b200_ctx *, const void *, const void *, const void *, void *, size_t, size_t, size_t, size_t, size_t,
+                size_t, size_t, size_t, b200_dtype);
+int gather_rows(b200_ctx *, const void *, void *, size_t, size_t, size_t, size_t, b200_dtype);
+
+extern "C" int b200_model_decode_begin(b200_model *m, size_t batch, size_t max_total_len) {
+  if (!m) return B200_ERR_INVALID;
+  b200_ctx *ctx = m->ctx;
+  B200_REQUIRE(ctx, batch > 0 && batch <= m->max_batch && max_total_len > 0 && max_total_len <= m->cfg.max_seq_len,
+               "decode_begin: batch / length exceed what the model was created for");
+  if (m->cache_batch >= batch && m->cache_len >= max_total_len) return B200_OK;
+  B200_REQUIRE(ctx, m->k_cache.empty(), "decode_begin: caches already allocated with a smaller shape");
+  const size_t es = dtype_size(m->dt), bytes = batch * max_total_len * m->KV * es;
+  m->k_cache.assign(m->L, nullptr); m->v_cache.assign(m->L, nullptr);
+  for (size_t l = 0; l < m->L; ++l) { TRY(dalloc(m, &m->k_cache[l], bytes)); TRY(dalloc(m, &m->v_cache[l], bytes)); }
+  TRY(dalloc(m, &m->dec_logits, batch * m->V * es));
+  TRY(dalloc(m, &m->dec_h, batch * m->H * es));
+  TRY(dalloc(m, (void **)&m->dec_history, batch * max_total_len * sizeof(int32_t)));
+  TRY(dalloc(m, (void **)&m->dec_next, batch * sizeof(int32_t)));
+  m->cache_batch = batch; m->cache_len = max_total_len;
+  return B200_OK;
+}
+
+extern "C" int b200_model_prefill(b200_model *m, const int32_t *tok, size_t B, size_t P, void *logits_last) {
+  if (!m) return B200_ERR_INVALID;
+  b200_ctx *ctx = m->ctx;
+  TRY(check_shape(m, B, P));
+  B200_REQUIRE(ctx, tok && logits_last && B <= m->cache_batch && P <= m->cache_len, "prefill: call decode_begin first");
+  TRY(forward_all(m, tok, B, P));
+  for (size_t l = 0; l < m->L; ++l)
+    TRY(kv_append(ctx, m->acts[l].qkv, m->k_cache[l], m->v_cache[l], B, P, 0, m->cache_len, m->Q, m->KV, m->QKV, m->dt));
+  // logits of the last prompt position only
+  TRY(gather_rows(ctx, m->fh, m->dec_h, B, P, m->H, P - 1, m->dt));
+  return b200_gemm_ld(ctx, m->dec_h, m->P(m->off_out()), logits_last, B, m->V, m->H, 0, 0, 0, m->dt, m->dt, m->H, m->V, m->V);
+}
+
+// One decoder layer for one new token per sequence (rows = sequences); h in hs[l], result h_mid/tmpH as in the
+// training forward so that the caller fuses the residual add with the next norm.
+static int layer_decode_core(b200_model *m, size_t l, const void *h_in, size_t B, size_t pos) {
+  b200_ctx *ctx = m->ctx;
+  const size_t H = m->H, I = m->I;
+  const float eps = m->cfg.rms_norm_eps;
+  b200_model::Act &a = m->acts[l];
+  const b200_dtype dt = m->dt;
+  const size_t es = dtype_size(dt), half = m->hd / 2;
+  TRY(b200_rms_norm_forward(ctx, a.a1, a.a2, m->ones, nullptr, eps, B, H, dt));
+  const float *cos_p = m->cos_t + pos * half, *sin_p = m->sin_t + pos * half;    // every row is at position `pos`
+  const bool rope_in_gemm = dt == B200_BF16 && m->hd % 32 == 0 && (pos * half * 4) % 16 == 0 &&
+                            gemm_tc_supported(a.a2, m->P(m->off_qkv(l)), a.qkv, B, m->QKV, H, H, m->QKV, m->QKV, dt);
+  if (rope_in_gemm) {
+    GemmEpilogue epi;
+    epi.cos_t = cos_p; epi.sin_t = sin_p; epi.S = 1; epi.hd = (int)m->hd; epi.cols = (int)(m->Q + m->KV);
+    TRY(b200_gemm_ld(ctx, a.a2, m->P(m->off_qkv(l)), a.qkv, B, m->QKV, H, 0, 0, 0, dt, dt, H, m->QKV, m->QKV, &epi));
+  } else {
+    TRY(b200_gemm_ld(ctx, a.a2, m->P(m->off_qkv(l)), a.qkv, B, m->QKV, H, 0, 0, 0, dt, dt, H, m->QKV, m->QKV));
+    TRY(rope_strided(ctx, a.qkv, cos_p, sin_p, B, m->nH + m->nKV, 1, m->hd, (long long)m->QKV, (long long)m->hd, (long long)m->QKV, dt, false));
+  }
+  TRY(kv_append(ctx, a.qkv, m->k_cache[l], m->v_cache[l], B, 1, pos, m->cache_len, m->Q, m->KV, m->QKV, dt));
+  TRY(attn_decode(ctx, a.qkv, m->k_cache[l], m->v_cache[l], a.o, B, m->nH, m->nKV, m->hd, m->cache_len, pos + 1, m->QKV, m->Q, dt));
+  TRY(b200_gemm_ld(ctx, a.o, m->P(m->off_o(l)), m->tmpH, B, H, m->Q, 0, 0, 0, dt, dt, m->Q, H, H));
+  TRY(add_norm_oop(ctx, h_in, m->tmpH, a.h_mid, m->P(m->off_ffn_norm(l)), a.ffn_in, B, H, eps, dt));
+  TRY(b200_gemm_ld(ctx, a.ffn_in, m->P(m->off_gate_up(l)), a.gate_up, B, 2 * I, H, 0, 0, 0, dt, dt, H, 2 * I, 2 * I));
+  TRY(swiglu_fwd_strided(ctx, a.gate_up, (char *)a.gate_up + I * es, a.act, B, I, 2 * I, I, dt));
+  TRY(b200_gemm_ld(ctx, a.act, m->P(m->off_down(l)), m->tmpH, B, H, I, 0, 0, 0, dt, dt, I, H, H));
+  return B200_OK;
+}
+
+extern "C" int b200_model_decode_step(b200_model *m, const int32_t *tok, size_t B, size_t pos, void *logits) {
+  if (!m) return B200_ERR_INVALID;
+  b200_ctx *ctx = m->ctx;
+  B200_REQUIRE(ctx, tok && logits && B > 0 && B <= m->cache_batch && pos < m->cache_len, "decode_step: bad arguments");
+  const size_t H = m->H;
+  const float eps = m->cfg.rms_norm_eps;
+  const b200_dtype dt = m->dt;
+  TRY(b200_embedding_forward(ctx, (const uint32_t *)tok, m->P(m->off_emb()), m->hs[0], B, H, m->V, dt));
+  if (m->L == 0) {
+    TRY(b200_rms_norm_forward(ctx, m->hs[0], m->fh, m->P(m->off_final_norm()), nullptr, eps, B, H, dt));
+  } else {
+    TRY(b200_rms_norm_forward(ctx, m->hs[0], m->acts[0].a1, m->P(m->off_attn_norm(0)), nullptr, eps, B, H, dt));
+    for (size_t l = 0; l < m->L; ++l) {
+      TRY(layer_decode_core(m, l, m->hs[l], B, pos));
+      const void *w = (l + 1 < m->L) ? m->P(m->off_attn_norm(l + 1)) : m->P(m->off_final_norm());
+      void *y = (l + 1 < m->L) ? m->acts[l + 1].a1 : m->fh;
+      TRY(add_norm_oop(ctx, m->acts[l].h_mid, m->tmpH, m->hs[l + 1], w, y, B, H, eps, dt));
+    }
+  }
+  return b200_gemm_ld(ctx, m->fh, m->P(m->off_out()), logits, B, m->V, H, 0, 0, 0, dt, dt, H, m->V, m->V);
+}
+
+extern "C" int b200_model_generate(b200_model *m, const int32_t *host_prompt, size_t B, size_t P, size_t new_tokens,
+                                   const b200_sampler_config *cfg, int32_t *host_out, float *prefill_ms, float *decode_ms) {
+  if (!m) return B200_ERR_INVALID;
+  b200_ctx *ctx = m->ctx;
+  B200_REQUIRE(ctx, host_prompt && cfg && host_out && new_tokens > 0, "generate: null pointer");
+  TRY(b200_model_decode_begin(m, B, P + new_tokens));
+  const size_t ld = m->cache_len;
+  // history rows hold prompt then generated ids (the repetition penalty looks at both, sampler.py:130-137)
+  B200_CUDA(ctx, cudaMemcpy2DAsync(m->dec_history, ld * 4, host_prompt, P * 4, P * 4, B, cudaMemcpyHostToDevice, ctx->stream));
+  int32_t *d_prompt = nullptr;
+  TRY(b200_malloc(ctx, B * P * 4, (void **)&d_prompt));
+  int rc = b200_memcpy_h2d(ctx, d_prompt, host_prompt, B * P * 4);
+  cudaEvent_t e0, e1, e2;
+  cudaEventCreate(&e0); cudaEventCreate(&e1); cudaEventCreate(&e2);
+  cudaEventRecord(e0, ctx->stream);
+  if (!rc) rc = b200_model_prefill(m, d_prompt, B, P, m->dec_logits);
+  if (!rc) rc = b200_sample(ctx, m->dec_logits, m->dt, B, m->V, m->dec_history, P, ld, 1, cfg, 0, m->dec_next, nullptr, nullptr);
+  cudaEventRecord(e1, ctx->stream);
+  for (size_t t = 1; t < new_tokens && !rc; ++t) {
+    rc = b200_model_decode_step(m, m->dec_next, B, P + t - 1, m->dec_logits);
+    if (!rc) rc = b200_sample(ctx, m->dec_logits, m->dt, B, m->V, m->dec_history, P + t, ld, 1, cfg, t, m->dec_next, nullptr, nullptr);
+  }
+  cudaEventRecord(e2, ctx->stream);
+  if (!rc) {
+    cudaError_t ce = cudaMemcpy2DAsync(host_out, new_tokens * 4, m->dec_history + P, ld * 4, new_tokens * 4, B, cudaMemcpyDeviceToHost, ctx->stream);
+    if (ce != cudaSuccess) rc = b200_fail(ctx, B200_ERR_CUDA, "copy of generated ids failed: %s", cudaGetErrorString(ce));
+  }
+  int rs = b200_sync(ctx);
+  float ms = 0.f;
+  if (prefill_ms) { cudaEventElapsedTime(&ms, e0, e1); *prefill_ms = ms; }
+  if (decode_ms) { cudaEventElapsedTime(&ms, e1, e2); *decode_ms = ms; }
+  cudaEventDestroy(e0); cudaEventDestroy(e1); cudaEventDestroy(e2);
+  b200_free(ctx, d_prompt);
+  return rc ? rc : rs;
 }
