@@ -120,6 +120,12 @@ extern "C" int b200_internal_set_gemm_2cta(b200_ctx *ctx, int enable) {
   ctx->gemm_2cta = enable != 0;
   return B200_OK;
 }
+// Same kind of hook: 0 sends few-row GEMMs through the general tile kernel instead of the weight-streaming one.
+extern "C" int b200_internal_set_gemm_skinny(b200_ctx *ctx, int enable) {
+  if (!ctx) return B200_ERR_INVALID;
+  ctx->gemm_skinny = enable != 0;
+  return B200_OK;
+}
 extern "C" int b200_profile_gemm(b200_ctx *ctx, int enable) {
   if (!ctx) return B200_ERR_INVALID;
   ctx->time_gemm = enable != 0;
@@ -191,6 +197,9 @@ int b200_gemm_ld(b200_ctx *ctx, const void *A, const void *B, void *C, size_t M,
   }
   if (in_dt == B200_BF16 && !(acc && out_dt == B200_BF16) && gemm_tc_supported(A, B, C, M, N, K, lda, ldb, ldc, out_dt))
   {
+    // a handful of rows against a stored [K,N] weight: bound by streaming the weight, own kernel
+    if (ctx->gemm_skinny && gemm_skinny_supported(M, ta, tb, acc))
+      return gemm_skinny_launch(ctx, A, B, C, M, N, K, out_dt, lda, ldb, ldc, epi);
     // two-CTA kernel when there are enough 256x256 tile pairs to fill the SM pairs; else 128x256 tiles
     const size_t pairs = ((M + 255) / 256) * ((N + 255) / 256);
     if (ctx->gemm_2cta && pairs >= (size_t)ctx->sm_count / 4)

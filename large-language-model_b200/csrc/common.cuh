@@ -29,6 +29,7 @@ struct b200_ctx {
   // optional per-launch timing of the tensor-core GEMM (CUDA events on the launching stream)
   // 1: large bf16 GEMMs use the two-CTA (cta_group::2) kernel; 0: always the single-CTA kernel
   int gemm_2cta = 1;
+  int gemm_skinny = 1;
   bool time_gemm = false;
   struct Timed { cudaEvent_t start, stop; double flops; };
   std::vector<Timed> timed;
@@ -132,6 +133,9 @@ int gemm_tc_launch(b200_ctx *ctx, const void *A, const void *B, void *C, size_t 
                    int acc, b200_dtype out_dt, size_t lda, size_t ldb, size_t ldc, const GemmEpilogue *epi = nullptr);
 int gemm_tc2_launch(b200_ctx *ctx, const void *A, const void *B, void *C, size_t M, size_t N, size_t K, int ta, int tb,
                     int acc, b200_dtype out_dt, size_t lda, size_t ldb, size_t ldc, const GemmEpilogue *epi = nullptr);
+bool gemm_skinny_supported(size_t M, int ta, int tb, int acc);
+int gemm_skinny_launch(b200_ctx *ctx, const void *A, const void *W, void *C, size_t M, size_t N, size_t K, b200_dtype out_dt,
+                       size_t lda, size_t ldb, size_t ldc, const GemmEpilogue *epi = nullptr);
 bool gemm_tc_supported(const void *A, const void *B, const void *C, size_t M, size_t N, size_t K, size_t lda,
                        size_t ldb, size_t ldc, b200_dtype out_dt);
 // Strided general form used by the engine (leading dimensions in elements).

@@ -1,0 +1,236 @@
+// Single-query GQA attention over the KV cache (decode: one new token per sequence).
+// The reference engine declares a KVCache (cpp/include/TransformerConfig.hpp:121-124) but never uses it;
+// the maths is the causal GQA attention of cpp/src/Attention.cpp:236-280 for the last query position.
+//
+// HBM/L2-bound: every K and V row of the cache is read once per KV head.  Work split:
+//   grid = (key splits, query-head groups, sequences); a CTA of 8 warps takes one contiguous run of
+//   keys for GQ query heads that share a KV head (GQ = nH/nKV when that is 1, 2, 4 or 8, so the K/V
+//   rows are read once for the whole group); a warp takes one key at a time, the lanes split the head
+//   dimension (coalesced row reads), scores are reduced with shuffles and folded into an online softmax.
+//   Warps merge through shared memory, splits merge through a small fp32 workspace: the CTA that
+//   arrives last at a per-(sequence, group) ticket does the final merge (no waiting anywhere).
+// The new token's K/V row is taken from the projection output and appended to the cache here.
+#include "common.cuh"
+
+namespace {
+
+constexpr int WARPS = 8;
+
+template <class T, int EPL> struct RowLoad;
+template <int EPL> struct RowLoad<bf16, EPL> {
+  static __device__ __forceinline__ void load(const bf16 *p, float *f) {
+    if constexpr (EPL == 1) { f[0] = to_f(p[0]); }
+    else if constexpr (EPL == 2) { const float2 v = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(p)); f[0] = v.x; f[1] = v.y; }
+    else if constexpr (EPL == 4) {
+      const uint2 u = *reinterpret_cast<const uint2 *>(p);
+      const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&u.x)), b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&u.y));
+      f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y;
+    } else {
+      const uint4 u = *reinterpret_cast<const uint4 *>(p);
+      const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) { const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&w[i])); f[2 * i] = a.x; f[2 * i + 1] = a.y; }
+    }
+  }
+  static __device__ __forceinline__ void store(bf16 *p, const float *f) {
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) p[i] = __float2bfloat16(f[i]);
+  }
+};
+template <int EPL> struct RowLoad<float, EPL> {
+  static __device__ __forceinline__ void load(const float *p, float *f) {
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) f[i] = p[i];
+  }
+  static __device__ __forceinline__ void store(float *p, const float *f) {
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) p[i] = f[i];
+  }
+};
+
+struct DecodeAttnArgs {
+  const void *q, *k_new, *v_new;     // rows of the fused projection output (row stride ldq elements)
+  void *kc, *vc, *o;                 // caches [B, S_max, nKV*hd]; output [B, ldo]
+  float *ws_o, *ws_ml;               // [B, nH, splits, hd] and [B, nH, splits, 2]
+  int *tickets;                      // [B, nH / GQ], zero between launches
+  int nH, nKV, S_max, t_len, ldq, ldo, chunk;
+  float scale;
+};
+
+// EPL = head_dim / 32 elements per lane; GQ = query heads per CTA (all share one KV head).
+template <class T, int EPL, int GQ>
+__global__ void __launch_bounds__(WARPS * 32)
+attn_decode_kernel(DecodeAttnArgs a) {
+  constexpr int HD = EPL * 32;
+  __shared__ float s_o[WARPS][GQ][HD];
+  __shared__ float s_m[WARPS][GQ], s_l[WARPS][GQ];
+  __shared__ int s_last;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int split = blockIdx.x, nsplit = gridDim.x, grp = blockIdx.y, b = blockIdx.z;
+  const int G = a.nH / a.nKV, h0 = grp * GQ, kvh = h0 / G, KV = a.nKV * HD;
+  const int t_len = a.t_len;
+  const int k0 = split * a.chunk, k1 = min(t_len, k0 + a.chunk);
+  const T *q = (const T *)a.q + (size_t)b * a.ldq + (size_t)h0 * HD + lane * EPL;
+  T *kc = (T *)a.kc + (size_t)b * a.S_max * KV + (size_t)kvh * HD + lane * EPL;
+  T *vc = (T *)a.vc + (size_t)b * a.S_max * KV + (size_t)kvh * HD + lane * EPL;
+
+  float qf[GQ][EPL], acc[GQ][EPL], m[GQ], l[GQ];
+#pragma unroll
+  for (int g = 0; g < GQ; ++g) {
+    RowLoad<T, EPL>::load(q + g * HD, qf[g]);
+    m[g] = -INFINITY; l[g] = 0.f;
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) { qf[g][e] *= a.scale; acc[g][e] = 0.f; }
+  }
+#pragma unroll 2
+  for (int j = k0 + warp; j < k1; j += WARPS) {
+    float kf[EPL], vf[EPL];
+    if (j == t_len - 1 && a.k_new != nullptr) {
+      // the token being decoded: read its K/V from the projection output and append them to the cache
+      RowLoad<T, EPL>::load((const T *)a.k_new + (size_t)b * a.ldq + (size_t)kvh * HD + lane * EPL, kf);
+      RowLoad<T, EPL>::load((const T *)a.v_new + (size_t)b * a.ldq + (size_t)kvh * HD + lane * EPL, vf);
+      if (h0 % G == 0) {
+        RowLoad<T, EPL>::store(kc + (size_t)j * KV, kf);
+        RowLoad<T, EPL>::store(vc + (size_t)j * KV, vf);
+      }
+    } else {
+      RowLoad<T, EPL>::load(kc + (size_t)j * KV, kf);
+      RowLoad<T, EPL>::load(vc + (size_t)j * KV, vf);
+    }
+    float s[GQ];
+#pragma unroll
+    for (int g = 0; g < GQ; ++g) {
+      float d = 0.f;
+#pragma unroll
+      for (int e = 0; e < EPL; ++e) d += qf[g][e] * kf[e];
+      s[g] = d;
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+#pragma unroll
+      for (int g = 0; g < GQ; ++g) s[g] += __shfl_xor_sync(0xffffffffu, s[g], off);
+    }
+#pragma unroll
+    for (int g = 0; g < GQ; ++g) {
+      const float m_new = fmaxf(m[g], s[g]);
+      const float corr = __expf(m[g] - m_new), p = __expf(s[g] - m_new);
+      l[g] = l[g] * corr + p;
+#pragma unroll
+      for (int e = 0; e < EPL; ++e) acc[g][e] = acc[g][e] * corr + p * vf[e];
+      m[g] = m_new;
+    }
+  }
+  // ---- merge the warps of this CTA ------------------------------------------------------------
+#pragma unroll
+  for (int g = 0; g < GQ; ++g) {
+    if (lane == 0) { s_m[warp][g] = m[g]; s_l[warp][g] = l[g]; }
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) s_o[warp][g][lane * EPL + e] = acc[g][e];
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < GQ * HD; i += WARPS * 32) {
+    const int g = i / HD, d = i % HD;
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < WARPS; ++w) M = fmaxf(M, s_m[w][g]);
+    float L = 0.f, O = 0.f;
+#pragma unroll
+    for (int w = 0; w < WARPS; ++w) {
+      const float f = s_m[w][g] == -INFINITY ? 0.f : __expf(s_m[w][g] - M);
+      L += s_l[w][g] * f; O += s_o[w][g][d] * f;
+    }
+    if (nsplit == 1) {
+      ((T *)a.o)[(size_t)b * a.ldo + (size_t)(h0 + g) * HD + d] = from_f<T>(O / L);
+    } else {
+      const size_t slot = ((size_t)b * a.nH + h0 + g) * nsplit + split;
+      a.ws_o[slot * HD + d] = O;
+      if (d == 0) { a.ws_ml[slot * 2] = M; a.ws_ml[slot * 2 + 1] = L; }
+    }
+  }
+  if (nsplit == 1) return;
+  // ---- the CTA that takes the last ticket merges the splits --------------------------------------
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int *t = a.tickets + (size_t)b * gridDim.y + grp;
+    const int prev = atomicAdd(t, 1);
+    s_last = prev == nsplit - 1;
+    if (s_last) *t = 0;                            // ready for the next launch
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  for (int i = threadIdx.x; i < GQ * HD; i += WARPS * 32) {
+    const int g = i / HD, d = i % HD;
+    const size_t slot0 = ((size_t)b * a.nH + h0 + g) * nsplit;
+    float M = -INFINITY;
+    for (int s = 0; s < nsplit; ++s) M = fmaxf(M, __ldcg(a.ws_ml + (slot0 + s) * 2));
+    float L = 0.f, O = 0.f;
+    for (int s = 0; s < nsplit; ++s) {
+      const float ms = __ldcg(a.ws_ml + (slot0 + s) * 2);
+      const float f = ms == -INFINITY ? 0.f : __expf(ms - M);
+      L += __ldcg(a.ws_ml + (slot0 + s) * 2 + 1) * f;
+      O += __ldcg(a.ws_o + (slot0 + s) * HD + d) * f;
+    }
+    ((T *)a.o)[(size_t)b * a.ldo + (size_t)(h0 + g) * HD + d] = from_f<T>(O / L);
+  }
+}
+
+template <class T, int EPL>
+int launch_gq(b200_ctx *ctx, const DecodeAttnArgs &a, int gq, dim3 grid) {
+  switch (gq) {
+    case 8:
+      if constexpr (EPL < 8) { attn_decode_kernel<T, EPL, 8><<<grid, WARPS * 32, 0, ctx->stream>>>(a); break; }
+      else return b200_fail(ctx, B200_ERR_INVALID, "attn_decode: 8 heads of dimension 256 per CTA exceed shared memory");
+    case 4: attn_decode_kernel<T, EPL, 4><<<grid, WARPS * 32, 0, ctx->stream>>>(a); break;
+    case 2: attn_decode_kernel<T, EPL, 2><<<grid, WARPS * 32, 0, ctx->stream>>>(a); break;
+    default: attn_decode_kernel<T, EPL, 1><<<grid, WARPS * 32, 0, ctx->stream>>>(a); break;
+  }
+  B200_LAUNCHED(ctx);
+  return B200_OK;
+}
+template <class T>
+int launch_hd(b200_ctx *ctx, const DecodeAttnArgs &a, int hd, int gq, dim3 grid) {
+  switch (hd) {
+    case 32: return launch_gq<T, 1>(ctx, a, gq, grid);
+    case 64: return launch_gq<T, 2>(ctx, a, gq, grid);
+    case 128: return launch_gq<T, 4>(ctx, a, gq, grid);
+    default: return launch_gq<T, 8>(ctx, a, gq, grid);   // head_dim 256: the caller keeps gq <= 4 (shared memory)
+  }
+}
+
+}  // namespace
+
+constexpr int ATTN_DECODE_MAX_SPLITS = 16;
+
+size_t attn_decode_workspace_floats(size_t B, size_t nH, size_t hd) { return B * nH * ATTN_DECODE_MAX_SPLITS * (hd + 2); }
+
+// q/k_new/v_new: rows of the fused projection (stride ldq); k_new/v_new may be null when the cache already
+// holds position t_len-1.  ws: attn_decode_workspace_floats() floats; tickets: B*nH ints, zero-initialised.
+int attn_decode(b200_ctx *ctx, const void *q, const void *k_new, const void *v_new, void *kc, void *vc, void *o, size_t B,
+                size_t nH, size_t nKV, size_t hd, size_t S_max, size_t t_len, size_t ldq, size_t ldo, float *ws, int *tickets,
+                b200_dtype dt) {
+  B200_REQUIRE(ctx, (hd == 32 || hd == 64 || hd == 128 || hd == 256) && t_len >= 1 && t_len <= S_max && nKV > 0 && nH % nKV == 0,
+               "attn_decode: head_dim must be 32, 64, 128 or 256 and 1 <= length <= cache length");
+  B200_REQUIRE(ctx, ws && tickets && B <= 65535, "attn_decode: workspace missing");
+  const size_t G = nH / nKV;
+  int gq = (G == 2 || G == 4 || G == 8) ? (int)G : 1;
+  if (hd == 256 && gq > 4) gq = 1;
+  DecodeAttnArgs a;
+  a.q = q; a.k_new = k_new; a.v_new = v_new; a.kc = kc; a.vc = vc; a.o = o;
+  a.ws_o = ws; a.ws_ml = ws + B * nH * ATTN_DECODE_MAX_SPLITS * hd; a.tickets = tickets;
+  a.nH = (int)nH; a.nKV = (int)nKV; a.S_max = (int)S_max; a.t_len = (int)t_len; a.ldq = (int)ldq; a.ldo = (int)ldo;
+  a.scale = 1.0f / sqrtf((float)hd);
+  // key runs: enough CTAs for two waves of the SMs, at least 8 keys per warp, at most 16 splits
+  const size_t groups = B * (nH / gq);
+  size_t want = (2 * (size_t)ctx->sm_count + groups - 1) / groups;
+  if (want > (size_t)ATTN_DECODE_MAX_SPLITS) want = ATTN_DECODE_MAX_SPLITS;
+  size_t chunk = (t_len + want - 1) / want;
+  if (chunk < 64) chunk = 64;
+  chunk = (chunk + WARPS - 1) / WARPS * WARPS;
+  const size_t nsplit = (t_len + chunk - 1) / chunk;
+  a.chunk = (int)chunk;
+  dim3 grid((unsigned)nsplit, (unsigned)(nH / gq), (unsigned)B);
+  if (dt == B200_BF16) return launch_hd<bf16>(ctx, a, (int)hd, gq, grid);
+  return launch_hd<float>(ctx, a, (int)hd, gq, grid);
+}

@@ -96,6 +96,8 @@ struct b200_model {
   size_t cache_batch = 0, cache_len = 0;
   void *dec_logits = nullptr, *dec_h = nullptr;      // [cache_batch, V], [cache_batch, H]
   int32_t *dec_history = nullptr, *dec_next = nullptr;
+  float *dec_attn_ws = nullptr;                      // partial results of the split-key decode attention
+  int *dec_attn_tickets = nullptr;                   // [cache_batch, nH], zero between launches
   // data parallel
   nccl::comm_t comm = nullptr;
   int rank = 0, world = 1;
@@ -545,8 +547,10 @@ extern "C" int b200_dp_shutdown(b200_model *m) {
 
 // ---- autoregressive decode ------------------------------------------------------------------
 int kv_append(b200_ctx *, const void *, void *, void *, size_t, size_t, size_t, size_t, size_t, size_t, size_t, b200_dtype);
-int attn_decode(b200_ctx *, const void *, const void *, const void *, void *, size_t, size_t, size_t, size_t, size_t,
-                size_t, size_t, size_t, b200_dtype);
+size_t attn_decode_workspace_floats(size_t B, size_t nH, size_t hd);
+int attn_decode(b200_ctx *ctx, const void *q, const void *k_new, const void *v_new, void *kc, void *vc, void *o, size_t B,
+                size_t nH, size_t nKV, size_t hd, size_t S_max, size_t t_len, size_t ldq, size_t ldo, float *ws, int *tickets,
+                b200_dtype dt);
 int gather_rows(b200_ctx *, const void *, void *, size_t, size_t, size_t, size_t, b200_dtype);
 
 extern "C" int b200_model_decode_begin(b200_model *m, size_t batch, size_t max_total_len) {
@@ -563,6 +567,9 @@ extern "C" int b200_model_decode_begin(b200_model *m, size_t batch, size_t max_t
   TRY(dalloc(m, &m->dec_h, batch * m->H * es));
   TRY(dalloc(m, (void **)&m->dec_history, batch * max_total_len * sizeof(int32_t)));
   TRY(dalloc(m, (void **)&m->dec_next, batch * sizeof(int32_t)));
+  TRY(dalloc(m, (void **)&m->dec_attn_ws, attn_decode_workspace_floats(batch, m->nH, m->hd) * sizeof(float)));
+  TRY(dalloc(m, (void **)&m->dec_attn_tickets, batch * m->nH * sizeof(int)));
+  TRY(b200_fill_zero(ctx, m->dec_attn_tickets, batch * m->nH * sizeof(int)));
   m->cache_batch = batch; m->cache_len = max_total_len;
   return B200_OK;
 }
@@ -601,8 +608,9 @@ static int layer_decode_core(b200_model *m, size_t l, const void *h_in, size_t B
     TRY(b200_gemm_ld(ctx, a.a2, m->P(m->off_qkv(l)), a.qkv, B, m->QKV, H, 0, 0, 0, dt, dt, H, m->QKV, m->QKV));
     TRY(rope_strided(ctx, a.qkv, cos_p, sin_p, B, m->nH + m->nKV, 1, m->hd, (long long)m->QKV, (long long)m->hd, (long long)m->QKV, dt, false));
   }
-  TRY(kv_append(ctx, a.qkv, m->k_cache[l], m->v_cache[l], B, 1, pos, m->cache_len, m->Q, m->KV, m->QKV, dt));
-  TRY(attn_decode(ctx, a.qkv, m->k_cache[l], m->v_cache[l], a.o, B, m->nH, m->nKV, m->hd, m->cache_len, pos + 1, m->QKV, m->Q, dt));
+  // attention over the cache; the new token's K/V rows go from the projection output into the cache in the same kernel
+  TRY(attn_decode(ctx, a.qkv, (const char *)a.qkv + m->Q * es, (const char *)a.qkv + (m->Q + m->KV) * es, m->k_cache[l], m->v_cache[l],
+                  a.o, B, m->nH, m->nKV, m->hd, m->cache_len, pos + 1, m->QKV, m->Q, m->dec_attn_ws, m->dec_attn_tickets, dt));
   TRY(b200_gemm_ld(ctx, a.o, m->P(m->off_o(l)), m->tmpH, B, H, m->Q, 0, 0, 0, dt, dt, m->Q, H, H));
   TRY(add_norm_oop(ctx, h_in, m->tmpH, a.h_mid, m->P(m->off_ffn_norm(l)), a.ffn_in, B, H, eps, dt));
   TRY(b200_gemm_ld(ctx, a.ffn_in, m->P(m->off_gate_up(l)), a.gate_up, B, 2 * I, H, 0, 0, 0, dt, dt, H, 2 * I, 2 * I));

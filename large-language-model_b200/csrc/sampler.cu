@@ -1,0 +1,269 @@
+// On-device sampler for the decode loop.  Rules follow the reference's Python sampler
+// (python/pipeline/inference/sampler.py:43-108): repetition penalty over the last 128 ids
+// (v/p if v>0 else v*p, then -(p-1)*35, whitespace ids exempt), top-k (keep logits >= the k-th largest),
+// top-p (softmax of the survivors in descending order, keep through the first index whose cumulative
+// probability exceeds p, at least two tokens), then a categorical draw from logits/temperature, or the
+// lowest-id argmax at temperature 0.
+//
+// One CTA of 1024 threads per sequence; the penalised logits of the row live in shared memory as fp32.
+// Nothing is sorted: the k-th largest value and the top-p crossing value are found by repeated linear
+// histograms (2048 bins) over a shrinking value range, walking the bins from the largest values down.
+// Probability mass is accumulated as 2^-40 fixed point integers, so the result does not depend on the order
+// in which threads add to a bin, and a given (logits, seed, step, row) always yields the same token.
+#include "common.cuh"
+
+namespace {
+
+constexpr int THREADS = 1024, BINS = 2048, MAX_V = 32768, WINDOW = 128;
+
+__device__ __forceinline__ uint64_t mix64(uint64_t x) {
+  x += 0x9E3779B97F4A7C15ull;
+  uint64_t z = x;
+  z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+  z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+  return z ^ (z >> 31);
+}
+
+struct SamplerArgs {
+  int V, hist_len, hist_ld, top_k, n_ws;
+  float penalty, top_p, temperature;
+  uint64_t seed, step;
+  int ws[8];
+};
+
+struct Scratch {
+  uint32_t cnt[BINS];
+  unsigned long long mass[BINS];
+  unsigned long long wtot[32], ctot[32];
+  float fred[32], fred2[32];
+  int ired[32];
+  int sel_bin, sel_above_c;
+  unsigned long long sel_above_w;
+  int pick;
+};
+
+__device__ __forceinline__ float block_max(float v, float *red) {
+  v = warp_max(v);
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+  __syncthreads();
+  float r = red[threadIdx.x & 31];
+  return warp_max(r);
+}
+__device__ __forceinline__ float block_min(float v, float *red) { return -block_max(-v, red); }
+__device__ __forceinline__ unsigned long long block_sum_u64(unsigned long long v, unsigned long long *red) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+  __syncthreads();
+  unsigned long long r = red[threadIdx.x & 31];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) r += __shfl_xor_sync(0xffffffffu, r, o);
+  return r;
+}
+// exclusive prefix over the 1024 threads (thread order), 64-bit
+__device__ __forceinline__ unsigned long long block_excl_scan(unsigned long long v, unsigned long long *red) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  unsigned long long inc = v;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) { const unsigned long long t = __shfl_up_sync(0xffffffffu, inc, o); if (lane >= o) inc += t; }
+  __syncthreads();
+  if (lane == 31) red[warp] = inc;
+  __syncthreads();
+  unsigned long long w = red[lane], winc = w;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) { const unsigned long long t = __shfl_up_sync(0xffffffffu, winc, o); if (lane >= o) winc += t; }
+  const unsigned long long wex = __shfl_sync(0xffffffffu, winc - w, warp);
+  return wex + inc - v;
+}
+
+__device__ __forceinline__ unsigned long long qmass(float x, float mx) { return (unsigned long long)(__expf(x - mx) * 1099511627776.0f); }
+
+// Walk the finite keys >= floor_v from the largest down, adding 1 per key (BY_COUNT) or its fixed-point softmax
+// numerator; find the value v* at which the running total first exceeds `target`.  above_c / above_w are the count and
+// weight of the keys strictly greater than v*.  Returns false when the total never exceeds the target.
+template <bool BY_COUNT>
+__device__ bool select_desc(const float *keys, int V, float floor_v, float mx, unsigned long long target, float &vstar,
+                            int &above_c, unsigned long long &above_w, Scratch *s) {
+  const int tid = threadIdx.x;
+  float lo_l = INFINITY;
+  for (int i = tid; i < V; i += THREADS) { const float x = keys[i]; if (x >= floor_v && x > -INFINITY) lo_l = fminf(lo_l, x); }
+  float lo = block_min(lo_l, s->fred), hi = mx;
+  above_c = 0; above_w = 0;
+  if (!(lo <= hi)) return false;                       // no finite key at or above the floor
+  for (int iter = 0; iter < 8; ++iter) {
+    const float scale = hi > lo ? (float)(BINS - 1) / (hi - lo) : 0.f;
+    s->cnt[tid] = 0; s->cnt[tid + THREADS] = 0; s->mass[tid] = 0; s->mass[tid + THREADS] = 0;
+    if (tid == 0) s->sel_bin = -1;
+    __syncthreads();
+    for (int i = tid; i < V; i += THREADS) {
+      const float x = keys[i];
+      if (x >= lo && x <= hi) {
+        const int bin = min(BINS - 1, (int)((hi - x) * scale));
+        atomicAdd(&s->cnt[bin], 1u);
+        if (!BY_COUNT) atomicAdd(&s->mass[bin], qmass(x, mx));
+      }
+    }
+    __syncthreads();
+    const unsigned long long c0 = s->cnt[2 * tid], c1 = s->cnt[2 * tid + 1];
+    const unsigned long long w0 = BY_COUNT ? c0 : s->mass[2 * tid], w1 = BY_COUNT ? c1 : s->mass[2 * tid + 1];
+    const unsigned long long ex_w = block_excl_scan(w0 + w1, s->wtot);
+    const unsigned long long ex_c = BY_COUNT ? ex_w : block_excl_scan(c0 + c1, s->ctot);
+    const unsigned long long base = above_w + ex_w;
+    if (base <= target && target < base + w0) { s->sel_bin = 2 * tid; s->sel_above_w = base; s->sel_above_c = above_c + (int)ex_c; }
+    else if (base + w0 <= target && target < base + w0 + w1) { s->sel_bin = 2 * tid + 1; s->sel_above_w = base + w0; s->sel_above_c = above_c + (int)(ex_c + c0); }
+    __syncthreads();
+    const int sel = s->sel_bin;
+    if (sel < 0) return false;
+    above_w = s->sel_above_w; above_c = s->sel_above_c;
+    float nlo = INFINITY, nhi = -INFINITY;
+    for (int i = tid; i < V; i += THREADS) {
+      const float x = keys[i];
+      if (x >= lo && x <= hi && min(BINS - 1, (int)((hi - x) * scale)) == sel) { nlo = fminf(nlo, x); nhi = fmaxf(nhi, x); }
+    }
+    nlo = block_min(nlo, s->fred); nhi = block_max(nhi, s->fred2);
+    hi = nhi; lo = nlo;
+    if (hi == lo) break;
+  }
+  vstar = hi;
+  return true;
+}
+
+template <class T>
+__global__ void __launch_bounds__(THREADS)
+sample_kernel(const T *__restrict__ logits, int32_t *history, int32_t *__restrict__ out_tokens,
+              float *__restrict__ out_threshold, int32_t *__restrict__ out_kept, SamplerArgs a, int append) {
+  extern __shared__ float keys[];                  // V penalised logits
+  __shared__ Scratch sc;
+  __shared__ int recent[WINDOW];
+  const int b = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const T *row = logits + (size_t)b * a.V;
+  for (int v = tid; v < a.V; v += THREADS) keys[v] = to_f(row[v]);
+  const int n_hist = a.penalty != 1.0f ? min(a.hist_len, WINDOW) : 0;
+  if (tid < n_hist) recent[tid] = history[(size_t)b * a.hist_ld + a.hist_len - n_hist + tid];
+  __syncthreads();
+  if (tid < n_hist) {                              // each distinct, non-whitespace recent id is penalised once
+    const int id = recent[tid];
+    bool skip = id < 0 || id >= a.V;
+    for (int w = 0; w < a.n_ws; ++w) skip |= (a.ws[w] == id);
+    for (int j = 0; j < tid; ++j) skip |= (recent[j] == id);
+    if (!skip) { const float x = keys[id]; keys[id] = (x > 0.f ? x / a.penalty : x * a.penalty) - (a.penalty - 1.0f) * 35.0f; }
+  }
+  __syncthreads();
+  float mx_l = -INFINITY;
+  for (int v = tid; v < a.V; v += THREADS) mx_l = fmaxf(mx_l, keys[v]);
+  const float mx = block_max(mx_l, sc.fred);
+
+  float thr = -INFINITY;
+  const bool want_filters = a.temperature > 0.f || out_threshold != nullptr || out_kept != nullptr;
+  if (want_filters) {
+    int above_c; unsigned long long above_w; float vstar;
+    if (a.top_k > 0 && a.top_k < a.V) {
+      if (select_desc<true>(keys, a.V, -INFINITY, mx, (unsigned long long)(a.top_k - 1), vstar, above_c, above_w, &sc)) thr = vstar;
+    }
+    if (a.top_p < 1.0f) {
+      unsigned long long z_l = 0;
+      for (int v = tid; v < a.V; v += THREADS) { const float x = keys[v]; if (x >= thr && x > -INFINITY) z_l += qmass(x, mx); }
+      const unsigned long long Z = block_sum_u64(z_l, sc.wtot);
+      const unsigned long long target = (unsigned long long)((double)a.top_p * (double)Z);
+      if (select_desc<false>(keys, a.V, thr, mx, target, vstar, above_c, above_w, &sc)) {
+        float cut = vstar;
+        if (above_c == 0 && qmass(mx, mx) > target) {
+          // the top token alone crosses p: the reference still keeps the second entry of the sorted order
+          int n_top = 0; float second_l = -INFINITY;
+          for (int v = tid; v < a.V; v += THREADS) { const float x = keys[v]; if (x == mx) ++n_top; else second_l = fmaxf(second_l, x); }
+          const unsigned long long n_max = block_sum_u64((unsigned long long)n_top, sc.ctot);
+          const float second = block_max(second_l, sc.fred);
+          cut = n_max >= 2 ? mx : second;
+        }
+        thr = fmaxf(thr, cut);
+      }
+    }
+  }
+  // ---- kept set, then the draw in token-id order: warp w owns ids [w*per_w, (w+1)*per_w) ----------------
+  const float invT = a.temperature > 0.f ? 1.0f / a.temperature : 0.f;
+  const int per_w = ((a.V + 31) / 32 + 31) / 32 * 32, v_lo = warp * per_w, v_hi = min(a.V, v_lo + per_w);
+  float wsum = 0.f; int cnt = 0; int last_kept = -1;
+  for (int v = v_lo + lane; v < v_hi; v += 32) {
+    const float x = keys[v];
+    if (x >= thr) { ++cnt; wsum += __expf((x - mx) * invT); last_kept = v; }
+  }
+  const int kept = (int)block_sum_u64((unsigned long long)cnt, sc.ctot);
+  if (tid == 0) { if (out_threshold) out_threshold[b] = thr; if (out_kept) out_kept[b] = kept; sc.pick = a.V; }
+  if (a.temperature > 0.f) {
+    const float wt = warp_sum(wsum);
+    last_kept = __reduce_max_sync(0xffffffffu, last_kept);
+    __syncthreads();
+    if (lane == 0) { sc.fred[warp] = wt; sc.ired[warp] = last_kept; }
+    __syncthreads();
+    // every warp scans the 32 warp totals (same arithmetic everywhere)
+    const float my = sc.fred[lane];
+    float inc = my;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) { const float t = __shfl_up_sync(0xffffffffu, inc, o); if (lane >= o) inc += t; }
+    const float W = __shfl_sync(0xffffffffu, inc, 31);
+    const uint64_t bits = mix64(a.seed ^ mix64(a.step * 0x10001ull + (uint64_t)b));
+    const float u = ((float)(bits >> 40) + 0.5f) * (1.0f / 16777216.0f);
+    const float target = u * W;
+    const unsigned hit = __ballot_sync(0xffffffffu, my > 0.f && inc >= target);
+    const unsigned any = __ballot_sync(0xffffffffu, my > 0.f);
+    const int sel_warp = hit ? __ffs(hit) - 1 : 31 - __clz(any);     // rounding: fall back to the last warp with weight
+    if (warp == sel_warp) {
+      float run = __shfl_sync(0xffffffffu, inc - my, sel_warp);
+      int found = -1;
+      for (int v0 = v_lo; v0 < v_hi && found < 0; v0 += 32) {
+        const int v = v0 + lane;
+        const float x = v < v_hi ? keys[v] : -INFINITY;
+        const float w = (v < v_hi && x >= thr) ? __expf((x - mx) * invT) : 0.f;
+        float winc = w;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) { const float t = __shfl_up_sync(0xffffffffu, winc, o); if (lane >= o) winc += t; }
+        const unsigned h = __ballot_sync(0xffffffffu, w > 0.f && run + winc >= target);
+        if (h) found = v0 + __ffs(h) - 1;
+        run += __shfl_sync(0xffffffffu, winc, 31);
+      }
+      if (found < 0) found = sc.ired[sel_warp];
+      if (lane == 0) sc.pick = found;
+    }
+  } else {
+    // greedy: lowest id among the maxima
+    int best = 0x7fffffff;
+    for (int v = v_lo + lane; v < v_hi; v += 32) if (keys[v] == mx) { best = v; break; }
+    best = __reduce_min_sync(0xffffffffu, best);
+    __syncthreads();
+    if (lane == 0 && best != 0x7fffffff) atomicMin(&sc.pick, best);
+  }
+  __syncthreads();
+  if (tid == 0) {
+    out_tokens[b] = sc.pick;
+    if (append) history[(size_t)b * a.hist_ld + a.hist_len] = sc.pick;     // the entry just past the ones read above
+  }
+}
+}  // namespace
+
+extern "C" int b200_sample(b200_ctx *ctx, const void *logits, b200_dtype dt, size_t batch, size_t vocab,
+                           int32_t *history, size_t hist_len, size_t hist_ld, int append, const b200_sampler_config *cfg,
+                           uint64_t step, int32_t *out_tokens, float *out_threshold, int32_t *out_kept) {
+  B200_REQUIRE(ctx, logits && cfg && out_tokens && batch > 0, "sample: null pointer");
+  B200_REQUIRE(ctx, vocab >= 2 && vocab <= (size_t)MAX_V, "sample: vocabulary must be in [2, 32768]");
+  B200_REQUIRE(ctx, cfg->n_whitespace_ids >= 0 && cfg->n_whitespace_ids <= 8 && (history || (hist_len == 0 && !append)) && (!append || hist_len < hist_ld),
+               "sample: bad configuration");
+  B200_REQUIRE(ctx, cfg->repetition_penalty > 0.f && cfg->temperature >= 0.f, "sample: penalty must be > 0 and temperature >= 0");
+  SamplerArgs a;
+  a.V = (int)vocab; a.hist_len = (int)hist_len; a.hist_ld = (int)hist_ld; a.top_k = cfg->top_k;
+  a.n_ws = cfg->n_whitespace_ids; a.penalty = cfg->repetition_penalty; a.top_p = cfg->top_p; a.temperature = cfg->temperature;
+  a.seed = cfg->seed; a.step = step;
+  for (int i = 0; i < 8; ++i) a.ws[i] = i < a.n_ws ? cfg->whitespace_ids[i] : -1;
+  static bool attr[2] = {false, false};
+  const size_t smem = (size_t)MAX_V * sizeof(float);
+  if (dt == B200_BF16) {
+    if (!attr[1]) { B200_CUDA(ctx, cudaFuncSetAttribute(sample_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); attr[1] = true; }
+    sample_kernel<bf16><<<(unsigned)batch, THREADS, smem, ctx->stream>>>((const bf16 *)logits, history, out_tokens, out_threshold, out_kept, a, append);
+  } else {
+    if (!attr[0]) { B200_CUDA(ctx, cudaFuncSetAttribute(sample_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); attr[0] = true; }
+    sample_kernel<float><<<(unsigned)batch, THREADS, smem, ctx->stream>>>((const float *)logits, history, out_tokens, out_threshold, out_kept, a, append);
+  }
+  B200_LAUNCHED(ctx);
+  return B200_OK;
+}

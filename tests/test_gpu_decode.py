@@ -89,7 +89,7 @@ def test_sampling_draw_is_seeded_and_stays_in_the_nucleus(ctx):
 
 def test_fp32_greedy_decode_is_bit_exact_against_the_checker(ctx, orc):
     B, P, NEW = 3, 7, 6
-    shape = dict(H=64, I=96, nH=4, nKV=2, hd=16, V=97, L=2)
+    shape = dict(H=128, I=96, nH=4, nKV=2, hd=32, V=97, L=2)
     params = synth.model_params(21, oracle.Config(B=B, S=P + NEW, **shape), std=0.3)
     prompt = synth.token_ids(21, "prompt", (B, P), shape["V"])
     model = bridge.Model(ctx, bridge.Shape(B=B, S=P + NEW, **shape), "f32", with_optimizer=False)

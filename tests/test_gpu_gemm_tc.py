@@ -71,6 +71,29 @@ def test_many_tiles_exercise_the_persistent_schedule(ctx):
     assert rel(out, _ref(A, B, False, False)) < 1e-5
 
 
+@pytest.mark.parametrize("M", [1, 7, 32, 33, 64])
+@pytest.mark.parametrize("N,K", [(8, 8), (104, 72), (2048, 2048), (3072, 2048), (11264, 2048), (2048, 5632), (32000, 2048), (200, 4096)])
+def test_few_row_weight_streaming_kernel(ctx, M, N, K):
+    """Decode-shaped GEMMs (rows = sequences) go through the swapped-operand, cluster split-K kernel:
+    exact against the CPU product up to accumulation order, bit-identical between runs, and equal to the
+    general tile kernel within rounding."""
+    A, B = _ab(M, N, K, False, False, std_b=0.05)
+    exp = _ref(A, B, False, False)
+    da, db = ctx.array(A, "bf16"), ctx.array(B, "bf16")
+    out32 = ctx.gemm(da, db, M, N, K, out_dtype="f32").download()
+    assert rel(out32, exp) < 1e-5
+    np.testing.assert_array_equal(out32, ctx.gemm(da, db, M, N, K, out_dtype="f32").download())
+    out16 = ctx.gemm(da, db, M, N, K, out_dtype="bf16").download()
+    assert rel(out16, exp) < 5e-3
+    ctx.lib.b200_internal_set_gemm_skinny.argtypes = [bridge._vp, bridge._i]
+    ctx.lib.b200_internal_set_gemm_skinny(ctx.h, 0)
+    try:
+        tile = ctx.gemm(da, db, M, N, K, out_dtype="f32").download()
+    finally:
+        ctx.lib.b200_internal_set_gemm_skinny(ctx.h, 1)
+    assert rel(out32, tile) < 1e-5
+
+
 PROJ = [("qkv", 2048, 3072), ("o", 2048, 2048), ("gate_up", 2048, 11264), ("down", 5632, 2048)]
 
 
