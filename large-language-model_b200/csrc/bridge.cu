@@ -187,6 +187,8 @@ int b200_gemm_ld(b200_ctx *ctx, const void *A, const void *B, void *C, size_t M,
   B200_REQUIRE(ctx, !epi || (in_dt == B200_BF16 && out_dt == B200_BF16 && !acc && K > 0 &&
                              gemm_tc_supported(A, B, C, M, N, K, lda, ldb, ldc, out_dt)),
                "gemm: a fused epilogue needs the tensor-core path");
+  B200_REQUIRE(ctx, !(epi && (epi->swiglu_I || epi->pos_dev)) || (K > 0 && ctx->gemm_skinny && gemm_skinny_supported(M, ta, tb, acc)),
+               "gemm: the SwiGLU epilogue and device-side positions exist only in the few-row kernel");
   if (M == 0 || N == 0) return B200_OK;
   if (K == 0) {
     if (!acc) {

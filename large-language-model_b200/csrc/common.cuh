@@ -128,6 +128,8 @@ int gemm_simt_launch(b200_ctx *ctx, const void *A, const void *B, void *C, size_
 struct GemmEpilogue {
   const float *cos_t = nullptr, *sin_t = nullptr;
   int S = 0, hd = 0, cols = 0;
+  const int *pos_dev = nullptr;   // few-row kernel only: every row is at token position *pos_dev (decode; read on the device so that a captured step can be replayed)
+  int swiglu_I = 0;     // few-row kernel only: W = [gate | up] (I columns each), C[M, I] = silu(A*gate) * (A*up)
 };
 int gemm_tc_launch(b200_ctx *ctx, const void *A, const void *B, void *C, size_t M, size_t N, size_t K, int ta, int tb,
                    int acc, b200_dtype out_dt, size_t lda, size_t ldb, size_t ldc, const GemmEpilogue *epi = nullptr);

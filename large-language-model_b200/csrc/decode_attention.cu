@@ -16,35 +16,22 @@ namespace {
 
 constexpr int WARPS = 8;
 
-template <class T, int EPL> struct RowLoad;
-template <int EPL> struct RowLoad<bf16, EPL> {
-  static __device__ __forceinline__ void load(const bf16 *p, float *f) {
-    if constexpr (EPL == 1) { f[0] = to_f(p[0]); }
-    else if constexpr (EPL == 2) { const float2 v = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(p)); f[0] = v.x; f[1] = v.y; }
-    else if constexpr (EPL == 4) {
-      const uint2 u = *reinterpret_cast<const uint2 *>(p);
-      const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&u.x)), b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&u.y));
-      f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y;
-    } else {
-      const uint4 u = *reinterpret_cast<const uint4 *>(p);
-      const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+// One lane's EPL consecutive elements of a row: raw load (so that several rows can be in flight before any
+// conversion), unpack to fp32, raw store.
+template <int BYTES> struct RawVec;
+template <> struct RawVec<2> { typedef unsigned short type; };
+template <> struct RawVec<4> { typedef uint32_t type; };
+template <> struct RawVec<8> { typedef uint2 type; };
+template <> struct RawVec<16> { typedef uint4 type; };
+template <> struct RawVec<32> { struct type { uint4 a, b; }; };
+template <class T, int EPL> struct RowLoad {
+  typedef typename RawVec<sizeof(T) * EPL>::type Raw;
+  static __device__ __forceinline__ Raw ldg(const T *p) { return *reinterpret_cast<const Raw *>(p); }
+  static __device__ __forceinline__ void stg(T *p, const Raw &r) { *reinterpret_cast<Raw *>(p) = r; }
+  static __device__ __forceinline__ void unpack(const Raw &r, float *f) {
+    const T *e = reinterpret_cast<const T *>(&r);
 #pragma unroll
-      for (int i = 0; i < 4; ++i) { const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&w[i])); f[2 * i] = a.x; f[2 * i + 1] = a.y; }
-    }
-  }
-  static __device__ __forceinline__ void store(bf16 *p, const float *f) {
-#pragma unroll
-    for (int i = 0; i < EPL; ++i) p[i] = __float2bfloat16(f[i]);
-  }
-};
-template <int EPL> struct RowLoad<float, EPL> {
-  static __device__ __forceinline__ void load(const float *p, float *f) {
-#pragma unroll
-    for (int i = 0; i < EPL; ++i) f[i] = p[i];
-  }
-  static __device__ __forceinline__ void store(float *p, const float *f) {
-#pragma unroll
-    for (int i = 0; i < EPL; ++i) p[i] = f[i];
+    for (int i = 0; i < EPL; ++i) f[i] = to_f(e[i]);
   }
 };
 
@@ -53,6 +40,7 @@ struct DecodeAttnArgs {
   void *kc, *vc, *o;                 // caches [B, S_max, nKV*hd]; output [B, ldo]
   float *ws_o, *ws_ml;               // [B, nH, splits, hd] and [B, nH, splits, 2]
   int *tickets;                      // [B, nH / GQ], zero between launches
+  const int *pos_dev;                // when set: length = *pos_dev + 1 (read on the device: replayable capture)
   int nH, nKV, S_max, t_len, ldq, ldo, chunk;
   float scale;
 };
@@ -68,7 +56,7 @@ attn_decode_kernel(DecodeAttnArgs a) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int split = blockIdx.x, nsplit = gridDim.x, grp = blockIdx.y, b = blockIdx.z;
   const int G = a.nH / a.nKV, h0 = grp * GQ, kvh = h0 / G, KV = a.nKV * HD;
-  const int t_len = a.t_len;
+  const int t_len = a.pos_dev ? __ldg(a.pos_dev) + 1 : a.t_len;
   const int k0 = split * a.chunk, k1 = min(t_len, k0 + a.chunk);
   const T *q = (const T *)a.q + (size_t)b * a.ldq + (size_t)h0 * HD + lane * EPL;
   T *kc = (T *)a.kc + (size_t)b * a.S_max * KV + (size_t)kvh * HD + lane * EPL;
@@ -77,46 +65,71 @@ attn_decode_kernel(DecodeAttnArgs a) {
   float qf[GQ][EPL], acc[GQ][EPL], m[GQ], l[GQ];
 #pragma unroll
   for (int g = 0; g < GQ; ++g) {
-    RowLoad<T, EPL>::load(q + g * HD, qf[g]);
+    RowLoad<T, EPL>::unpack(RowLoad<T, EPL>::ldg(q + g * HD), qf[g]);
     m[g] = -INFINITY; l[g] = 0.f;
 #pragma unroll
     for (int e = 0; e < EPL; ++e) { qf[g][e] *= a.scale; acc[g][e] = 0.f; }
   }
-#pragma unroll 2
-  for (int j = k0 + warp; j < k1; j += WARPS) {
-    float kf[EPL], vf[EPL];
-    if (j == t_len - 1 && a.k_new != nullptr) {
-      // the token being decoded: read its K/V from the projection output and append them to the cache
-      RowLoad<T, EPL>::load((const T *)a.k_new + (size_t)b * a.ldq + (size_t)kvh * HD + lane * EPL, kf);
-      RowLoad<T, EPL>::load((const T *)a.v_new + (size_t)b * a.ldq + (size_t)kvh * HD + lane * EPL, vf);
-      if (h0 % G == 0) {
-        RowLoad<T, EPL>::store(kc + (size_t)j * KV, kf);
-        RowLoad<T, EPL>::store(vc + (size_t)j * KV, vf);
-      }
-    } else {
-      RowLoad<T, EPL>::load(kc + (size_t)j * KV, kf);
-      RowLoad<T, EPL>::load(vc + (size_t)j * KV, vf);
+  constexpr int KB = 4;                            // keys per warp step: their rows are all in flight before any maths
+  const bool fused_append = a.k_new != nullptr;
+  for (int j = k0 + warp; j < k1; j += WARPS * KB) {
+    // raw loads of all KB rows first (branch-free: rows past the run re-read the first one and are masked below)
+    typename RowLoad<T, EPL>::Raw kr[KB], vr[KB];
+    const T *k_new = (const T *)a.k_new + (size_t)b * a.ldq + (size_t)kvh * HD + lane * EPL;
+    const T *v_new = (const T *)a.v_new + (size_t)b * a.ldq + (size_t)kvh * HD + lane * EPL;
+#pragma unroll
+    for (int i = 0; i < KB; ++i) {
+      const int ji = j + i * WARPS, jc = ji < k1 ? ji : j;
+      const bool from_proj = fused_append && jc == t_len - 1;      // the token being decoded: rows of the projection output
+      kr[i] = RowLoad<T, EPL>::ldg(from_proj ? k_new : kc + (size_t)jc * KV);
+      vr[i] = RowLoad<T, EPL>::ldg(from_proj ? v_new : vc + (size_t)jc * KV);
     }
-    float s[GQ];
+    if (fused_append && h0 % G == 0) {                             // ... and are appended to the cache here
 #pragma unroll
-    for (int g = 0; g < GQ; ++g) {
-      float d = 0.f;
+      for (int i = 0; i < KB; ++i) {
+        const int ji = j + i * WARPS;
+        if (ji == t_len - 1) { RowLoad<T, EPL>::stg(kc + (size_t)ji * KV, kr[i]); RowLoad<T, EPL>::stg(vc + (size_t)ji * KV, vr[i]); }
+      }
+    }
+    float kf[KB][EPL], vf[KB][EPL];
 #pragma unroll
-      for (int e = 0; e < EPL; ++e) d += qf[g][e] * kf[e];
-      s[g] = d;
+    for (int i = 0; i < KB; ++i) { RowLoad<T, EPL>::unpack(kr[i], kf[i]); RowLoad<T, EPL>::unpack(vr[i], vf[i]); }
+    float s[KB][GQ];
+#pragma unroll
+    for (int i = 0; i < KB; ++i) {
+#pragma unroll
+      for (int g = 0; g < GQ; ++g) {
+        float d = 0.f;
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) d += qf[g][e] * kf[i][e];
+        s[i][g] = d;
+      }
     }
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) {
 #pragma unroll
-      for (int g = 0; g < GQ; ++g) s[g] += __shfl_xor_sync(0xffffffffu, s[g], off);
+      for (int i = 0; i < KB; ++i) {
+#pragma unroll
+        for (int g = 0; g < GQ; ++g) s[i][g] += __shfl_xor_sync(0xffffffffu, s[i][g], off);
+      }
     }
 #pragma unroll
     for (int g = 0; g < GQ; ++g) {
-      const float m_new = fmaxf(m[g], s[g]);
-      const float corr = __expf(m[g] - m_new), p = __expf(s[g] - m_new);
-      l[g] = l[g] * corr + p;
+      float m_new = m[g];
 #pragma unroll
-      for (int e = 0; e < EPL; ++e) acc[g][e] = acc[g][e] * corr + p * vf[e];
+      for (int i = 0; i < KB; ++i) if (j + i * WARPS < k1) m_new = fmaxf(m_new, s[i][g]);
+      const float corr = __expf(m[g] - m_new);
+      float psum = 0.f;
+#pragma unroll
+      for (int e = 0; e < EPL; ++e) acc[g][e] *= corr;
+#pragma unroll
+      for (int i = 0; i < KB; ++i) {
+        const float p = (j + i * WARPS < k1) ? __expf(s[i][g] - m_new) : 0.f;
+        psum += p;
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) acc[g][e] += p * vf[i][e];
+      }
+      l[g] = l[g] * corr + psum;
       m[g] = m_new;
     }
   }
@@ -206,10 +219,10 @@ constexpr int ATTN_DECODE_MAX_SPLITS = 16;
 size_t attn_decode_workspace_floats(size_t B, size_t nH, size_t hd) { return B * nH * ATTN_DECODE_MAX_SPLITS * (hd + 2); }
 
 // q/k_new/v_new: rows of the fused projection (stride ldq); k_new/v_new may be null when the cache already
-// holds position t_len-1.  ws: attn_decode_workspace_floats() floats; tickets: B*nH ints, zero-initialised.
+// holds position t_len-1.  pos_dev (optional): device int, length = *pos_dev + 1 instead of t_len.  ws: attn_decode_workspace_floats() floats; tickets: B*nH ints, zero-initialised.
 int attn_decode(b200_ctx *ctx, const void *q, const void *k_new, const void *v_new, void *kc, void *vc, void *o, size_t B,
                 size_t nH, size_t nKV, size_t hd, size_t S_max, size_t t_len, size_t ldq, size_t ldo, float *ws, int *tickets,
-                b200_dtype dt) {
+                b200_dtype dt, const int *pos_dev) {
   B200_REQUIRE(ctx, (hd == 32 || hd == 64 || hd == 128 || hd == 256) && t_len >= 1 && t_len <= S_max && nKV > 0 && nH % nKV == 0,
                "attn_decode: head_dim must be 32, 64, 128 or 256 and 1 <= length <= cache length");
   B200_REQUIRE(ctx, ws && tickets && B <= 65535, "attn_decode: workspace missing");
@@ -218,15 +231,17 @@ int attn_decode(b200_ctx *ctx, const void *q, const void *k_new, const void *v_n
   if (hd == 256 && gq > 4) gq = 1;
   DecodeAttnArgs a;
   a.q = q; a.k_new = k_new; a.v_new = v_new; a.kc = kc; a.vc = vc; a.o = o;
+  a.pos_dev = pos_dev;
+  if (pos_dev) t_len = S_max;                      // the grid is sized for the longest length so that it never changes
   a.ws_o = ws; a.ws_ml = ws + B * nH * ATTN_DECODE_MAX_SPLITS * hd; a.tickets = tickets;
   a.nH = (int)nH; a.nKV = (int)nKV; a.S_max = (int)S_max; a.t_len = (int)t_len; a.ldq = (int)ldq; a.ldo = (int)ldo;
   a.scale = 1.0f / sqrtf((float)hd);
-  // key runs: enough CTAs for two waves of the SMs, at least 8 keys per warp, at most 16 splits
+  // key runs: enough CTAs for about four per SM, at least 4 keys per warp, at most 16 splits
   const size_t groups = B * (nH / gq);
-  size_t want = (2 * (size_t)ctx->sm_count + groups - 1) / groups;
+  size_t want = (4 * (size_t)ctx->sm_count + groups - 1) / groups;
   if (want > (size_t)ATTN_DECODE_MAX_SPLITS) want = ATTN_DECODE_MAX_SPLITS;
   size_t chunk = (t_len + want - 1) / want;
-  if (chunk < 64) chunk = 64;
+  if (chunk < 32) chunk = 32;
   chunk = (chunk + WARPS - 1) / WARPS * WARPS;
   const size_t nsplit = (t_len + chunk - 1) / chunk;
   a.chunk = (int)chunk;

@@ -202,7 +202,8 @@ static int norm_grid(b200_ctx *ctx, size_t rows) {
 
 // warp-per-row kernels (norm_warp.cu): 1 = launched, 0 = shape does not fit, < 0 = error
 template <class T>
-int rms_fwd_warp(b200_ctx *, const void *, void *, const void *, const void *, void *, float *, float, size_t, size_t, bool);
+int rms_fwd_warp(b200_ctx *, const void *, void *, const void *, const void *, void *, float *, float, size_t, size_t, bool,
+                 const void *w2 = nullptr, void *y2 = nullptr);
 template <class T>
 int rms_bwd_warp(b200_ctx *, const void *, const void *, const void *, const void *, void *, float *, float, size_t, size_t, bool);
 
@@ -263,6 +264,22 @@ int add_norm_oop(b200_ctx *ctx, const void *x, const void *r, void *h_out, const
   if (rows == 0) return B200_OK;
   return dt == B200_BF16 ? rms_fwd_t<bf16>(ctx, x, h_out, r, w, y, nullptr, eps, rows, D, true)
                          : rms_fwd_t<float>(ctx, x, h_out, r, w, y, nullptr, eps, rows, D, true);
+}
+// Engine form of the block entry: h_out = x (+ r); y = rmsnorm(h_out) * w; y2 = rmsnorm(y) * w2, one pass when the
+// row fits the warp kernel.  r may be null (no add; h_out unused); y may be null when only y2 is wanted.
+int add_norm_norm_oop(b200_ctx *ctx, const void *x, const void *r, void *h_out, const void *w, void *y, const void *w2,
+                      void *y2, void *y_scratch, size_t rows, size_t D, float eps, b200_dtype dt) {
+  if (rows == 0) return B200_OK;
+  const bool add = r != nullptr;
+  const int rc = dt == B200_BF16 ? rms_fwd_warp<bf16>(ctx, x, h_out, r, w, y, nullptr, eps, rows, D, add, w2, y2)
+                                 : rms_fwd_warp<float>(ctx, x, h_out, r, w, y, nullptr, eps, rows, D, add, w2, y2);
+  if (rc) return rc < 0 ? rc : B200_OK;
+  void *y1 = y ? y : y_scratch;                    // two passes for shapes the warp kernel does not take
+  B200_REQUIRE(ctx, y1, "add_norm_norm: no buffer for the first norm's output");
+  const int r1 = dt == B200_BF16 ? rms_fwd_t<bf16>(ctx, x, h_out, r, w, y1, nullptr, eps, rows, D, add)
+                                 : rms_fwd_t<float>(ctx, x, h_out, r, w, y1, nullptr, eps, rows, D, add);
+  if (r1) return r1;
+  return b200_rms_norm_forward(ctx, y1, y2, w2, nullptr, eps, rows, D, dt);
 }
 extern "C" int b200_rms_norm_backward(b200_ctx *ctx, const void *g, const void *x, const void *w, void *dx,
                                       float *dw, float eps, size_t rows, size_t D, b200_dtype dt) {

@@ -9,7 +9,10 @@
 //     partial sums meet in distributed shared memory (each CTA owns 128/SPLIT features, receives the other
 //     CTAs' partials for them, adds them in a fixed order and writes its slice of C), so the result is
 //     deterministic and needs no zero-filled fp32 workspace;
-//   * the optional rotary epilogue rotates interleaved feature pairs on the fp32 sums.
+//   * the optional rotary epilogue rotates interleaved feature pairs on the fp32 sums;
+//   * the optional SwiGLU epilogue (W = [gate | up], each `swiglu_I` columns wide) puts 64 gate and the matching
+//     64 up features in one tile and writes silu(gate) * up, so the [M, 2I] intermediate never exists
+//     (metal_bridge::fused_swiglu_gemm, cpp/include/gpu_kernel/MetalBridge.hpp:44-46).
 // 128 threads: warp 0 lane 0 issues TMA, warp 1 lane 0 issues the MMAs, all four warps run the epilogue.
 #include "common.cuh"
 #include "tc_common.cuh"
@@ -56,7 +59,8 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = split > 1 ? cluster_rank() : 0;
   const int tile = blockIdx.x / split;
-  const int n0 = tile * FT;
+  const bool swiglu = epi.swiglu_I > 0;
+  const int n0 = tile * (swiglu ? FT / 2 : FT);   // first output feature of the tile
   const int num_kb = (K + BK - 1) / BK;
   const int kb_lo = (int)((long long)num_kb * rank / split), kb_hi = (int)((long long)num_kb * (rank + 1) / split);
   volatile int *abort_flag = &sh->abort_flag;
@@ -84,7 +88,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
       tc::mbar_expect_tx(&sh->full[stage], W_STAGE_BYTES + a_stage_bytes(NT));
       uint8_t *w = sW + stage * W_STAGE_BYTES;
       tc::tma_load_2d(w, &map_w, n0, kb * BK, &sh->full[stage]);
-      tc::tma_load_2d(w + CHUNK_BYTES, &map_w, n0 + 64, kb * BK, &sh->full[stage]);
+      tc::tma_load_2d(w + CHUNK_BYTES, &map_w, swiglu ? epi.swiglu_I + n0 : n0 + 64, kb * BK, &sh->full[stage]);
       tc::tma_load_2d(sA + stage * a_stage_bytes(NT), &map_a, kb * BK, 0, &sh->full[stage]);
       if (++stage == STAGES) { stage = 0; phase ^= 1; }
     }
@@ -117,8 +121,10 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   tc::tc_fence_after();
   if (ok) {
     const int f = warp * 32 + lane;             // feature of this thread = tensor-memory lane
-    const uint32_t owner = (uint32_t)(f / NL);
-    const int fl = f % NL;
+    // SwiGLU tiles: rows 0..63 are gate features, 64..127 the matching up features; an owner gets both halves
+    const int NLh = NL / 2;
+    const uint32_t owner = swiglu ? (uint32_t)((f & 63) / NLh) : (uint32_t)(f / NL);
+    const int fl = swiglu ? (f >> 6) * NLh + (f & 63) % NLh : f % NL;
     const uint32_t base = tc::smem_u32(red) + (uint32_t)(((int)rank * NT) * NL + fl) * 4u;
 #pragma unroll
     for (int c = 0; c < NT / 32; ++c) {
@@ -143,7 +149,21 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   if (split > 1) cluster_sync_all(); else __syncthreads();
 
   // ---- fixed-order sum over the K splits, optional rotary embedding, store ---------------------
-  if (!*abort_flag) {
+  if (!*abort_flag && swiglu) {
+    const int NLh = NL / 2, nf0 = n0 + (int)rank * NLh;
+    for (int i = threadIdx.x; i < NT * NLh; i += THREADS) {
+      const int m = i / NLh, p = i % NLh;
+      const int n = nf0 + p;
+      if (m >= M || n >= epi.swiglu_I) continue;
+      float g = 0.f, u = 0.f;
+      for (int s = 0; s < split; ++s) {
+        const float *r = red + ((size_t)s * NT + m) * NL;
+        g += r[p]; u += r[NLh + p];
+      }
+      const float sig = 1.0f / (1.0f + __expf(-g));
+      C[(size_t)m * ldc + n] = from_f<TO>(g * sig * u);
+    }
+  } else if (!*abort_flag) {
     const int pairs = NL / 2, nf0 = n0 + (int)rank * NL;
     for (int i = threadIdx.x; i < NT * pairs; i += THREADS) {
       const int m = i / pairs, p = i % pairs;
@@ -155,7 +175,8 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         x0 += v.x; x1 += v.y;
       }
       if (epi.cos_t != nullptr && n < epi.cols) {
-        const size_t tab = (size_t)(m % epi.S) * (epi.hd >> 1) + ((n % epi.hd) >> 1);
+        const int prow = epi.pos_dev ? __ldg(epi.pos_dev) : m % epi.S;
+        const size_t tab = (size_t)prow * (epi.hd >> 1) + ((n % epi.hd) >> 1);
         const float cv = __ldg(epi.cos_t + tab), sv = __ldg(epi.sin_t + tab);
         const float y0 = x0 * cv - x1 * sv, y1 = x0 * sv + x1 * cv;
         x0 = y0; x1 = y1;
@@ -189,7 +210,8 @@ int launch(b200_ctx *ctx, const CUtensorMap &mw, const CUtensorMap &ma, void *C,
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = split; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
-  cfg.gridDim = dim3(((N + FT - 1) / FT) * split);
+  const int ft = epi.swiglu_I > 0 ? FT / 2 : FT;
+  cfg.gridDim = dim3(((N + ft - 1) / ft) * split);
   cfg.blockDim = dim3(THREADS);
   cfg.dynamicSmemBytes = smem_bytes(NT);
   cfg.stream = ctx->stream;
@@ -209,7 +231,7 @@ int gemm_skinny_launch(b200_ctx *ctx, const void *A, const void *W, void *C, siz
   GemmEpilogue epi;
   if (epi_in) {
     epi = *epi_in;
-    B200_REQUIRE(ctx, epi.cos_t && epi.sin_t && epi.S > 0 && epi.hd % 2 == 0 && epi.cols % 2 == 0, "gemm: unsupported fused rotary epilogue");
+    B200_REQUIRE(ctx, epi.swiglu_I > 0 || (epi.cos_t && epi.sin_t && epi.S > 0 && epi.hd % 2 == 0 && epi.cols % 2 == 0), "gemm: unsupported fused epilogue");
   }
   const int nt = M <= 32 ? 32 : 64;
   CUtensorMap mw, ma;
@@ -218,7 +240,11 @@ int gemm_skinny_launch(b200_ctx *ctx, const void *A, const void *W, void *C, siz
   r = tc_make_map_2d(&ma, A, K, M, lda * 2, BK, nt);
   if (r) return b200_fail(ctx, B200_ERR_CUDA, "cuTensorMapEncodeTiled(A) failed: %d", r);
   // K split: as many CTAs per feature tile as keep the grid within two CTAs per SM, each with >= 2 K slices
-  const int tiles = (int)((N + FT - 1) / FT), num_kb = (int)((K + BK - 1) / BK);
+  if (epi.swiglu_I > 0) {
+    B200_REQUIRE(ctx, !epi.cos_t && (size_t)epi.swiglu_I * 2 == N && epi.swiglu_I % 8 == 0, "gemm: the SwiGLU epilogue needs W = [gate | up] with N = 2 I");
+    N = (size_t)epi.swiglu_I;                      // output width
+  }
+  const int tiles = (int)((N + (epi.swiglu_I > 0 ? FT / 2 : FT) - 1) / (epi.swiglu_I > 0 ? FT / 2 : FT)), num_kb = (int)((K + BK - 1) / BK);
   int split = 1;
   while (split < 8 && tiles * split * 2 <= 2 * ctx->sm_count && num_kb >= split * 4) split *= 2;
   const int m = (int)M, n = (int)N, k = (int)K;

@@ -11,6 +11,8 @@
 // reads the token-major QKV rows directly (no head split/merge passes), gradients are
 // fp32 and all-reduced per layer on a side stream while backward continues.
 #include "common.cuh"
+#include <chrono>
+#include <cstdlib>
 #include <dlfcn.h>
 #include <vector>
 
@@ -19,6 +21,8 @@ int rope_strided(b200_ctx *, void *, const float *, const float *, size_t, size_
 int swiglu_fwd_strided(b200_ctx *, const void *, const void *, void *, size_t, size_t, size_t, size_t, b200_dtype);
 int swiglu_bwd_strided(b200_ctx *, const void *, const void *, const void *, void *, void *, size_t, size_t, size_t,
                        size_t, size_t, b200_dtype);
+int add_norm_norm_oop(b200_ctx *ctx, const void *x, const void *r, void *h_out, const void *w, void *y, const void *w2,
+                      void *y2, void *y_scratch, size_t rows, size_t D, float eps, b200_dtype dt);
 int add_norm_oop(b200_ctx *, const void *, const void *, void *, const void *, void *, size_t, size_t, float,
                  b200_dtype);
 int convert2d(b200_ctx *, const void *, b200_dtype, void *, b200_dtype, size_t, size_t, size_t, size_t);
@@ -98,6 +102,8 @@ struct b200_model {
   int32_t *dec_history = nullptr, *dec_next = nullptr;
   float *dec_attn_ws = nullptr;                      // partial results of the split-key decode attention
   int *dec_attn_tickets = nullptr;                   // [cache_batch, nH], zero between launches
+  uint64_t dec_graph_nodes = 0;                      // kernel launches in one captured decode step
+  int *dec_pos = nullptr;                            // device copy of the position being decoded (captured steps read it)
   // data parallel
   nccl::comm_t comm = nullptr;
   int rank = 0, world = 1;
@@ -297,14 +303,14 @@ extern "C" int b200_model_init_synthetic(b200_model *m, uint64_t seed, float std
 // ---- one decoder layer ------------------------------------------------------------------
 // Forward, given the layer input h_in and its first norm output a1 already in acts[l].a1:
 // returns h_mid and ffn_out(tmpH) so that the caller fuses "h_out = h_mid + ffn_out" with the next norm.
-static int layer_forward_core(b200_model *m, size_t l, const void *h_in, size_t B, size_t S) {
+static int layer_forward_core(b200_model *m, size_t l, const void *h_in, size_t B, size_t S, bool a2_ready = false) {
   b200_ctx *ctx = m->ctx;
   const size_t M = B * S, H = m->H, I = m->I;
   const float eps = m->cfg.rms_norm_eps;
   b200_model::Act &a = m->acts[l];
   const b200_dtype dt = m->dt;
-  // inner unit-weight norm (cpp/src/Attention.cpp:192-194)
-  TRY(b200_rms_norm_forward(ctx, a.a1, a.a2, m->ones, nullptr, eps, M, H, dt));
+  // inner unit-weight norm (cpp/src/Attention.cpp:192-194), unless the caller produced it with the outer one
+  if (!a2_ready) TRY(b200_rms_norm_forward(ctx, a.a1, a.a2, m->ones, nullptr, eps, M, H, dt));
   // Q|K|V in one GEMM on the fused weight
   // RoPE on the q and k column blocks (cpp/src/Attention.cpp:203): in the GEMM epilogue on the tensor-core
   // path (applied to the fp32 accumulators), else as its own in-place pass
@@ -385,13 +391,16 @@ static int forward_all(b200_model *m, const int32_t *tok, size_t B, size_t S) {
   const b200_dtype dt = m->dt;
   TRY(b200_embedding_forward(ctx, (const uint32_t *)tok, m->P(m->off_emb()), m->hs[0], M, H, m->V, dt));
   if (m->L == 0) return b200_rms_norm_forward(ctx, m->hs[0], m->fh, m->P(m->off_final_norm()), nullptr, eps, M, H, dt);
-  TRY(b200_rms_norm_forward(ctx, m->hs[0], m->acts[0].a1, m->P(m->off_attn_norm(0)), nullptr, eps, M, H, dt));
+  // the layer's outer norm and the attention's inner unit-weight norm are produced in one pass
+  TRY(add_norm_norm_oop(ctx, m->hs[0], nullptr, nullptr, m->P(m->off_attn_norm(0)), m->acts[0].a1, m->ones, m->acts[0].a2, nullptr, M, H, eps, dt));
   for (size_t l = 0; l < m->L; ++l) {
-    TRY(layer_forward_core(m, l, m->hs[l], B, S));
-    // h_out = h_mid + ffn_out, fused with the norm that consumes it next
-    const void *w = (l + 1 < m->L) ? m->P(m->off_attn_norm(l + 1)) : m->P(m->off_final_norm());
-    void *y = (l + 1 < m->L) ? m->acts[l + 1].a1 : m->fh;
-    TRY(add_norm_oop(ctx, m->acts[l].h_mid, m->tmpH, m->hs[l + 1], w, y, M, H, eps, dt));
+    TRY(layer_forward_core(m, l, m->hs[l], B, S, true));
+    // h_out = h_mid + ffn_out, fused with the norm(s) that consume it next
+    if (l + 1 < m->L)
+      TRY(add_norm_norm_oop(ctx, m->acts[l].h_mid, m->tmpH, m->hs[l + 1], m->P(m->off_attn_norm(l + 1)), m->acts[l + 1].a1, m->ones,
+                            m->acts[l + 1].a2, nullptr, M, H, eps, dt));
+    else
+      TRY(add_norm_oop(ctx, m->acts[l].h_mid, m->tmpH, m->hs[l + 1], m->P(m->off_final_norm()), m->fh, M, H, eps, dt));
   }
   return B200_OK;
 }
@@ -550,7 +559,11 @@ int kv_append(b200_ctx *, const void *, void *, void *, size_t, size_t, size_t, 
 size_t attn_decode_workspace_floats(size_t B, size_t nH, size_t hd);
 int attn_decode(b200_ctx *ctx, const void *q, const void *k_new, const void *v_new, void *kc, void *vc, void *o, size_t B,
                 size_t nH, size_t nKV, size_t hd, size_t S_max, size_t t_len, size_t ldq, size_t ldo, float *ws, int *tickets,
-                b200_dtype dt);
+                b200_dtype dt, const int *pos_dev = nullptr);
+int sample_launch(b200_ctx *ctx, const void *logits, b200_dtype dt, size_t batch, size_t vocab, int32_t *history,
+                  size_t hist_len, size_t hist_ld, int append, const b200_sampler_config *cfg, uint64_t step,
+                  int32_t *out_tokens, float *out_threshold, int32_t *out_kept, const int *pos_dev);
+int advance_pos(b200_ctx *ctx, int *pos);
 int gather_rows(b200_ctx *, const void *, void *, size_t, size_t, size_t, size_t, b200_dtype);
 
 extern "C" int b200_model_decode_begin(b200_model *m, size_t batch, size_t max_total_len) {
@@ -570,6 +583,7 @@ extern "C" int b200_model_decode_begin(b200_model *m, size_t batch, size_t max_t
   TRY(dalloc(m, (void **)&m->dec_attn_ws, attn_decode_workspace_floats(batch, m->nH, m->hd) * sizeof(float)));
   TRY(dalloc(m, (void **)&m->dec_attn_tickets, batch * m->nH * sizeof(int)));
   TRY(b200_fill_zero(ctx, m->dec_attn_tickets, batch * m->nH * sizeof(int)));
+  TRY(dalloc(m, (void **)&m->dec_pos, sizeof(int)));
   m->cache_batch = batch; m->cache_len = max_total_len;
   return B200_OK;
 }
@@ -589,20 +603,23 @@ extern "C" int b200_model_prefill(b200_model *m, const int32_t *tok, size_t B, s
 
 // One decoder layer for one new token per sequence (rows = sequences); h in hs[l], result h_mid/tmpH as in the
 // training forward so that the caller fuses the residual add with the next norm.
-static int layer_decode_core(b200_model *m, size_t l, const void *h_in, size_t B, size_t pos) {
+// pos_dev (optional): device int holding `pos`; the kernels then read the position on the device, which makes the
+// enqueued step independent of the position (it can be captured once and replayed).  Needs the few-row GEMM path.
+static int layer_decode_core(b200_model *m, size_t l, const void *h_in, size_t B, size_t pos, const int *pos_dev = nullptr) {
   b200_ctx *ctx = m->ctx;
   const size_t H = m->H, I = m->I;
   const float eps = m->cfg.rms_norm_eps;
   b200_model::Act &a = m->acts[l];
   const b200_dtype dt = m->dt;
   const size_t es = dtype_size(dt), half = m->hd / 2;
-  TRY(b200_rms_norm_forward(ctx, a.a1, a.a2, m->ones, nullptr, eps, B, H, dt));
   const float *cos_p = m->cos_t + pos * half, *sin_p = m->sin_t + pos * half;    // every row is at position `pos`
   const bool rope_in_gemm = dt == B200_BF16 && m->hd % 32 == 0 && (pos * half * 4) % 16 == 0 &&
                             gemm_tc_supported(a.a2, m->P(m->off_qkv(l)), a.qkv, B, m->QKV, H, H, m->QKV, m->QKV, dt);
+  B200_REQUIRE(ctx, !pos_dev || rope_in_gemm, "decode: device-side positions need the bf16 few-row GEMM path");
   if (rope_in_gemm) {
     GemmEpilogue epi;
     epi.cos_t = cos_p; epi.sin_t = sin_p; epi.S = 1; epi.hd = (int)m->hd; epi.cols = (int)(m->Q + m->KV);
+    if (pos_dev) { epi.cos_t = m->cos_t; epi.sin_t = m->sin_t; epi.pos_dev = pos_dev; }
     TRY(b200_gemm_ld(ctx, a.a2, m->P(m->off_qkv(l)), a.qkv, B, m->QKV, H, 0, 0, 0, dt, dt, H, m->QKV, m->QKV, &epi));
   } else {
     TRY(b200_gemm_ld(ctx, a.a2, m->P(m->off_qkv(l)), a.qkv, B, m->QKV, H, 0, 0, 0, dt, dt, H, m->QKV, m->QKV));
@@ -610,17 +627,23 @@ static int layer_decode_core(b200_model *m, size_t l, const void *h_in, size_t B
   }
   // attention over the cache; the new token's K/V rows go from the projection output into the cache in the same kernel
   TRY(attn_decode(ctx, a.qkv, (const char *)a.qkv + m->Q * es, (const char *)a.qkv + (m->Q + m->KV) * es, m->k_cache[l], m->v_cache[l],
-                  a.o, B, m->nH, m->nKV, m->hd, m->cache_len, pos + 1, m->QKV, m->Q, m->dec_attn_ws, m->dec_attn_tickets, dt));
+                  a.o, B, m->nH, m->nKV, m->hd, m->cache_len, pos + 1, m->QKV, m->Q, m->dec_attn_ws, m->dec_attn_tickets, dt, pos_dev));
   TRY(b200_gemm_ld(ctx, a.o, m->P(m->off_o(l)), m->tmpH, B, H, m->Q, 0, 0, 0, dt, dt, m->Q, H, H));
   TRY(add_norm_oop(ctx, h_in, m->tmpH, a.h_mid, m->P(m->off_ffn_norm(l)), a.ffn_in, B, H, eps, dt));
-  TRY(b200_gemm_ld(ctx, a.ffn_in, m->P(m->off_gate_up(l)), a.gate_up, B, 2 * I, H, 0, 0, 0, dt, dt, H, 2 * I, 2 * I));
-  TRY(swiglu_fwd_strided(ctx, a.gate_up, (char *)a.gate_up + I * es, a.act, B, I, 2 * I, I, dt));
+  if (dt == B200_BF16 && ctx->gemm_skinny && gemm_skinny_supported(B, 0, 0, 0) && I % 8 == 0 &&
+      gemm_tc_supported(a.ffn_in, m->P(m->off_gate_up(l)), a.act, B, 2 * I, H, H, 2 * I, I, dt)) {
+    GemmEpilogue epi;                               // silu(gate) * up in the GEMM epilogue: no [B, 2I] intermediate
+    epi.swiglu_I = (int)I;
+    TRY(b200_gemm_ld(ctx, a.ffn_in, m->P(m->off_gate_up(l)), a.act, B, 2 * I, H, 0, 0, 0, dt, dt, H, 2 * I, I, &epi));
+  } else {
+    TRY(b200_gemm_ld(ctx, a.ffn_in, m->P(m->off_gate_up(l)), a.gate_up, B, 2 * I, H, 0, 0, 0, dt, dt, H, 2 * I, 2 * I));
+    TRY(swiglu_fwd_strided(ctx, a.gate_up, (char *)a.gate_up + I * es, a.act, B, I, 2 * I, I, dt));
+  }
   TRY(b200_gemm_ld(ctx, a.act, m->P(m->off_down(l)), m->tmpH, B, H, I, 0, 0, 0, dt, dt, I, H, H));
   return B200_OK;
 }
 
-extern "C" int b200_model_decode_step(b200_model *m, const int32_t *tok, size_t B, size_t pos, void *logits) {
-  if (!m) return B200_ERR_INVALID;
+static int decode_step_core(b200_model *m, const int32_t *tok, size_t B, size_t pos, void *logits, const int *pos_dev) {
   b200_ctx *ctx = m->ctx;
   B200_REQUIRE(ctx, tok && logits && B > 0 && B <= m->cache_batch && pos < m->cache_len, "decode_step: bad arguments");
   const size_t H = m->H;
@@ -630,15 +653,22 @@ extern "C" int b200_model_decode_step(b200_model *m, const int32_t *tok, size_t 
   if (m->L == 0) {
     TRY(b200_rms_norm_forward(ctx, m->hs[0], m->fh, m->P(m->off_final_norm()), nullptr, eps, B, H, dt));
   } else {
-    TRY(b200_rms_norm_forward(ctx, m->hs[0], m->acts[0].a1, m->P(m->off_attn_norm(0)), nullptr, eps, B, H, dt));
+    TRY(add_norm_norm_oop(ctx, m->hs[0], nullptr, nullptr, m->P(m->off_attn_norm(0)), nullptr, m->ones, m->acts[0].a2, m->acts[0].a1, B, H, eps, dt));
     for (size_t l = 0; l < m->L; ++l) {
-      TRY(layer_decode_core(m, l, m->hs[l], B, pos));
-      const void *w = (l + 1 < m->L) ? m->P(m->off_attn_norm(l + 1)) : m->P(m->off_final_norm());
-      void *y = (l + 1 < m->L) ? m->acts[l + 1].a1 : m->fh;
-      TRY(add_norm_oop(ctx, m->acts[l].h_mid, m->tmpH, m->hs[l + 1], w, y, B, H, eps, dt));
+      TRY(layer_decode_core(m, l, m->hs[l], B, pos, pos_dev));
+      if (l + 1 < m->L)
+        TRY(add_norm_norm_oop(ctx, m->acts[l].h_mid, m->tmpH, m->hs[l + 1], m->P(m->off_attn_norm(l + 1)), nullptr, m->ones,
+                              m->acts[l + 1].a2, m->acts[l + 1].a1, B, H, eps, dt));
+      else
+        TRY(add_norm_oop(ctx, m->acts[l].h_mid, m->tmpH, m->hs[l + 1], m->P(m->off_final_norm()), m->fh, B, H, eps, dt));
     }
   }
   return b200_gemm_ld(ctx, m->fh, m->P(m->off_out()), logits, B, m->V, H, 0, 0, 0, dt, dt, H, m->V, m->V);
+}
+
+extern "C" int b200_model_decode_step(b200_model *m, const int32_t *tok, size_t B, size_t pos, void *logits) {
+  if (!m) return B200_ERR_INVALID;
+  return decode_step_core(m, tok, B, pos, logits, nullptr);
 }
 
 extern "C" int b200_model_generate(b200_model *m, const int32_t *host_prompt, size_t B, size_t P, size_t new_tokens,
@@ -657,13 +687,59 @@ extern "C" int b200_model_generate(b200_model *m, const int32_t *host_prompt, si
   cudaEventCreate(&e0); cudaEventCreate(&e1); cudaEventCreate(&e2);
   cudaEventRecord(e0, ctx->stream);
   if (!rc) rc = b200_model_prefill(m, d_prompt, B, P, m->dec_logits);
-  if (!rc) rc = b200_sample(ctx, m->dec_logits, m->dt, B, m->V, m->dec_history, P, ld, 1, cfg, 0, m->dec_next, nullptr, nullptr);
+  if (!rc) rc = b200_sample(ctx, m->dec_logits, m->dt, B, m->V, m->dec_history, P, ld, 1, cfg, P, m->dec_next, nullptr, nullptr);   // draw counter = history length
   cudaEventRecord(e1, ctx->stream);
-  for (size_t t = 1; t < new_tokens && !rc; ++t) {
-    rc = b200_model_decode_step(m, m->dec_next, B, P + t - 1, m->dec_logits);
-    if (!rc) rc = b200_sample(ctx, m->dec_logits, m->dt, B, m->V, m->dec_history, P + t, ld, 1, cfg, t, m->dec_next, nullptr, nullptr);
+  const auto host_t0 = std::chrono::steady_clock::now();
+  // The per-token step is a chain of ~230 short kernels: enqueueing it costs more host time than it takes to run.
+  // So the position lives in device memory, one step is captured into a CUDA graph and replayed for the rest.
+  const char *genv = getenv("B200_DECODE_GRAPH");
+  bool use_graph = !(genv && genv[0] == '0') && new_tokens > 3 && m->dt == B200_BF16 && ctx->gemm_skinny &&
+                   gemm_skinny_supported(B, 0, 0, 0) && m->hd % 32 == 0 && m->H % 8 == 0 && m->QKV % 8 == 0 && m->L > 0;
+  cudaGraphExec_t exec = nullptr;
+  bool capture_tried = false;
+  if (use_graph && !rc) {
+    const int p0 = (int)P;
+    cudaError_t ce = cudaMemcpyAsync(m->dec_pos, &p0, sizeof(int), cudaMemcpyHostToDevice, ctx->stream);
+    if (ce != cudaSuccess) rc = b200_fail(ctx, B200_ERR_CUDA, "generate: position upload failed: %s", cudaGetErrorString(ce));
   }
+  const int *pos_dev = use_graph ? m->dec_pos : nullptr;
+  for (size_t t = 1; t < new_tokens && !rc; ++t) {
+    if (exec) {
+      cudaError_t ce = cudaGraphLaunch(exec, ctx->stream);
+      if (ce != cudaSuccess) rc = b200_fail(ctx, B200_ERR_CUDA, "generate: graph launch failed: %s", cudaGetErrorString(ce));
+      else ctx->launches += m->dec_graph_nodes;
+      continue;
+    }
+    // t == 1 runs eagerly (one-time attribute calls stay outside the capture); t == 2 is captured
+    const bool capturing = use_graph && t == 2 && !capture_tried;
+    const uint64_t launches_before = ctx->launches;
+    if (capturing) {
+      capture_tried = true;
+      if (cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal) != cudaSuccess) { cudaGetLastError(); --t; continue; }
+    }
+    rc = decode_step_core(m, m->dec_next, B, P + t - 1, m->dec_logits, pos_dev);
+    if (!rc) rc = sample_launch(ctx, m->dec_logits, m->dt, B, m->V, m->dec_history, P + t, ld, 1, cfg, P + t, m->dec_next, nullptr, nullptr, pos_dev);
+    if (!rc && pos_dev) rc = advance_pos(ctx, m->dec_pos);
+    if (capturing) {
+      cudaGraph_t graph = nullptr;
+      const cudaError_t ce = cudaStreamEndCapture(ctx->stream, &graph);
+      if (!rc && ce == cudaSuccess && graph && cudaGraphInstantiate(&exec, graph, 0) == cudaSuccess) {
+        m->dec_graph_nodes = ctx->launches - launches_before;
+        ctx->launches = launches_before;
+      } else {
+        exec = nullptr;
+        cudaGetLastError();
+        ctx->launches = launches_before;
+      }
+      if (graph) cudaGraphDestroy(graph);
+      if (!rc) --t;                                 // nothing ran while capturing: do step t again (replay, or eagerly)
+    }
+  }
+  if (exec) cudaGraphExecDestroy(exec);
   cudaEventRecord(e2, ctx->stream);
+  if (getenv("B200_DEBUG_TIMING"))
+    fprintf(stderr, "[b200] decode loop enqueued in %.3f ms of host time\n",
+            std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - host_t0).count());
   if (!rc) {
     cudaError_t ce = cudaMemcpy2DAsync(host_out, new_tokens * 4, m->dec_history + P, ld * 4, new_tokens * 4, B, cudaMemcpyDeviceToHost, ctx->stream);
     if (ce != cudaSuccess) rc = b200_fail(ctx, B200_ERR_CUDA, "copy of generated ids failed: %s", cudaGetErrorString(ce));

@@ -12,7 +12,8 @@ constexpr int WARPS_PER_CTA = 8;
 template <class T, int VPL, bool ADD>
 __global__ void __launch_bounds__(WARPS_PER_CTA * 32)
 rms_fwd_warp_kernel(const T *x, T *h_out, const T *__restrict__ r, const T *__restrict__ w, T *__restrict__ y,
-                    float *__restrict__ rstd_out, float eps, size_t rows, int D) {
+                    float *__restrict__ rstd_out, float eps, size_t rows, int D, const T *__restrict__ w2,
+                    T *__restrict__ y2) {
   constexpr int N = Vec16<T>::N;
   const int lane = threadIdx.x & 31;
   const size_t warp_global = (size_t)blockIdx.x * WARPS_PER_CTA + (threadIdx.x >> 5);
@@ -44,13 +45,34 @@ rms_fwd_warp_kernel(const T *x, T *h_out, const T *__restrict__ r, const T *__re
     ss = warp_sum(ss);
     const float rstd = rsqrtf(ss / (float)D + eps);
     if (rstd_out && lane == 0) rstd_out[row] = rstd;
+    float ss2 = 0.f;
 #pragma unroll
     for (int i = 0; i < VPL; ++i) {
       Vec16<T> wv; float wf[N], o[N];
       wv.load(w + (lane + 32 * i) * N); wv.unpack(wf);
 #pragma unroll
       for (int j = 0; j < N; ++j) o[j] = v[i][j] * rstd * wf[j];
-      Vec16<T> ov; ov.pack(o); ov.store(y + base + (lane + 32 * i) * N);
+      Vec16<T> ov; ov.pack(o);
+      if (y) ov.store(y + base + (lane + 32 * i) * N);
+      if (y2) {                                   // second norm reads the first one's output as stored
+        ov.unpack(v[i]);
+#pragma unroll
+        for (int j = 0; j < N; ++j) ss2 += v[i][j] * v[i][j];
+      }
+    }
+    if (y2) {
+      // y2 = rmsnorm(y) * w2 in the same pass (the reference's attention re-normalises its already normalised
+      // input, cpp/src/Attention.cpp:171-190)
+      ss2 = warp_sum(ss2);
+      const float rstd2 = rsqrtf(ss2 / (float)D + eps);
+#pragma unroll
+      for (int i = 0; i < VPL; ++i) {
+        Vec16<T> wv; float wf[N], o[N];
+        wv.load(w2 + (lane + 32 * i) * N); wv.unpack(wf);
+#pragma unroll
+        for (int j = 0; j < N; ++j) o[j] = v[i][j] * rstd2 * wf[j];
+        Vec16<T> ov; ov.pack(o); ov.store(y2 + base + (lane + 32 * i) * N);
+      }
     }
   }
 }
@@ -138,12 +160,12 @@ bool aligned16(std::initializer_list<const void *> ps) {
 // Returns 1 when the warp-per-row kernel was launched, 0 when the shape does not fit it, <0 on error.
 template <class T>
 int rms_fwd_warp(b200_ctx *ctx, const void *x, void *h, const void *r, const void *w, void *y, float *rstd, float eps,
-                 size_t rows, size_t D, bool add) {
+                 size_t rows, size_t D, bool add, const void *w2, void *y2) {
   constexpr int N = Vec16<T>::N;
-  if (D % (32 * N) || !aligned16({x, h, r, w, y})) return 0;
+  if (D % (32 * N) || !aligned16({x, h, r, w, y, w2, y2})) return 0;
   const int vpl = (int)(D / (32 * N));
   const int grid = warp_grid(ctx, rows);
-#define FW(V, A) rms_fwd_warp_kernel<T, V, A><<<grid, WARPS_PER_CTA * 32, 0, ctx->stream>>>((const T *)x, (T *)h, (const T *)r, (const T *)w, (T *)y, rstd, eps, rows, (int)D)
+#define FW(V, A) rms_fwd_warp_kernel<T, V, A><<<grid, WARPS_PER_CTA * 32, 0, ctx->stream>>>((const T *)x, (T *)h, (const T *)r, (const T *)w, (T *)y, rstd, eps, rows, (int)D, (const T *)w2, (T *)y2)
   switch (vpl) {
     case 1: if (add) FW(1, true); else FW(1, false); break;
     case 2: if (add) FW(2, true); else FW(2, false); break;
@@ -178,7 +200,7 @@ int rms_bwd_warp(b200_ctx *ctx, const void *g, const void *x, const void *w, con
   if (cudaGetLastError() != cudaSuccess) return b200_fail(ctx, B200_ERR_CUDA, "rms_norm backward launch failed");
   return 1;
 }
-template int rms_fwd_warp<float>(b200_ctx *, const void *, void *, const void *, const void *, void *, float *, float, size_t, size_t, bool);
-template int rms_fwd_warp<bf16>(b200_ctx *, const void *, void *, const void *, const void *, void *, float *, float, size_t, size_t, bool);
+template int rms_fwd_warp<float>(b200_ctx *, const void *, void *, const void *, const void *, void *, float *, float, size_t, size_t, bool, const void *, void *);
+template int rms_fwd_warp<bf16>(b200_ctx *, const void *, void *, const void *, const void *, void *, float *, float, size_t, size_t, bool, const void *, void *);
 template int rms_bwd_warp<float>(b200_ctx *, const void *, const void *, const void *, const void *, void *, float *, float, size_t, size_t, bool);
 template int rms_bwd_warp<bf16>(b200_ctx *, const void *, const void *, const void *, const void *, void *, float *, float, size_t, size_t, bool);

@@ -28,6 +28,7 @@ struct SamplerArgs {
   int V, hist_len, hist_ld, top_k, n_ws;
   float penalty, top_p, temperature;
   uint64_t seed, step;
+  const int *pos_dev;      // when set: hist_len = step = *pos_dev + 1 (read on the device: replayable capture)
   int ws[8];
 };
 
@@ -134,6 +135,7 @@ template <class T>
 __global__ void __launch_bounds__(THREADS)
 sample_kernel(const T *__restrict__ logits, int32_t *history, int32_t *__restrict__ out_tokens,
               float *__restrict__ out_threshold, int32_t *__restrict__ out_kept, SamplerArgs a, int append) {
+  if (a.pos_dev) { a.hist_len = __ldg(a.pos_dev) + 1; a.step = (uint64_t)a.hist_len; }
   extern __shared__ float keys[];                  // V penalised logits
   __shared__ Scratch sc;
   __shared__ int recent[WINDOW];
@@ -240,11 +242,20 @@ sample_kernel(const T *__restrict__ logits, int32_t *history, int32_t *__restric
     if (append) history[(size_t)b * a.hist_ld + a.hist_len] = sc.pick;     // the entry just past the ones read above
   }
 }
+
+__global__ void advance_pos_kernel(int *pos) { *pos += 1; }
 }  // namespace
 
-extern "C" int b200_sample(b200_ctx *ctx, const void *logits, b200_dtype dt, size_t batch, size_t vocab,
-                           int32_t *history, size_t hist_len, size_t hist_ld, int append, const b200_sampler_config *cfg,
-                           uint64_t step, int32_t *out_tokens, float *out_threshold, int32_t *out_kept) {
+int advance_pos(b200_ctx *ctx, int *pos) {
+  advance_pos_kernel<<<1, 1, 0, ctx->stream>>>(pos);
+  B200_LAUNCHED(ctx);
+  return B200_OK;
+}
+
+// pos_dev (optional): device int; the kernel then takes hist_len = step = *pos_dev + 1.
+int sample_launch(b200_ctx *ctx, const void *logits, b200_dtype dt, size_t batch, size_t vocab, int32_t *history,
+                  size_t hist_len, size_t hist_ld, int append, const b200_sampler_config *cfg, uint64_t step,
+                  int32_t *out_tokens, float *out_threshold, int32_t *out_kept, const int *pos_dev) {
   B200_REQUIRE(ctx, logits && cfg && out_tokens && batch > 0, "sample: null pointer");
   B200_REQUIRE(ctx, vocab >= 2 && vocab <= (size_t)MAX_V, "sample: vocabulary must be in [2, 32768]");
   B200_REQUIRE(ctx, cfg->n_whitespace_ids >= 0 && cfg->n_whitespace_ids <= 8 && (history || (hist_len == 0 && !append)) && (!append || hist_len < hist_ld),
@@ -253,7 +264,7 @@ extern "C" int b200_sample(b200_ctx *ctx, const void *logits, b200_dtype dt, siz
   SamplerArgs a;
   a.V = (int)vocab; a.hist_len = (int)hist_len; a.hist_ld = (int)hist_ld; a.top_k = cfg->top_k;
   a.n_ws = cfg->n_whitespace_ids; a.penalty = cfg->repetition_penalty; a.top_p = cfg->top_p; a.temperature = cfg->temperature;
-  a.seed = cfg->seed; a.step = step;
+  a.seed = cfg->seed; a.step = step; a.pos_dev = pos_dev;
   for (int i = 0; i < 8; ++i) a.ws[i] = i < a.n_ws ? cfg->whitespace_ids[i] : -1;
   static bool attr[2] = {false, false};
   const size_t smem = (size_t)MAX_V * sizeof(float);
@@ -266,4 +277,11 @@ extern "C" int b200_sample(b200_ctx *ctx, const void *logits, b200_dtype dt, siz
   }
   B200_LAUNCHED(ctx);
   return B200_OK;
+}
+
+extern "C" int b200_sample(b200_ctx *ctx, const void *logits, b200_dtype dt, size_t batch, size_t vocab,
+                           int32_t *history, size_t hist_len, size_t hist_ld, int append, const b200_sampler_config *cfg,
+                           uint64_t step, int32_t *out_tokens, float *out_threshold, int32_t *out_kept) {
+  return sample_launch(ctx, logits, dt, batch, vocab, history, hist_len, hist_ld, append, cfg, step, out_tokens, out_threshold,
+                       out_kept, nullptr);
 }

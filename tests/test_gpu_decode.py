@@ -126,3 +126,26 @@ def test_bf16_cache_decode_matches_full_context_forward(ctx, hd, nH, nKV):
         logits = model.decode_step(ctx.array(nxt, "i32"), B, P + t).download()
         ctxt = np.concatenate([ctxt, nxt[:, None]], 1)
     model.close()
+
+
+@pytest.mark.parametrize("temperature", [0.0, 0.8])
+def test_captured_decode_step_equals_the_eagerly_enqueued_one(ctx, temperature, monkeypatch):
+    """generate() replays one captured step (position read on the device); the ids must equal those of the
+    step-by-step enqueued loop, for greedy and for seeded sampling."""
+    B, P, NEW = 5, 37, 14
+    shape = dict(H=256, I=512, nH=4, nKV=2, hd=64, V=2048, L=3)
+    model = bridge.Model(ctx, bridge.Shape(B=B, S=P + NEW, **shape), "bf16", with_optimizer=False)
+    model.init_synthetic(9, 0.08)
+    prompt = synth.token_ids(9, "prompt", (B, P), shape["V"])
+    cfg = bridge.SamplerConfig.make(temperature=temperature, top_p=0.9, repetition_penalty=1.1, top_k=40, seed=77, whitespace_ids=(3, 4))
+    n0 = ctx.launch_count()
+    graph_ids, _, _ = model.generate(prompt, NEW, cfg)
+    n_graph = ctx.launch_count() - n0
+    monkeypatch.setenv("B200_DECODE_GRAPH", "0")
+    n0 = ctx.launch_count()
+    eager_ids, _, _ = model.generate(prompt, NEW, cfg)
+    n_eager = ctx.launch_count() - n0
+    np.testing.assert_array_equal(graph_ids, eager_ids)
+    assert graph_ids.min() >= 0 and graph_ids.max() < shape["V"]
+    assert n_graph == n_eager + (NEW - 1)          # same kernels, plus the position increment of each captured-mode step
+    model.close()
