@@ -198,9 +198,15 @@ int b200_model_create(b200_ctx *ctx, const b200_model_config *cfg, b200_dtype co
                       int with_optimizer, b200_model **out);
 int b200_model_destroy(b200_model *m);
 size_t b200_model_param_count(const b200_model *m);
+int b200_model_get_config(const b200_model *m, b200_model_config *out);
 int b200_model_load_params(b200_model *m, const float *host_flat);
 int b200_model_read_params(b200_model *m, float *host_flat);
 int b200_model_read_grads(b200_model *m, float *host_flat);
+/* AdamW first/second moments in the parameter layout above (norm slots: zero on read, ignored on load) and the
+ * optimizer step counter; what Checkpoint::save / ::load put in and take from the ".opt.safetensors" file
+ * (cpp/src/Checkpoint.cpp:836-1040, 1066-1110). */
+int b200_model_read_opt_state(b200_model *m, float *host_m_flat, float *host_v_flat, uint64_t *step);
+int b200_model_load_opt_state(b200_model *m, const float *host_m_flat, const float *host_v_flat, uint64_t step);
 int b200_model_init_synthetic(b200_model *m, uint64_t seed, float std);
 /* Transformer::forward (cpp/src/Transformer.cpp:90-197): logits_out (optional, device, compute dtype, [B*S,V]). */
 int b200_model_forward(b200_model *m, const int32_t *dev_tokens, size_t batch, size_t seq_len, void *logits_out);
@@ -259,6 +265,32 @@ int b200_model_decode_step(b200_model *m, const int32_t *dev_tokens, size_t batc
  * decode_ms (optional) receives the device time of the new_tokens-1 decode steps (prefill excluded). */
 int b200_model_generate(b200_model *m, const int32_t *host_prompt, size_t batch, size_t prompt_len, size_t new_tokens,
                         const b200_sampler_config *cfg, int32_t *host_out, float *prefill_ms, float *decode_ms);
+
+/* ---- training driver files: checkpoints, learning-rate schedule, metrics (host code, no GPU needed for the
+ * *_flat and metrics forms).
+ * Checkpoint::save / ::load (cpp/src/Checkpoint.cpp:721-1040, 1045-1116): "<path>" holds the weights and
+ * "<path with .safetensors -> .opt.safetensors>" the AdamW moments and a U64 "step", both safetensors files in
+ * the reference's Python/MLX tensor naming (projections transposed to [out,in], wqkv and w12 fused, fp32).
+ * Flat arrays use the parameter order of b200_model_load_params; loading also accepts BF16 / F16 payloads. */
+size_t b200_checkpoint_param_count(const b200_model_config *cfg);
+int b200_checkpoint_write_flat(const b200_model_config *cfg, const float *params, const float *adam_m /* optional */,
+                               const float *adam_v /* optional */, uint64_t step, const char *path);
+/* adam_m / adam_v optional; a missing optimizer file leaves them zero, *step 0 and *has_opt_state 0 (the
+ * reference restarts the moments in that case, cpp/src/Checkpoint.cpp:1076-1112). */
+int b200_checkpoint_read_flat(const b200_model_config *cfg, const char *path, float *params, float *adam_m, float *adam_v,
+                              uint64_t *step, int *has_opt_state);
+/* Device-resident engine <-> files.  step_override == UINT64_MAX stores the engine's own optimizer step count. */
+int b200_checkpoint_save(b200_model *m, const char *path, uint64_t step_override, int with_optimizer);
+int b200_checkpoint_load(b200_model *m, const char *path, int with_optimizer, uint64_t *step);
+const char *b200_checkpoint_last_error(void);
+/* Trainer::get_scheduled_lr (cpp/src/Trainer.cpp:40-51): linear warm-up then cosine decay to lr_min. */
+float b200_scheduled_lr(size_t step, size_t warmup_steps, size_t max_steps, float lr_max, float lr_min);
+/* metrics.csv of Trainer::train (cpp/src/Trainer.cpp:136-170, 247-255, 347-365): begin writes the header, or on
+ * resume keeps the rows below start_step; append adds one row in the reference's column order and formatting. */
+int b200_metrics_begin(const char *path, size_t start_step);
+int b200_metrics_append(const char *path, size_t step, double train_loss, double tokens_per_sec, double learning_rate,
+                        double vram_usage_gb, double mfu_pct, double step_time_ms, uint64_t gpu_calls,
+                        double gpu_time_ms, uint64_t cpu_calls, double cpu_time_ms, double gpu_active_pct);
 
 /* ---- data parallel (no counterpart in the reference, which is single-device):
  * replicas all-reduce (average) fp32 gradient buckets with NCCL on a side

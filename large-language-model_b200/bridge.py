@@ -102,6 +102,19 @@ _SIGS = {
     "b200_model_load_params": (_i, [_vp, _vp]),
     "b200_model_read_params": (_i, [_vp, _vp]),
     "b200_model_read_grads": (_i, [_vp, _vp]),
+    "b200_model_get_config": (_i, [_vp, _vp]),
+    "b200_checkpoint_param_count": (_sz, [_vp]),
+    "b200_checkpoint_write_flat": (_i, [_vp, _vp, _vp, _vp, C.c_uint64, C.c_char_p]),
+    "b200_checkpoint_read_flat": (_i, [_vp, C.c_char_p, _vp, _vp, _vp, _vp, _vp]),
+    "b200_checkpoint_save": (_i, [_vp, C.c_char_p, C.c_uint64, _i]),
+    "b200_checkpoint_load": (_i, [_vp, C.c_char_p, _i, _vp]),
+    "b200_checkpoint_last_error": (C.c_char_p, []),
+    "b200_scheduled_lr": (_f, [_sz, _sz, _sz, _f, _f]),
+    "b200_metrics_begin": (_i, [C.c_char_p, _sz]),
+    "b200_metrics_append": (_i, [C.c_char_p, _sz, C.c_double, C.c_double, C.c_double, C.c_double, C.c_double, C.c_double,
+                                C.c_uint64, C.c_double, C.c_uint64, C.c_double, C.c_double]),
+    "b200_model_read_opt_state": (_i, [_vp, _vp, _vp, _vp]),
+    "b200_model_load_opt_state": (_i, [_vp, _vp, _vp, C.c_uint64]),
     "b200_model_init_synthetic": (_i, [_vp, C.c_uint64, _f]),
     "b200_model_forward": (_i, [_vp, _vp, _sz, _sz, _vp]),
     "b200_model_loss_and_grads": (_i, [_vp, _vp, _vp, _sz, _sz, _vp]),
@@ -461,6 +474,18 @@ class Model:
         out = np.empty(self.n_params, np.float32)
         self.ctx._check(self.ctx.lib.b200_model_read_grads(self.h, _np_ptr(out)))
         return out
+
+    def read_opt_state(self):
+        """(m, v, step): AdamW moments in the parameter order, and the optimizer step counter."""
+        mm, vv = np.empty(self.n_params, np.float32), np.empty(self.n_params, np.float32)
+        step = C.c_uint64(0)
+        self.ctx._check(self.ctx.lib.b200_model_read_opt_state(self.h, _np_ptr(mm), _np_ptr(vv), C.byref(step)))
+        return mm, vv, int(step.value)
+
+    def load_opt_state(self, m: np.ndarray, v: np.ndarray, step: int):
+        m, v = np.ascontiguousarray(m, np.float32), np.ascontiguousarray(v, np.float32)
+        assert m.size == self.n_params and v.size == self.n_params
+        self.ctx._check(self.ctx.lib.b200_model_load_opt_state(self.h, _np_ptr(m), _np_ptr(v), int(step)))
 
     def forward(self, tokens_dev: DeviceArray, B: int, S: int) -> DeviceArray:
         logits = self.ctx.empty((B * S, self.cfg.V), self.dtype)

@@ -209,6 +209,11 @@ extern "C" int b200_model_destroy(b200_model *m) {
 }
 
 extern "C" size_t b200_model_param_count(const b200_model *m) { return m ? m->n_total : 0; }
+extern "C" int b200_model_get_config(const b200_model *m, b200_model_config *out) {
+  if (!m || !out) return B200_ERR_INVALID;
+  *out = m->cfg;
+  return B200_OK;
+}
 
 // ---- import / export in the reference's per-tensor order -----------------------------------
 namespace {
@@ -283,6 +288,60 @@ extern "C" int b200_model_read_params(b200_model *m, float *host) {
 extern "C" int b200_model_read_grads(b200_model *m, float *host) {
   if (!m || !host) return B200_ERR_INVALID;
   return export_flat(m, m->grads, B200_F32, host);
+}
+
+// AdamW moments in the same per-tensor order as the parameters (norm weights are not trained by the reference,
+// cpp/src/Trainer.cpp:188-198: their slots read as zero and are ignored on load) plus the step counter, for
+// checkpoints (cpp/src/Checkpoint.cpp:836-1040).
+extern "C" int b200_model_read_opt_state(b200_model *m, float *host_m, float *host_v, uint64_t *step) {
+  if (!m) return B200_ERR_INVALID;
+  b200_ctx *ctx = m->ctx;
+  B200_REQUIRE(ctx, m->with_opt && host_m && host_v && step, "read_opt_state: model has no optimizer state or null pointer");
+  auto map = layout_map(m);
+  size_t biggest = 0;
+  for (auto &p : map) biggest = p.rows * p.cols > biggest ? p.rows * p.cols : biggest;
+  float *stage = nullptr;
+  TRY(b200_malloc(ctx, biggest * 4, (void **)&stage));
+  int rc = B200_OK;
+  for (int which = 0; which < 2 && !rc; ++which) {
+    const float *src = which ? m->adam_v : m->adam_m;
+    float *host = which ? host_v : host_m;
+    for (auto &p : map) {
+      if (p.eng_off >= m->n_train) { memset(host + p.ref_off, 0, p.rows * p.cols * 4); continue; }
+      rc = convert2d(ctx, src + p.eng_off, B200_F32, stage, B200_F32, p.rows, p.cols, p.eng_ld, p.cols);
+      if (!rc) rc = b200_memcpy_d2h(ctx, host + p.ref_off, stage, p.rows * p.cols * 4);
+      if (!rc) rc = b200_sync(ctx);
+      if (rc) break;
+    }
+  }
+  b200_free(ctx, stage);
+  *step = m->step_count;
+  return rc;
+}
+extern "C" int b200_model_load_opt_state(b200_model *m, const float *host_m, const float *host_v, uint64_t step) {
+  if (!m) return B200_ERR_INVALID;
+  b200_ctx *ctx = m->ctx;
+  B200_REQUIRE(ctx, m->with_opt && host_m && host_v, "load_opt_state: model has no optimizer state or null pointer");
+  auto map = layout_map(m);
+  size_t biggest = 0;
+  for (auto &p : map) biggest = p.rows * p.cols > biggest ? p.rows * p.cols : biggest;
+  float *stage = nullptr;
+  TRY(b200_malloc(ctx, biggest * 4, (void **)&stage));
+  int rc = B200_OK;
+  for (int which = 0; which < 2 && !rc; ++which) {
+    float *dst = which ? m->adam_v : m->adam_m;
+    const float *host = which ? host_v : host_m;
+    for (auto &p : map) {
+      if (p.eng_off >= m->n_train) continue;
+      rc = b200_memcpy_h2d(ctx, stage, host + p.ref_off, p.rows * p.cols * 4);
+      if (!rc) rc = convert2d(ctx, stage, B200_F32, dst + p.eng_off, B200_F32, p.rows, p.cols, p.cols, p.eng_ld);
+      if (!rc) rc = b200_sync(ctx);
+      if (rc) break;
+    }
+  }
+  b200_free(ctx, stage);
+  m->step_count = (size_t)step;
+  return rc;
 }
 
 extern "C" int b200_model_init_synthetic(b200_model *m, uint64_t seed, float std) {

@@ -16,6 +16,10 @@
 #     argument and h_cache_ aliases every cached hidden state; two clone()
 #     calls give the mathematically intended behaviour.  ALIAS_FIX=0 builds the
 #     as-is variant (_ref/libref_oracle_asis.so) used only to report the delta.
+#  5. Checkpoint::save fills a local SavedTensor whose `data` points into its own `owned_data` vector, then
+#     push_back()s a COPY of it: the copy's `data` still points into the local, which is destroyed at the end of
+#     the block, so every transposed tensor is written from freed memory (cpp/src/Checkpoint.cpp:736-742, 706-713).
+#     The fixed variant makes the writer prefer the element's own `owned_data`; the file layout is unchanged.
 set -e
 HERE="$(cd "$(dirname "$0")" && pwd)"
 REF="${REFERENCE_ROOT:-/root/reference}"
@@ -25,7 +29,7 @@ CXX_BIN="${ORC_CXX:-g++}"
 OUT="$HERE/_ref"
 SRC="$OUT/src_fix$ALIAS_FIX"
 mkdir -p "$SRC"
-for f in RMSNorm Activations Positional Loss Transformer Optimizer Attention; do
+for f in RMSNorm Activations Positional Loss Transformer Optimizer Attention Checkpoint Trainer DataIngestion; do
   sed 's/DType::BF16/DType::FP32/g' "$REF/cpp/src/$f.cpp" > "$SRC/$f.cpp"
 done
 cp "$REF/cpp/src/Tensor.cpp" "$SRC/Tensor.cpp"
@@ -43,6 +47,8 @@ if [ "$ALIAS_FIX" = "1" ]; then
   sed -i 's/h_cache_.push_back(h);/h_cache_.push_back(h.clone());/g' "$SRC/Transformer.cpp"
   grep -q 'gate.clone()' "$SRC/Activations.cpp"
   [ "$(grep -c 'push_back(h.clone())' "$SRC/Transformer.cpp")" = "2" ]
+  sed -i 's/reinterpret_cast<const char \*>(tensors\[i\].data),/reinterpret_cast<const char *>(tensors[i].owned_data.empty() ? tensors[i].data : tensors[i].owned_data.data()),/' "$SRC/Checkpoint.cpp"
+  [ "$(grep -c 'owned_data.empty() ? tensors' "$SRC/Checkpoint.cpp")" = "1" ]
   LIB="$OUT/libref_oracle.so"
 else
   LIB="$OUT/libref_oracle_asis.so"

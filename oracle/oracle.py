@@ -108,6 +108,11 @@ class Oracle:
         self._layer_b = sig("layer_backward", None, C.POINTER(_Cfg), _F, _F, _F, _F, _F)
         self._model = sig("model_loss_and_grads", C.c_float, C.POINTER(_Cfg), _I, _I, _F, C.c_void_p,
                           C.c_void_p)
+        # training-driver files: only the reference build has them (its own Checkpoint / Trainer classes)
+        if hasattr(L, prefix + "checkpoint_save"):
+            self._ck_save = sig("checkpoint_save", C.c_int, C.POINTER(_Cfg), _F, _F, _F, C.c_uint64, C.c_char_p)
+            self._ck_load = sig("checkpoint_load", C.c_int, C.POINTER(_Cfg), C.c_char_p, _F, _F, _F, C.POINTER(C.c_uint64))
+            self._lr = sig("scheduled_lr", C.c_float, _sz, _sz, _sz, C.c_float, C.c_float)
 
     # ---- primitive ops -------------------------------------------------
     def gemm(self, A, B, M, N, K, transA=False, transB=False, C_in=None):
@@ -223,6 +228,25 @@ class Oracle:
                            grads.ctypes.data if want_grads else None,
                            logits.ctypes.data if want_logits else None)
         return float(loss), grads, logits
+
+
+    # ---- the reference's Checkpoint::save / ::load and Trainer::get_scheduled_lr (reference build only) ----
+    def checkpoint_save(self, cfg: Config, path: str, params, m, v, step: int):
+        rc = self._ck_save(C.byref(cfg.c()), _f(params), _f(m), _f(v), int(step), path.encode())
+        if rc:
+            raise RuntimeError(f"reference Checkpoint::save failed for {path}")
+
+    def checkpoint_load(self, cfg: Config, path: str):
+        n = cfg.model_params
+        p, m, v = np.empty(n, np.float32), np.empty(n, np.float32), np.empty(n, np.float32)
+        step = C.c_uint64(0)
+        rc = self._ck_load(C.byref(cfg.c()), path.encode(), p, m, v, C.byref(step))
+        if rc:
+            raise RuntimeError(f"reference Checkpoint::load failed for {path}")
+        return p, m, v, int(step.value)
+
+    def scheduled_lr(self, step, warmup, max_steps, lr_max, lr_min) -> float:
+        return float(self._lr(step, warmup, max_steps, lr_max, lr_min))
 
 
 def _f(a):

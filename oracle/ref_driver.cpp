@@ -248,3 +248,94 @@ REF_API float ref_model_loss_and_grads(const Cfg *c, const int32_t *tokens, cons
   }
   return loss;
 }
+
+// ---- training-driver files: the reference's own Checkpoint::save / ::load and LR schedule ------------------
+#include "Checkpoint.hpp"
+#include "Trainer.hpp"
+namespace {
+// Registers the parameters in the order Trainer::train does (cpp/src/Trainer.cpp:188-198) so that the moment
+// vectors line up with what Checkpoint expects; grads are dummies of the right shape.
+struct OptHarness {
+  Transformer model;
+  AdamWOptimizer opt;
+  std::vector<Tensor> grads;
+  explicit OptHarness(const Cfg *c) : model(mc(c)), opt(0.9f, 0.95f, 1e-8f, 0.1f) {
+    std::vector<Tensor *> ps{&model.token_embeddings(), &model.output_projection()};
+    for (auto &l : model.layers()) {
+      ps.push_back(&l.w_gate); ps.push_back(&l.w_up); ps.push_back(&l.w_down);
+      ps.push_back(&l.attn.Wq()); ps.push_back(&l.attn.Wk()); ps.push_back(&l.attn.Wv()); ps.push_back(&l.attn.Wo());
+    }
+    grads.reserve(ps.size());
+    for (Tensor *p : ps) { grads.emplace_back(p->shape(), 0.0f); opt.register_parameter(p, &grads.back()); }
+  }
+  // flat (per-tensor order of ref_model_loss_and_grads) <-> the optimizer's registration order
+  template <class F> void each_state(const Cfg *c, std::vector<Tensor> &st, float *flat, F f) {
+    const size_t V = c->V, H = c->H, L = c->L, lp = layer_params(c);
+    f(st[0], flat);
+    f(st[1], flat + V * H + L * lp + H);
+    for (size_t l = 0; l < L; ++l) {
+      float *p = flat + V * H + l * lp;
+      const size_t i0 = 2 + l * 7;
+      p += H; f(st[i0 + 3], p); p += st[i0 + 3].size(); f(st[i0 + 4], p); p += st[i0 + 4].size();
+      f(st[i0 + 5], p); p += st[i0 + 5].size(); f(st[i0 + 6], p); p += st[i0 + 6].size();
+      p += H; f(st[i0 + 0], p); p += st[i0 + 0].size(); f(st[i0 + 1], p); p += st[i0 + 1].size(); f(st[i0 + 2], p);
+    }
+  }
+  void load_model(const Cfg *c, const float *params) {
+    const size_t V = c->V, H = c->H, L = c->L, lp = layer_params(c);
+    load(model.token_embeddings(), params);
+    for (size_t l = 0; l < L; ++l) load_layer(model.layers()[l], params + V * H + l * lp);
+    load(model.final_norm().weight(), params + V * H + L * lp);
+    load(model.output_projection(), params + V * H + L * lp + H);
+  }
+  void store_model(const Cfg *c, float *params) {
+    const size_t V = c->V, H = c->H, L = c->L, lp = layer_params(c);
+    to(model.token_embeddings(), params);
+    for (size_t l = 0; l < L; ++l) {
+      float *p = params + V * H + l * lp;
+      TransformerLayer &y = model.layers()[l];
+      to(y.attn_norm.weight(), p); p += H; to(y.attn.Wq(), p); p += y.attn.Wq().size(); to(y.attn.Wk(), p); p += y.attn.Wk().size();
+      to(y.attn.Wv(), p); p += y.attn.Wv().size(); to(y.attn.Wo(), p); p += y.attn.Wo().size(); to(y.ffn_norm.weight(), p); p += H;
+      to(y.w_gate, p); p += y.w_gate.size(); to(y.w_up, p); p += y.w_up.size(); to(y.w_down, p);
+    }
+    to(model.final_norm().weight(), params + V * H + L * lp);
+    to(model.output_projection(), params + V * H + L * lp + H);
+  }
+};
+}  // namespace
+
+REF_API int ref_checkpoint_save(const Cfg *c, const float *params, const float *m, const float *v, uint64_t step, const char *path) {
+  Quiet q;
+  OptHarness h(c);
+  h.load_model(c, params);
+  h.each_state(c, h.opt.m_states(), const_cast<float *>(m), [](Tensor &t, float *p) { load(t, p); });
+  h.each_state(c, h.opt.v_states(), const_cast<float *>(v), [](Tensor &t, float *p) { load(t, p); });
+  h.opt.step_count() = (size_t)step;
+  return Checkpoint::save(path, h.model, h.opt, (size_t)step) ? 0 : 1;
+}
+REF_API int ref_checkpoint_load(const Cfg *c, const char *path, float *params, float *m, float *v, uint64_t *step) {
+  Quiet q;
+  OptHarness h(c);
+  size_t st = 0;
+  if (!Checkpoint::load(path, h.model, h.opt, st)) return 1;
+  h.store_model(c, params);
+  std::memset(m, 0, (2 * c->V * c->H + c->L * layer_params(c) + c->H) * sizeof(float));
+  std::memset(v, 0, (2 * c->V * c->H + c->L * layer_params(c) + c->H) * sizeof(float));
+  h.each_state(c, h.opt.m_states(), m, [](Tensor &t, float *p) { to(t, p); });
+  h.each_state(c, h.opt.v_states(), v, [](Tensor &t, float *p) { to(t, p); });
+  *step = st;
+  return 0;
+}
+// Trainer::get_scheduled_lr reads nothing but its config; the model / optimizer / data-loader references the
+// constructor wants are never touched, so a small real model and an unconstructed loader slot are enough.
+REF_API float ref_scheduled_lr(size_t step, size_t warmup, size_t max_steps, float lr_max, float lr_min) {
+  Quiet q;
+  Cfg c{1, 4, 8, 8, 2, 1, 4, 8, 1, 1e-5f, 10000.0f};
+  OptHarness h(&c);
+  RoPE rope(4, 4, 10000.0f);
+  alignas(DataIngestion) static unsigned char slot[sizeof(DataIngestion)];
+  TrainerConfig tc;
+  tc.warmup_steps = warmup; tc.max_steps = max_steps; tc.lr_max = lr_max; tc.lr_min = lr_min;
+  Trainer t(tc, h.model, h.opt, *reinterpret_cast<DataIngestion *>(slot), rope);
+  return t.get_scheduled_lr(step);
+}

@@ -3,6 +3,7 @@ C++ CPU ops (oracle/_ref/libref_oracle.so, built by oracle/build_ref.sh from
 the reference checkout, alias-fixed variant).  Run from the repository root:
 
     sh oracle/build_ref.sh && python tests/golden/make_golden.py
+    (python tests/golden/make_golden.py trainer   regenerates only the checkpoint / schedule fixtures)
 
 The fixtures are what pins oracle/block_oracle.c (tests/test_oracle.py) and,
 through it, the CUDA kernels, on machines where the reference checkout is
@@ -109,5 +110,28 @@ def main():
     print("wrote", len(out), "arrays;", os.path.getsize(os.path.join(HERE, "reference_cpu_ops.npz")), "bytes")
 
 
+TINY = dict(B=1, S=4, H=8, I=12, nH=2, nKV=1, hd=4, V=11, L=2)
+LR_CASES = [(w, mx, lmax, lmin) for (w, mx) in ((10, 100), (0, 7), (2000, 100000), (5, 5)) for (lmax, lmin) in ((3e-4, 3e-5), (1e-3, 0.0))]
+LR_STEPS = [0, 1, 2, 4, 5, 6, 7, 9, 10, 11, 50, 99, 100, 101, 1999, 2000, 2001, 51000, 99999, 100000, 123456]
+
+
+def trainer_files():
+    """The reference's Checkpoint::save output for a tiny seeded model (the two files are committed as they are)
+    and Trainer::get_scheduled_lr on a grid of steps / configurations."""
+    ref = oracle.load_ref()
+    cfg = oracle.Config(**TINY)
+    params = synth.model_params(SEED, cfg, std=0.5)
+    m = synth.normal(SEED, "ckpt.m", (cfg.model_params,), 0.01)
+    v = np.abs(synth.normal(SEED, "ckpt.v", (cfg.model_params,), 1e-4))
+    ref.checkpoint_save(cfg, os.path.join(HERE, "ckpt_tiny.safetensors"), params, m, v, 1234)
+    lr = np.array([[ref.scheduled_lr(st, *case) for st in LR_STEPS] for case in LR_CASES], np.float32)
+    np.savez_compressed(os.path.join(HERE, "reference_trainer.npz"), lr=lr)
+    print("wrote ckpt_tiny.safetensors (+ .opt) and", lr.size, "schedule values")
+
+
 if __name__ == "__main__":
-    main()
+    if len(sys.argv) > 1 and sys.argv[1] == "trainer":
+        trainer_files()
+    else:
+        main()
+        trainer_files()
