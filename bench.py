@@ -6,6 +6,7 @@ random-init N(0, 0.02) weights.
 
     python bench.py --gpus N --steps K --warmup W            # this backend (CUDA, sm_100a)
     python bench.py --impl reference --steps K --warmup W    # the reference's CPU ops on the host cores
+    python bench.py --workload decode [--layers L]           # only the decode workload (batch 32, prompt 512, +256 tokens)
 
 Prints ONE JSON line on rank 0.  For N > 1 launch with torch.distributed.run (one rank per GPU).
 `value` is whole-job tokens/s with inputs resident in HBM; `e2e` is the same step driven from
@@ -33,6 +34,12 @@ MODEL = dict(V=32000, H=2048, I=5632, L=28, nH=16, nKV=4, hd=128, S=2048)
 MICRO_BATCH = 8
 HYPER = dict(lr=3e-4, beta1=0.9, beta2=0.95, eps=1e-8, wd=0.1)
 METRIC, UNIT = "train_tokens_per_sec", "tokens/s"
+# DRAM traffic of the GEMM kernels, average per launch over one training step (ncu dram__bytes_read.sum +
+# dram__bytes_write.sum of the 15 GEMM launches of a 1-layer step, the 12 layer GEMMs weighted x28), and the
+# algorithmic bytes (each operand read once, the result written once) over the same launches.
+GEMM_DRAM_BYTES_PER_LAUNCH = 417951780
+GEMM_ALGO_BYTES_PER_LAUNCH = 286487047
+GEMM_TRAFFIC_SOURCE = "profiles/gemm_dram_traffic_train_step.md (ncu, 1-layer step scaled by launch counts to 28 layers)"
 
 
 def model_flops_per_token(m=MODEL):
@@ -47,6 +54,63 @@ def model_flops_per_token(m=MODEL):
 def n_params(m=MODEL):
     q, kv = m["nH"] * m["hd"], m["nKV"] * m["hd"]
     return m["L"] * (m["H"] * (q + 2 * kv) + q * m["H"] + 3 * m["H"] * m["I"]) + 2 * m["V"] * m["H"] + m["H"]
+
+
+DECODE = dict(batch=32, prompt=512, new_tokens=256)
+
+
+def hbm_peak():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        return float(json.load(open(p))["hbm_gbs"]), "measured (MEASURED_PEAKS.json, copy bandwidth)"
+    return 6650.0, "fallback (6.65 TB/s)"
+
+
+def decode_metrics(ctx, bridge, synth, layers=MODEL["L"], reps=2):
+    """Autoregressive decode of the same model: batch 32, prompt 512, 256 new tokens, sampling with
+    temperature 0.8 / top-p 0.9 / repetition penalty 1.1 (python/pipeline/inference/sampler.py defaults), through
+    the host-buffer entry point b200_model_generate.  HBM-bound: per token-step every projection weight is read
+    once (bf16) and the K/V cache of every layer is read once for all query heads of a KV head."""
+    B, P, NEW = DECODE["batch"], DECODE["prompt"], DECODE["new_tokens"]
+    m = dict(MODEL); m["L"] = layers
+    shape = bridge.Shape(B=B, S=P + NEW, H=m["H"], I=m["I"], nH=m["nH"], nKV=m["nKV"], hd=m["hd"], V=m["V"], L=layers)
+    model = bridge.Model(ctx, shape, "bf16", with_optimizer=False)
+    model.init_synthetic(1234, 0.02)
+    prompt = synth.token_ids(7, "prompt", (B, P), m["V"])
+    cfg = bridge.SamplerConfig.make(temperature=0.8, top_p=0.9, repetition_penalty=1.1, top_k=0, seed=5, whitespace_ids=(220, 256, 198))
+    n0 = ctx.launch_count()
+    for _ in range(reps):
+        t0 = time.perf_counter()
+        out, prefill_ms, decode_ms = model.generate(prompt, NEW, cfg)
+        wall = time.perf_counter() - t0
+    launches = (ctx.launch_count() - n0) // reps
+    model.close()
+    steps = NEW - 1
+    q, kv = m["nH"] * m["hd"], m["nKV"] * m["hd"]
+    w_bytes = 2 * (layers * (m["H"] * (q + 2 * kv) + q * m["H"] + 3 * m["H"] * m["I"]) + m["H"] * m["V"])
+    t_avg = P + (NEW + 1) / 2.0                       # keys read per step, averaged over the generated positions
+    kv_bytes = 2 * layers * B * t_avg * kv * 2
+    step_s = decode_ms / 1e3 / steps
+    peak, src = hbm_peak()
+    achieved = (w_bytes + kv_bytes) / step_s / 1e9
+    return {"workload": f"decode: batch {B}, prompt {P}, +{NEW} tokens, {layers}L, KV cache, temperature 0.8 top-p 0.9 rep 1.1",
+            "decode_tokens_per_sec": B * steps / (decode_ms / 1e3), "ms_per_token_step": step_s * 1e3,
+            "prefill_tokens_per_sec": B * P / (prefill_ms / 1e3), "prefill_ms": prefill_ms,
+            "e2e_tokens_per_sec": B * NEW / wall, "gpu_launches": int(launches),
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "peak_source": src, "bytes_per_step": {"weights": w_bytes, "kv_cache_avg": kv_bytes}},
+            "distinct_ids": int(len(np.unique(out)))}
+
+
+def run_decode(args):
+    bridge = importlib.import_module(PKG + ".bridge")
+    synth = importlib.import_module(PKG + ".synth")
+    ctx = bridge.Context(int(os.environ.get("LOCAL_RANK", "0")))
+    d = decode_metrics(ctx, bridge, synth, args.layers, reps=max(1, args.steps if args.steps < 3 else 2))
+    ctx.close()
+    print(json.dumps({"metric": "decode_tokens_per_sec", "value": d["decode_tokens_per_sec"], "unit": UNIT, "n_gpus": 1,
+                      "higher_is_better": True, "dtype": "bf16", "data": "synthetic", "config": {"workload": d["workload"]},
+                      "decode": d}))
 
 
 def measured_peaks():
@@ -247,19 +311,23 @@ def run_b200(args):
                     "six_n_tflops_per_gpu": 6.0 * n_params(mcfg) * B * S * args.steps / (ms / 1000.0) / 1e12,
                     "frac_of_measured_sustained_bf16": fpt * B * S * args.steps / (ms / 1000.0) / 1e12 / peak,
                     "frac_of_nominal_2250": fpt * B * S * args.steps / (ms / 1000.0) / 1e12 / 2250.0},
-            "roofline": {"kernel": "gemm_tc_kernel (tcgen05 bf16 GEMM, all projection/vocab GEMMs fwd+dgrad+wgrad)",
+            "roofline": {"kernel": "gemm_tc2_kernel / gemm_tc_kernel (tcgen05 bf16 GEMM: all projection and vocab GEMMs, fwd + dgrad + wgrad)",
                          "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
                          "frac": (achieved / peak) if achieved else None, "peak_source": peak_src,
                          "launches_timed": gemm_n, "share_of_step_time": gemm_ms / ms if ms > 0 else None,
-                         "traffic": None},
+                         "traffic": GEMM_DRAM_BYTES_PER_LAUNCH, "traffic_source": GEMM_TRAFFIC_SOURCE,
+                         "algorithmic_bytes_per_launch": GEMM_ALGO_BYTES_PER_LAUNCH},
             "e2e": {"value": tokens_total / e2e_s, "unit": UNIT, "h2d_bytes_per_step": int(2 * B * S * 4),
                     "d2h_bytes_per_step": 4},
             "gpu_launches": int(launches), "clocks": clocks, "loss": {"device_path": loss_dev, "host_path": loss_host},
         }
         if not args.no_cpu_baseline and world == 1:
             out["cpu_baseline"] = cpu_baseline()
-        print(json.dumps(out))
     model.close()
+    if rank == 0 and world == 1 and not args.no_decode:
+        out["decode"] = decode_metrics(ctx, bridge, synth, args.layers)
+    if rank == 0:
+        print(json.dumps(out))
     ctx.close()
     if world > 1:
         dist.destroy_process_group()
@@ -275,9 +343,13 @@ def main():
     ap.add_argument("--batch", type=int, default=MICRO_BATCH)
     ap.add_argument("--seq", type=int, default=MODEL["S"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-decode", action="store_true", help="skip the decode workload appended to the 1-GPU line")
+    ap.add_argument("--workload", default="train", choices=["train", "decode"])
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload == "decode":
+        run_decode(args)
     else:
         run_b200(args)
 

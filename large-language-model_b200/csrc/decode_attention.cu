@@ -70,13 +70,14 @@ attn_decode_kernel(DecodeAttnArgs a) {
 #pragma unroll
     for (int e = 0; e < EPL; ++e) { qf[g][e] *= a.scale; acc[g][e] = 0.f; }
   }
-  constexpr int KB = 4;                            // keys per warp step: their rows are all in flight before any maths
+  constexpr int KB = 4;                            // keys per warp step
   const bool fused_append = a.k_new != nullptr;
-  for (int j = k0 + warp; j < k1; j += WARPS * KB) {
-    // raw loads of all KB rows first (branch-free: rows past the run re-read the first one and are masked below)
-    typename RowLoad<T, EPL>::Raw kr[KB], vr[KB];
-    const T *k_new = (const T *)a.k_new + (size_t)b * a.ldq + (size_t)kvh * HD + lane * EPL;
-    const T *v_new = (const T *)a.v_new + (size_t)b * a.ldq + (size_t)kvh * HD + lane * EPL;
+  const T *k_new = (const T *)a.k_new + (size_t)b * a.ldq + (size_t)kvh * HD + lane * EPL;
+  const T *v_new = (const T *)a.v_new + (size_t)b * a.ldq + (size_t)kvh * HD + lane * EPL;
+  typedef typename RowLoad<T, EPL>::Raw Raw;
+  // Raw loads of the KB rows of one step, branch-free (rows past the run re-read the step's first row and are masked in
+  // the softmax).  The next step's rows are requested before this step's maths, so two steps of rows are in flight.
+  auto load_rows = [&](int j, Raw *kr, Raw *vr) {
 #pragma unroll
     for (int i = 0; i < KB; ++i) {
       const int ji = j + i * WARPS, jc = ji < k1 ? ji : j;
@@ -84,24 +85,30 @@ attn_decode_kernel(DecodeAttnArgs a) {
       kr[i] = RowLoad<T, EPL>::ldg(from_proj ? k_new : kc + (size_t)jc * KV);
       vr[i] = RowLoad<T, EPL>::ldg(from_proj ? v_new : vc + (size_t)jc * KV);
     }
-    if (fused_append && h0 % G == 0) {                             // ... and are appended to the cache here
+  };
+  Raw kr[KB], vr[KB];
+  if (k0 + warp < k1) load_rows(k0 + warp, kr, vr);
+  for (int j = k0 + warp; j < k1; j += WARPS * KB) {
+    Raw kn[KB], vn[KB];
+    const int jn = j + WARPS * KB;
+    if (jn < k1) load_rows(jn, kn, vn);
+    if (fused_append && h0 % G == 0) {                             // ... which are appended to the cache here
 #pragma unroll
       for (int i = 0; i < KB; ++i) {
         const int ji = j + i * WARPS;
         if (ji == t_len - 1) { RowLoad<T, EPL>::stg(kc + (size_t)ji * KV, kr[i]); RowLoad<T, EPL>::stg(vc + (size_t)ji * KV, vr[i]); }
       }
     }
-    float kf[KB][EPL], vf[KB][EPL];
-#pragma unroll
-    for (int i = 0; i < KB; ++i) { RowLoad<T, EPL>::unpack(kr[i], kf[i]); RowLoad<T, EPL>::unpack(vr[i], vf[i]); }
     float s[KB][GQ];
 #pragma unroll
     for (int i = 0; i < KB; ++i) {
+      float kf[EPL];
+      RowLoad<T, EPL>::unpack(kr[i], kf);
 #pragma unroll
       for (int g = 0; g < GQ; ++g) {
         float d = 0.f;
 #pragma unroll
-        for (int e = 0; e < EPL; ++e) d += qf[g][e] * kf[i][e];
+        for (int e = 0; e < EPL; ++e) d += qf[g][e] * kf[e];
         s[i][g] = d;
       }
     }
@@ -113,24 +120,37 @@ attn_decode_kernel(DecodeAttnArgs a) {
         for (int g = 0; g < GQ; ++g) s[i][g] += __shfl_xor_sync(0xffffffffu, s[i][g], off);
       }
     }
+    float corr[GQ];
 #pragma unroll
     for (int g = 0; g < GQ; ++g) {
       float m_new = m[g];
 #pragma unroll
       for (int i = 0; i < KB; ++i) if (j + i * WARPS < k1) m_new = fmaxf(m_new, s[i][g]);
-      const float corr = __expf(m[g] - m_new);
+      corr[g] = __expf(m[g] - m_new);
       float psum = 0.f;
 #pragma unroll
-      for (int e = 0; e < EPL; ++e) acc[g][e] *= corr;
-#pragma unroll
       for (int i = 0; i < KB; ++i) {
-        const float p = (j + i * WARPS < k1) ? __expf(s[i][g] - m_new) : 0.f;
-        psum += p;
-#pragma unroll
-        for (int e = 0; e < EPL; ++e) acc[g][e] += p * vf[i][e];
+        s[i][g] = (j + i * WARPS < k1) ? __expf(s[i][g] - m_new) : 0.f;      // scores become probabilities
+        psum += s[i][g];
       }
-      l[g] = l[g] * corr + psum;
+      l[g] = l[g] * corr[g] + psum;
       m[g] = m_new;
+#pragma unroll
+      for (int e = 0; e < EPL; ++e) acc[g][e] *= corr[g];
+    }
+#pragma unroll
+    for (int i = 0; i < KB; ++i) {
+      float vf[EPL];
+      RowLoad<T, EPL>::unpack(vr[i], vf);
+#pragma unroll
+      for (int g = 0; g < GQ; ++g) {
+#pragma unroll
+        for (int e = 0; e < EPL; ++e) acc[g][e] += s[i][g] * vf[e];
+      }
+    }
+    if (jn < k1) {
+#pragma unroll
+      for (int i = 0; i < KB; ++i) { kr[i] = kn[i]; vr[i] = vn[i]; }
     }
   }
   // ---- merge the warps of this CTA ------------------------------------------------------------
@@ -236,9 +256,9 @@ int attn_decode(b200_ctx *ctx, const void *q, const void *k_new, const void *v_n
   a.ws_o = ws; a.ws_ml = ws + B * nH * ATTN_DECODE_MAX_SPLITS * hd; a.tickets = tickets;
   a.nH = (int)nH; a.nKV = (int)nKV; a.S_max = (int)S_max; a.t_len = (int)t_len; a.ldq = (int)ldq; a.ldo = (int)ldo;
   a.scale = 1.0f / sqrtf((float)hd);
-  // key runs: enough CTAs for about four per SM, at least 4 keys per warp, at most 16 splits
+  // key runs: one wave of CTAs (two fit per SM), at least 4 keys per warp, at most 16 splits
   const size_t groups = B * (nH / gq);
-  size_t want = (4 * (size_t)ctx->sm_count + groups - 1) / groups;
+  size_t want = (2 * (size_t)ctx->sm_count + groups - 1) / groups;
   if (want > (size_t)ATTN_DECODE_MAX_SPLITS) want = ATTN_DECODE_MAX_SPLITS;
   size_t chunk = (t_len + want - 1) / want;
   if (chunk < 32) chunk = 32;

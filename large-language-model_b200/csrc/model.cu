@@ -109,6 +109,11 @@ struct b200_model {
   int rank = 0, world = 1;
   cudaStream_t comm_stream = nullptr;
   cudaEvent_t ev_grad_ready = nullptr, ev_comm_done = nullptr;
+  // optimizer-in-backward: AdamW of a bucket runs on a side stream as soon as its gradients are final and its
+  // weights are no longer read by the rest of the backward pass (HBM-bound work under the tensor-bound GEMMs)
+  cudaStream_t opt_stream = nullptr;
+  cudaEvent_t ev_bucket = nullptr, ev_opt_done = nullptr;
+  const b200_adamw_params *fused_opt = nullptr;
 
   size_t off_emb() const { return 0; }
   size_t off_layer(size_t l) const { return V * H + l * layer_train; }
@@ -191,6 +196,11 @@ extern "C" int b200_model_create(b200_ctx *ctx, const b200_model_config *cfg, b2
   if (rc == B200_OK) rc = b200_fill_zero(ctx, m->grads, m->n_total * 4);
   if (rc == B200_OK && m->with_opt) { rc = b200_fill_zero(ctx, m->adam_m, m->n_train * 4); if (!rc) rc = b200_fill_zero(ctx, m->adam_v, m->n_train * 4); }
   if (rc == B200_OK && !m->master && dt == B200_F32) m->master = (float *)m->params;
+  if (rc == B200_OK && m->with_opt &&
+      (cudaStreamCreateWithFlags(&m->opt_stream, cudaStreamNonBlocking) != cudaSuccess ||
+       cudaEventCreateWithFlags(&m->ev_bucket, cudaEventDisableTiming) != cudaSuccess ||
+       cudaEventCreateWithFlags(&m->ev_opt_done, cudaEventDisableTiming) != cudaSuccess))
+    rc = b200_fail(ctx, B200_ERR_CUDA, "side stream for the optimizer could not be created");
   if (rc != B200_OK) { b200_model_destroy(m); return rc; }
   *out = m;
   return B200_OK;
@@ -200,6 +210,9 @@ extern "C" int b200_model_destroy(b200_model *m) {
   if (!m) return B200_OK;
   b200_dp_shutdown(m);
   cudaStreamSynchronize(m->ctx->stream);
+  if (m->opt_stream) { cudaStreamSynchronize(m->opt_stream); cudaStreamDestroy(m->opt_stream); }
+  if (m->ev_bucket) cudaEventDestroy(m->ev_bucket);
+  if (m->ev_opt_done) cudaEventDestroy(m->ev_opt_done);
   for (void *p : m->allocs) cudaFree(p);
   if (m->pin_tokens) cudaFreeHost(m->pin_tokens);
   if (m->pin_targets) cudaFreeHost(m->pin_targets);
@@ -482,6 +495,28 @@ static int allreduce_async(b200_model *m, float *buf, size_t n) {
   if (r != 0) return b200_fail(ctx, B200_ERR_COMM, "ncclAllReduce failed: %s", nccl::api().GetErrorString ? nccl::api().GetErrorString(r) : "?");
   return B200_OK;
 }
+// AdamW for parameters [off, off+n) on the side stream, ordered after everything enqueued so far on the main stream
+// (and, data-parallel, after the bucket's all-reduce, which runs on that same side stream).
+static int opt_bucket(b200_model *m, size_t off, size_t n) {
+  if (!m->fused_opt || !n) return B200_OK;
+  b200_ctx *ctx = m->ctx;
+  cudaStream_t side = (m->world > 1 && m->comm) ? m->comm_stream : m->opt_stream;
+  B200_CUDA(ctx, cudaEventRecord(m->ev_bucket, ctx->stream));
+  B200_CUDA(ctx, cudaStreamWaitEvent(side, m->ev_bucket, 0));
+  void *shadow = ((void *)m->master != m->params) ? (void *)((char *)m->params + off * dtype_size(m->dt)) : nullptr;
+  cudaStream_t keep = ctx->stream;
+  ctx->stream = side;
+  const int rc = b200_adamw_step(ctx, m->master + off, m->grads + off, m->adam_m + off, m->adam_v + off, shadow, n, m->fused_opt);
+  ctx->stream = keep;
+  return rc;
+}
+static int opt_join(b200_model *m) {
+  if (!m->fused_opt || (m->world > 1 && m->comm)) return B200_OK;     // data-parallel: allreduce_join covers the side stream
+  b200_ctx *ctx = m->ctx;
+  B200_CUDA(ctx, cudaEventRecord(m->ev_opt_done, m->opt_stream));
+  B200_CUDA(ctx, cudaStreamWaitEvent(ctx->stream, m->ev_opt_done, 0));
+  return B200_OK;
+}
 static int allreduce_join(b200_model *m) {
   if (m->world <= 1 || !m->comm) return B200_OK;
   b200_ctx *ctx = m->ctx;
@@ -512,15 +547,19 @@ extern "C" int b200_model_loss_and_grads(b200_model *m, const int32_t *tok, cons
   TRY(b200_gemm_ld(ctx, m->fh, m->logits, m->G(m->off_out()), H, V, M, 1, 0, 0, dt, B200_F32, H, V, V));
   TRY(allreduce_async(m, m->G(m->off_out()), H * V));
   TRY(b200_gemm_ld(ctx, m->logits, m->P(m->off_out()), m->tmpH, M, H, V, 0, 1, 0, dt, dt, V, V, H));
+  TRY(opt_bucket(m, m->off_out(), H * V));          // after the data-gradient GEMM, the last reader of this weight
   void *g = m->g_ping, *g_next = m->g_pong;
   TRY(b200_rms_norm_backward(ctx, m->tmpH, m->hs[m->L], m->P(m->off_final_norm()), g, nullptr, eps, M, H, dt));
   for (size_t l = m->L; l-- > 0;) {
     TRY(layer_backward_core(m, l, g, g_next, B, S));
     TRY(allreduce_async(m, m->G(m->off_layer(l)), m->layer_train));
+    TRY(opt_bucket(m, m->off_layer(l), m->layer_train));
     void *t = g; g = g_next; g_next = t;
   }
   TRY(b200_embedding_backward(ctx, (const uint32_t *)tok, g, m->G(m->off_emb()), M, H, V, dt));
   TRY(allreduce_async(m, m->G(m->off_emb()), V * H));
+  TRY(opt_bucket(m, m->off_emb(), V * H));
+  TRY(opt_join(m));
   return allreduce_join(m);
 }
 
@@ -538,8 +577,25 @@ extern "C" int b200_model_adamw_step(b200_model *m, float lr, float beta1, float
 
 extern "C" int b200_model_train_step(b200_model *m, const int32_t *tok, const int32_t *tgt, size_t B, size_t S,
                                      float lr, float beta1, float beta2, float eps, float wd, float *dev_loss) {
-  TRY(b200_model_loss_and_grads(m, tok, tgt, B, S, dev_loss));
-  return b200_model_adamw_step(m, lr, beta1, beta2, eps, wd);
+  if (!m) return B200_ERR_INVALID;
+  // Optimizer in backward (opt-in, B200_FUSED_OPT=1): measured no faster on a power-capped B200 -- the GEMMs it runs
+  // under lose what the hidden AdamW gains -- so the plain order is the default.  Every bucket offset keeps the
+  // 16-byte alignment the AdamW kernel wants.
+  const char *env = getenv("B200_FUSED_OPT");
+  const bool fuse = (env && env[0] == '1') && m->with_opt && m->master && m->opt_stream && (m->V * m->H) % 4 == 0 && m->layer_train % 4 == 0;
+  if (!fuse) {
+    TRY(b200_model_loss_and_grads(m, tok, tgt, B, S, dev_loss));
+    return b200_model_adamw_step(m, lr, beta1, beta2, eps, wd);
+  }
+  m->step_count++;
+  b200_adamw_params p;
+  p.lr = lr; p.beta1 = beta1; p.beta2 = beta2; p.eps = eps; p.weight_decay = wd;
+  p.bias_correction1 = 1.0f - powf(beta1, (float)m->step_count);   // cpp/src/Optimizer.cpp:141-142
+  p.bias_correction2 = 1.0f - powf(beta2, (float)m->step_count);
+  m->fused_opt = &p;
+  const int rc = b200_model_loss_and_grads(m, tok, tgt, B, S, dev_loss);
+  m->fused_opt = nullptr;
+  return rc;
 }
 
 extern "C" int b200_model_train_step_host(b200_model *m, const int32_t *tok, const int32_t *tgt, size_t B, size_t S,

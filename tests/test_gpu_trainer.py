@@ -106,3 +106,20 @@ def test_engine_checkpoint_round_trip(ctx, tmp_path):
     b = other.train_step_host(np.ascontiguousarray(tok[:, :-1]), np.ascontiguousarray(tok[:, 1:]), 1e-2)
     assert abs(a - b) <= 2e-3 * abs(a)
     m.close(); other.close()
+
+
+def test_optimizer_in_backward_order_gives_the_same_update(ctx, monkeypatch):
+    """B200_FUSED_OPT=1 runs each bucket's AdamW on a side stream during the backward pass; same result."""
+    tok = synth.token_ids(6, "t", (SHAPE["B"], SHAPE["S"] + 1), SHAPE["V"])
+    x, y = np.ascontiguousarray(tok[:, :-1]), np.ascontiguousarray(tok[:, 1:])
+    results = []
+    for flag in ("0", "1"):
+        monkeypatch.setenv("B200_FUSED_OPT", flag)
+        m = fresh_model(ctx, "bf16")
+        losses = [m.train_step_host(x, y, 1e-2) for _ in range(4)]
+        results.append((losses, m.read_params(), m.read_opt_state()))
+        m.close()
+    (l0, p0, (m0, v0, s0)), (l1, p1, (m1, v1, s1)) = results
+    assert s0 == s1 == 4
+    np.testing.assert_allclose(l0, l1, rtol=1e-5)
+    assert rel(p1, p0) < 1e-6 and rel(m1, m0) < 1e-5 and rel(v1, v0) < 1e-5
