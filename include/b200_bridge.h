@@ -126,6 +126,12 @@ int b200_swiglu_backward(b200_ctx *ctx, const void *grad_output, const void *gat
 int b200_fused_swiglu_gemm(b200_ctx *ctx, const void *gate, const void *up, const void *B, void *C, void *scratch,
                            size_t M, size_t N, size_t K, b200_dtype dtype);
 
+/* metal_bridge::gemm_ffn (MetalBridge.hpp:119-120; gemm_ffn.metal:44-183): c[M,N] = silu(a*W_gate) * (a*W_up) with the two
+ * weights stored side by side, w_gate_up = [gate | up] of shape [K, 2N].  gate_up_out (optional, [M,2N]) receives the two
+ * products (kept for the backward pass).  For bf16 the activation runs in the GEMM epilogue. */
+int b200_gemm_ffn(b200_ctx *ctx, const void *a, const void *w_gate_up, void *gate_up_out, void *c, size_t M, size_t N,
+                  size_t K, b200_dtype dtype);
+
 /* ---- metal_bridge::residual_add (MetalBridge.hpp:78): a += b */
 int b200_residual_add(b200_ctx *ctx, void *a, const void *b, size_t n, b200_dtype dtype);
 

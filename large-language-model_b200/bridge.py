@@ -86,6 +86,7 @@ _SIGS = {
     "b200_swiglu_forward": (_i, [_vp, _vp, _vp, _vp, _sz, _i]),
     "b200_swiglu_backward": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _sz, _i]),
     "b200_fused_swiglu_gemm": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _sz, _sz, _sz, _i]),
+    "b200_gemm_ffn": (_i, [_vp, _vp, _vp, _vp, _vp, _sz, _sz, _sz, _i]),
     "b200_residual_add": (_i, [_vp, _vp, _vp, _sz, _i]),
     "b200_reshape_to_4d": (_i, [_vp, _vp, _vp, _sz, _sz, _sz, _sz, _i]),
     "b200_reshape_to_3d": (_i, [_vp, _vp, _vp, _sz, _sz, _sz, _sz, _i]),
@@ -324,6 +325,13 @@ class Context:
         dg, du = self.empty(gate.shape, gate.dtype), self.empty(gate.shape, gate.dtype)
         self._check(self.lib.b200_swiglu_backward(self.h, dy.ptr, gate.ptr, up.ptr, dg.ptr, du.ptr, gate.size, gate.code))
         return dg, du
+
+    def gemm_ffn(self, a, w_gate_up, M, N, K, want_gate_up=False):
+        """silu(a @ W_gate) * (a @ W_up) for w_gate_up = [gate | up] ([K, 2N]); optionally also the two products."""
+        out = self.empty((M, N), a.dtype)
+        gu = self.empty((M, 2 * N), a.dtype) if want_gate_up else None
+        self._check(self.lib.b200_gemm_ffn(self.h, a.ptr, w_gate_up.ptr, gu.ptr if gu is not None else None, out.ptr, M, N, K, a.code))
+        return (out, gu) if want_gate_up else out
 
     def residual_add(self, a, b):
         self._check(self.lib.b200_residual_add(self.h, a.ptr, b.ptr, a.size, a.code))

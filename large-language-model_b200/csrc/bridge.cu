@@ -187,8 +187,10 @@ int b200_gemm_ld(b200_ctx *ctx, const void *A, const void *B, void *C, size_t M,
   B200_REQUIRE(ctx, !epi || (in_dt == B200_BF16 && out_dt == B200_BF16 && !acc && K > 0 &&
                              gemm_tc_supported(A, B, C, M, N, K, lda, ldb, ldc, out_dt)),
                "gemm: a fused epilogue needs the tensor-core path");
-  B200_REQUIRE(ctx, !(epi && (epi->swiglu_I || epi->pos_dev)) || (K > 0 && ctx->gemm_skinny && gemm_skinny_supported(M, ta, tb, acc)),
-               "gemm: the SwiGLU epilogue and device-side positions exist only in the few-row kernel");
+  const bool few_rows = K > 0 && ctx->gemm_skinny && gemm_skinny_supported(M, ta, tb, acc);
+  B200_REQUIRE(ctx, !(epi && epi->pos_dev) || few_rows, "gemm: device-side positions exist only in the few-row kernel");
+  B200_REQUIRE(ctx, !(epi && epi->swiglu_I) || few_rows || (epi->act_out && K > 0 && gemm_tc2_swiglu_eligible(ctx, M, (size_t)epi->swiglu_I)),
+               "gemm: no kernel with a SwiGLU epilogue takes this shape");
   if (M == 0 || N == 0) return B200_OK;
   if (K == 0) {
     if (!acc) {
@@ -204,7 +206,7 @@ int b200_gemm_ld(b200_ctx *ctx, const void *A, const void *B, void *C, size_t M,
       return gemm_skinny_launch(ctx, A, B, C, M, N, K, out_dt, lda, ldb, ldc, epi);
     // two-CTA kernel when there are enough 256x256 tile pairs to fill the SM pairs; else 128x256 tiles
     const size_t pairs = ((M + 255) / 256) * ((N + 255) / 256);
-    if (ctx->gemm_2cta && pairs >= (size_t)ctx->sm_count / 4)
+    if ((epi && epi->swiglu_I) || (ctx->gemm_2cta && pairs >= (size_t)ctx->sm_count / 4))
       return gemm_tc2_launch(ctx, A, B, C, M, N, K, ta, tb, acc, out_dt, lda, ldb, ldc, epi);
     return gemm_tc_launch(ctx, A, B, C, M, N, K, ta, tb, acc, out_dt, lda, ldb, ldc, epi);
   }
@@ -223,6 +225,34 @@ extern "C" int b200_fused_swiglu_gemm(b200_ctx *ctx, const void *gate, const voi
   int rc = swiglu_fwd_strided(ctx, gate, up, scratch, 1, M * K, M * K, M * K, dt);
   if (rc) return rc;
   return b200_gemm(ctx, scratch, B, C, M, N, K, 0, 0, 0, dt, dt);
+}
+
+// metal_bridge::gemm_ffn (MetalBridge.hpp:119-120, gemm_ffn.metal:44-183): c = silu(a*W_gate) * (a*W_up), with the two
+// weights stored side by side as W = [gate | up] ([K, 2N], the engine's layout).  gate_up_out (optional, [M, 2N])
+// receives the two products, which the backward pass needs.  bf16: one GEMM whose epilogue applies the activation
+// (two-CTA kernel for large M, few-row kernel for M <= 64 when gate_up_out is not wanted); otherwise GEMM + SwiGLU.
+extern "C" int b200_gemm_ffn(b200_ctx *ctx, const void *a, const void *w_gate_up, void *gate_up_out, void *c, size_t M,
+                             size_t N, size_t K, b200_dtype dt) {
+  B200_REQUIRE(ctx, a && w_gate_up && c, "gemm_ffn: null pointer");
+  if (M == 0 || N == 0) return B200_OK;
+  const size_t es = dtype_size(dt);
+  if (dt == B200_BF16 && K > 0 && gemm_tc_supported(a, w_gate_up, c, M, 2 * N, K, K, 2 * N, N, dt) && N % 8 == 0) {
+    GemmEpilogue epi;
+    epi.swiglu_I = (int)N;
+    if (!gate_up_out && ctx->gemm_skinny && gemm_skinny_supported(M, 0, 0, 0))
+      return b200_gemm_ld(ctx, a, w_gate_up, c, M, 2 * N, K, 0, 0, 0, dt, dt, K, 2 * N, N, &epi);
+    if (!(ctx->gemm_skinny && gemm_skinny_supported(M, 0, 0, 0)) && gemm_tc2_swiglu_eligible(ctx, M, N)) {
+      void *gu = gate_up_out ? gate_up_out : b200_scratch(ctx, M * 2 * N * es);
+      if (!gu) return B200_ERR_NOMEM;
+      epi.act_out = c; epi.ld_act = N;
+      return b200_gemm_ld(ctx, a, w_gate_up, gu, M, 2 * N, K, 0, 0, 0, dt, dt, K, 2 * N, 2 * N, &epi);
+    }
+  }
+  void *gu = gate_up_out ? gate_up_out : b200_scratch(ctx, M * 2 * N * es);
+  if (!gu) return B200_ERR_NOMEM;
+  int rc = b200_gemm_ld(ctx, a, w_gate_up, gu, M, 2 * N, K, 0, 0, 0, dt, dt, K, 2 * N, 2 * N);
+  if (rc) return rc;
+  return swiglu_fwd_strided(ctx, gu, (const char *)gu + N * es, c, M, N, 2 * N, N, dt);
 }
 
 // ------------------------------------------------------------- attention --

@@ -129,12 +129,19 @@ struct GemmEpilogue {
   const float *cos_t = nullptr, *sin_t = nullptr;
   int S = 0, hd = 0, cols = 0;
   const int *pos_dev = nullptr;   // few-row kernel only: every row is at token position *pos_dev (decode; read on the device so that a captured step can be replayed)
-  int swiglu_I = 0;     // few-row kernel only: W = [gate | up] (I columns each), C[M, I] = silu(A*gate) * (A*up)
+  // W = [gate | up] (I columns each).  Few-row kernel: C[M, I] = silu(A*gate) * (A*up) and nothing else is written.
+  // Two-CTA kernel (act_out set): C[M, 2I] = A*W as usual AND act_out[M, I] = silu(gate) * up computed from the
+  // bf16-rounded values that were just stored (what the separate SwiGLU kernel would read back).
+  int swiglu_I = 0;
+  void *act_out = nullptr;
+  size_t ld_act = 0;
 };
 int gemm_tc_launch(b200_ctx *ctx, const void *A, const void *B, void *C, size_t M, size_t N, size_t K, int ta, int tb,
                    int acc, b200_dtype out_dt, size_t lda, size_t ldb, size_t ldc, const GemmEpilogue *epi = nullptr);
 int gemm_tc2_launch(b200_ctx *ctx, const void *A, const void *B, void *C, size_t M, size_t N, size_t K, int ta, int tb,
                     int acc, b200_dtype out_dt, size_t lda, size_t ldb, size_t ldc, const GemmEpilogue *epi = nullptr);
+// true when b200_gemm_ld would run the two-CTA kernel with the fused SwiGLU output for this [M, 2I] forward GEMM
+bool gemm_tc2_swiglu_eligible(const b200_ctx *ctx, size_t M, size_t I);
 bool gemm_skinny_supported(size_t M, int ta, int tb, int acc);
 int gemm_skinny_launch(b200_ctx *ctx, const void *A, const void *W, void *C, size_t M, size_t N, size_t K, b200_dtype out_dt,
                        size_t lda, size_t ldb, size_t ldc, const GemmEpilogue *epi = nullptr);

@@ -145,7 +145,11 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   const uint32_t rank = cluster_ctarank();
   const bool leader = rank == 0;
   const int cluster_id = blockIdx.x >> 1, n_clusters = gridDim.x >> 1;
-  const int tiles_m = (M + 2 * BM - 1) / (2 * BM), tiles_n = (N + BN - 1) / BN, total = tiles_m * tiles_n;
+  // fused SwiGLU output: a tile is 128 gate columns (staged by the leader CTA) next to the matching 128 up columns
+  // (staged by its peer), so one accumulator row holds both values of 128 activation features
+  const bool swiglu = epi.swiglu_I > 0;
+  const int tiles_m = (M + 2 * BM - 1) / (2 * BM), tiles_n = swiglu ? (epi.swiglu_I + BN / 2 - 1) / (BN / 2) : (N + BN - 1) / BN,
+            total = tiles_m * tiles_n;
   const int num_kb = (K + BK - 1) / BK;
   const int items = total * splits;                 // work item = (tile pair, K split); all tiles of split 0 first
   volatile int *abort_flag = &sh->abort_flag;
@@ -182,7 +186,8 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         int tm, tn; tile_coords(it % total, tm, tn);
         const int sp = it / total, kb0 = sp * num_kb / splits, kb1 = (sp + 1) * num_kb / splits;
         const int m0 = tm * 2 * BM + (int)rank * BM;            // this CTA's rows
-        const int n0 = tn * BN + (int)rank * (BN / 2);          // this CTA's half of the B columns
+        const int n0 = swiglu ? tn * (BN / 2) + (int)rank * epi.swiglu_I       // gate columns | matching up columns
+                              : tn * BN + (int)rank * (BN / 2);              // this CTA's half of the B columns
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!tc::mbar_wait(&sh->empty[stage], phase ^ 1, status, abort_flag, 111)) { ok = false; break; }
           const uint32_t full_leader = tc::smem_u32(&sh->full[stage]) & LEADER_MASK;
@@ -234,7 +239,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       }
     }
   } else {
-    const int q = warp & 3;
+    const int q = warp & 3;                        // tensor-memory lane quarter this warp may read
     int acc = 0; uint32_t acc_phase = 0;
     bool ok = true;
     for (int it = cluster_id; it < items && ok; it += n_clusters) {
@@ -244,6 +249,45 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       const int row = tm * 2 * BM + (int)rank * BM + q * 32 + lane;
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN;
       TO *crow = C + (size_t)row * ldc;
+      if constexpr (sizeof(TO) == 2 && !ACC) {
+        if (swiglu) {
+          bf16 *arow = (bf16 *)epi.act_out + (size_t)row * epi.ld_act;
+#pragma unroll 1
+          for (int c = 0; c < BN / 64; ++c) {
+            uint32_t g[32], u[32];
+            tc::tmem_ld_32x32(taddr + c * 32, g);
+            tc::tmem_ld_32x32(taddr + BN / 2 + c * 32, u);
+            tc::tmem_ld_wait();
+            const int col = tn * (BN / 2) + c * 32;
+            if (row < M && col < epi.swiglu_I) {
+#pragma unroll
+              for (int v = 0; v < 4; ++v) {
+                uint4 og, ou, oa;
+                uint32_t *pg = &og.x, *pu = &ou.x, *pa = &oa.x;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  const __nv_bfloat162 hg = __floats2bfloat162_rn(__uint_as_float(g[v * 8 + 2 * j]), __uint_as_float(g[v * 8 + 2 * j + 1]));
+                  const __nv_bfloat162 hu = __floats2bfloat162_rn(__uint_as_float(u[v * 8 + 2 * j]), __uint_as_float(u[v * 8 + 2 * j + 1]));
+                  const float2 gf = __bfloat1622float2(hg), uf = __bfloat1622float2(hu);
+                  const float s0 = 1.0f / (1.0f + __expf(-gf.x)), s1 = 1.0f / (1.0f + __expf(-gf.y));
+                  const __nv_bfloat162 ha = __floats2bfloat162_rn(gf.x * s0 * uf.x, gf.y * s1 * uf.y);
+                  pg[j] = *reinterpret_cast<const uint32_t *>(&hg);
+                  pu[j] = *reinterpret_cast<const uint32_t *>(&hu);
+                  pa[j] = *reinterpret_cast<const uint32_t *>(&ha);
+                }
+                *reinterpret_cast<uint4 *>(crow + col + v * 8) = og;
+                *reinterpret_cast<uint4 *>(crow + epi.swiglu_I + col + v * 8) = ou;
+                *reinterpret_cast<uint4 *>(arow + col + v * 8) = oa;
+              }
+            }
+          }
+          tc::tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive_cluster(tc::smem_u32(&sh->acc_empty[acc]) & LEADER_MASK);
+          if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+          continue;
+        }
+      }
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t r[32];
@@ -287,7 +331,7 @@ int launch_variant(b200_ctx *ctx, const CUtensorMap &ma, const CUtensorMap &mb, 
     max_clusters = n;
     attr_set = true;
   }
-  const int pairs = ((M + 2 * BM - 1) / (2 * BM)) * ((N + BN - 1) / BN);
+  const int pairs = ((M + 2 * BM - 1) / (2 * BM)) * (epi.swiglu_I > 0 ? (epi.swiglu_I + BN / 2 - 1) / (BN / 2) : (N + BN - 1) / BN);
   // Split K (fp32 output only: partial tiles are added with vector reductions) when whole tile pairs fill the
   // SM pairs badly -- the weight-gradient GEMMs have few tiles and a 16384-deep K.
   int splits = 1;
@@ -328,7 +372,12 @@ int gemm_tc2_launch(b200_ctx *ctx, const void *A, const void *B, void *C, size_t
                     int acc, b200_dtype out_dt, size_t lda, size_t ldb, size_t ldc, const GemmEpilogue *epi_in) {
   B200_REQUIRE(ctx, !(acc && out_dt == B200_BF16), "gemm: accumulate needs an fp32 C on the tensor-core path");
   GemmEpilogue epi;
-  if (epi_in) {
+  if (epi_in && epi_in->swiglu_I > 0) {
+    epi = *epi_in;
+    B200_REQUIRE(ctx, out_dt == B200_BF16 && !acc && !ta && !tb && !epi.cos_t && epi.act_out && (size_t)epi.swiglu_I * 2 == N &&
+                 epi.swiglu_I % 32 == 0 && (epi.ld_act * 2) % 16 == 0 && (uintptr_t)epi.act_out % 16 == 0,
+                 "gemm: the fused SwiGLU output needs a bf16 forward GEMM on W = [gate | up] with I a multiple of 32");
+  } else if (epi_in) {
     epi = *epi_in;
     B200_REQUIRE(ctx, out_dt == B200_BF16 && epi.cos_t && epi.sin_t && epi.S > 0 && epi.hd % 32 == 0 && epi.cols % 32 == 0 &&
                  ((uintptr_t)epi.cos_t | (uintptr_t)epi.sin_t) % 16 == 0, "gemm: unsupported fused rotary epilogue");
@@ -347,4 +396,9 @@ int gemm_tc2_launch(b200_ctx *ctx, const void *A, const void *B, void *C, size_t
   if (a_mn && !b_mn) return launch_out<true, false>(ctx, ma, mb, C, m, n, k, ldc, out_dt, acc, epi);
   if (!a_mn && b_mn) return launch_out<false, true>(ctx, ma, mb, C, m, n, k, ldc, out_dt, acc, epi);
   return launch_out<false, false>(ctx, ma, mb, C, m, n, k, ldc, out_dt, acc, epi);
+}
+
+bool gemm_tc2_swiglu_eligible(const b200_ctx *ctx, size_t M, size_t I) {
+  const size_t pairs = ((M + 2 * BM - 1) / (2 * BM)) * ((I + BN / 2 - 1) / (BN / 2));
+  return ctx->gemm_2cta && I % 32 == 0 && pairs >= (size_t)ctx->sm_count / 4;
 }

@@ -116,3 +116,25 @@ def test_full_size_projection_shapes(ctx, name, K, N):
     dw = ctx.gemm(x, dy, K, N, M, True, False, out_dtype="f32").download()       # wgrad    TN
     cols = rng.choice(N, 16, replace=False)
     assert rel(dw[:, cols], hx.astype(np.float64).T @ hdy[:, cols].astype(np.float64)) < 1e-4
+
+
+@pytest.mark.parametrize("M,I,K,want", [(4096, 1024, 512, True), (4096, 1024, 512, False), (2560, 2080, 200, True),
+                                         (32, 1024, 512, False), (7, 96, 64, False), (32, 1024, 512, True), (300, 96, 64, True)])
+def test_ffn_gemm_with_the_activation_in_the_epilogue(ctx, M, I, K, want):
+    """silu(x Wg) * (x Wu) on W = [gate | up]: two-CTA kernel (large M), few-row kernel (M <= 64, products not
+    wanted) and the GEMM + SwiGLU pair must agree; gate/up products equal the plain GEMM's bit for bit."""
+    x = synth.bf16_round(synth.normal(SEED, f"ffnx{M}{K}", (M, K)))
+    w = synth.bf16_round(synth.normal(SEED, f"ffnw{K}{I}", (K, 2 * I), 0.05))
+    dx, dw = ctx.array(x, "bf16"), ctx.array(w, "bf16")
+    res = ctx.gemm_ffn(dx, dw, M, I, K, want_gate_up=want)
+    act = (res[0] if want else res).download()
+    plain = ctx.gemm(dx, dw, M, 2 * I, K, out_dtype="bf16").download()
+    g, u = plain[:, :I].astype(np.float32), plain[:, I:].astype(np.float32)
+    ref_act = synth.bf16_round(g / (1.0 + np.exp(-g)) * u)
+    if want:
+        np.testing.assert_array_equal(res[1].download(), plain)
+        assert rel(act, ref_act) < 4e-3                     # same bf16 inputs; device exp differs in the last ulp
+    else:
+        exact = x.astype(np.float64) @ w.astype(np.float64)
+        ge, ue = exact[:, :I], exact[:, I:]
+        assert rel(act, ge / (1.0 + np.exp(-ge)) * ue) < 8e-3

@@ -103,8 +103,10 @@ def test_fp32_single_layer_forward_backward(ctx, orc, cfgd):
 
 
 @pytest.mark.parametrize("cfgd", [dict(B=2, S=128, H=256, I=688, nH=8, nKV=2, hd=32, V=4096, L=2),
-                                  dict(B=2, S=256, H=512, I=1024, nH=4, nKV=2, hd=128, V=2048, L=2)],
-                         ids=["hd32", "hd128"])
+                                  dict(B=2, S=256, H=512, I=1024, nH=4, nKV=2, hd=128, V=2048, L=2),
+                                  # enough 256x256 tile pairs for the two-CTA GEMM with the SwiGLU epilogues (forward and backward)
+                                  dict(B=2, S=1024, H=256, I=1280, nH=2, nKV=1, hd=128, V=1024, L=1)],
+                         ids=["hd32", "hd128", "two_cta_fused_swiglu"])
 def test_bf16_model_against_fp32_checker(ctx, orc, cfgd):
     cfg = oracle.Config(**cfgd)
     params, tok, tgt = inputs(cfg, seed=9)
@@ -127,6 +129,15 @@ def test_bf16_model_against_fp32_checker(ctx, orc, cfgd):
             n = int(np.prod(shp))
             sl = slice(e + l * lp + off, e + l * lp + off + n)
             assert rel(grads[sl], grads_ref[sl]) < BF16_TOL, (l, k, rel(grads[sl], grads_ref[sl]))
+    # the same step with the single-CTA GEMM forced: no fused SwiGLU epilogues, separate kernels instead
+    ctx.lib.b200_internal_set_gemm_2cta.argtypes = [bridge._vp, bridge._i]
+    ctx.lib.b200_internal_set_gemm_2cta(ctx.h, 0)
+    try:
+        loss1 = model.loss_and_grads_host(tok, tgt)
+        grads1 = model.read_grads()
+    finally:
+        ctx.lib.b200_internal_set_gemm_2cta(ctx.h, 1)
+    assert abs(loss1 - loss) < 1e-4 * abs(loss) and rel(grads1, grads) < 2e-3
     model.close()
 
 
