@@ -121,5 +121,8 @@ def test_optimizer_in_backward_order_gives_the_same_update(ctx, monkeypatch):
         m.close()
     (l0, p0, (m0, v0, s0)), (l1, p1, (m1, v1, s1)) = results
     assert s0 == s1 == 4
-    np.testing.assert_allclose(l0, l1, rtol=1e-5)
-    assert rel(p1, p0) < 1e-6 and rel(m1, m0) < 1e-5 and rel(v1, v0) < 1e-5
+    # gradients are not bit-reproducible between runs (fp32 atomics in the embedding and attention gradients) and AdamW
+    # normalises them, so near-zero gradients can move a weight by a fraction of lr; a bucket that missed or doubled an
+    # update would differ by ~1e-1 here
+    np.testing.assert_allclose(l0, l1, rtol=1e-3)
+    assert rel(p1, p0) < 1e-3 and rel(m1, m0) < 1e-3 and rel(v1, v0) < 1e-3
