@@ -75,7 +75,7 @@ def test_interrupted_and_resumed_run_equals_the_uninterrupted_one(ctx, tmp_path,
     parts_params, parts_rows = m.read_params(), rows(cfg("parts").metrics_filepath)
     m.close()
     assert [int(r["step"]) for r in parts_rows] == list(range(9))
-    tol = 1e-5 if dtype == "f32" else 2e-3      # bf16: the resumed run rebuilds its bf16 weights from the fp32 masters
+    tol = 2e-4 if dtype == "f32" else 2e-3      # atomically accumulated gradients are not bit-reproducible and AdamW amplifies the noise; a wrong resume is off by >1e-2
     assert rel(parts_params, whole_params) < tol
     np.testing.assert_allclose([float(r["train_loss"]) for r in parts_rows], [float(r["train_loss"]) for r in whole_rows], rtol=10 * tol)
 
