@@ -30,6 +30,9 @@ struct b200_ctx {
   // 1: large bf16 GEMMs use the two-CTA (cta_group::2) kernel; 0: always the single-CTA kernel
   int gemm_2cta = 1;
   int gemm_skinny = 1;
+  // decode step: kernels are launched with programmatic stream serialization, so a kernel's launch and set-up overlap the
+  // tail of the one before it; each such kernel waits (griddepcontrol.wait) before it touches anything a predecessor wrote
+  bool pdl = false;
   bool time_gemm = false;
   struct Timed { cudaEvent_t start, stop; double flops; };
   std::vector<Timed> timed;
@@ -65,6 +68,12 @@ void *b200_scratch(b200_ctx *ctx, size_t bytes);
 static inline size_t dtype_size(b200_dtype d) { return d == B200_BF16 ? 2 : 4; }
 
 // ---- device helpers ------------------------------------------------------
+// Programmatic dependent launch.  Both are no-ops in a kernel launched without the attribute.  pdl_wait() returns once
+// every kernel this one depends on has completed and its writes are visible; nothing written by a predecessor may be
+// read, and nothing a predecessor reads may be written, before it.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 __device__ __forceinline__ float to_f(float v) { return v; }
 __device__ __forceinline__ float to_f(bf16 v) { return __bfloat162float(v); }
 template <class T> __device__ __forceinline__ T from_f(float v);
@@ -169,3 +178,20 @@ int attn_bwd_launch(b200_ctx *ctx, const void *Q, const void *K, const void *V, 
 bool attn_bwd_fuses_rope(size_t B, size_t nH, size_t nKV, size_t S, size_t hd, const AttnStrides &st,
                          const AttnStrides &gst, b200_dtype dt, const void *Q, const void *K, const void *V,
                          const void *O, const void *dO, const void *dQ, const void *dK, const void *dV);
+
+// Kernel launch on the context's stream; with ctx->pdl the launch carries the programmatic-stream-serialization
+// attribute (the kernel must then call pdl_wait() before its first dependent access).  cluster_x > 1 adds a cluster.
+template <class... KArgs, class... Args>
+inline cudaError_t launch_k(b200_ctx *ctx, void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, int cluster_x, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = ctx->stream;
+  cudaLaunchAttribute at[2];
+  int n = 0;
+  if (cluster_x > 0) {
+    at[n].id = cudaLaunchAttributeClusterDimension;
+    at[n].val.clusterDim.x = (unsigned)cluster_x; at[n].val.clusterDim.y = 1; at[n].val.clusterDim.z = 1; ++n;
+  }
+  if (ctx->pdl) { at[n].id = cudaLaunchAttributeProgrammaticStreamSerialization; at[n].val.programmaticStreamSerializationAllowed = 1; ++n; }
+  cfg.attrs = at; cfg.numAttrs = (unsigned)n;
+  return cudaLaunchKernelEx(&cfg, kern, args...);
+}

@@ -50,13 +50,15 @@ template <class T, int EPL, int GQ>
 __global__ void __launch_bounds__(WARPS * 32)
 attn_decode_kernel(DecodeAttnArgs a) {
   constexpr int HD = EPL * 32;
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float s_o[WARPS][GQ][HD];
   __shared__ float s_m[WARPS][GQ], s_l[WARPS][GQ];
   __shared__ int s_last;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int split = blockIdx.x, nsplit = gridDim.x, grp = blockIdx.y, b = blockIdx.z;
   const int G = a.nH / a.nKV, h0 = grp * GQ, kvh = h0 / G, KV = a.nKV * HD;
-  const int t_len = a.pos_dev ? __ldg(a.pos_dev) + 1 : a.t_len;
+  const int t_len = a.pos_dev ? *a.pos_dev + 1 : a.t_len;      // plain load: written by the previous step's last kernel
   const int k0 = split * a.chunk, k1 = min(t_len, k0 + a.chunk);
   const T *q = (const T *)a.q + (size_t)b * a.ldq + (size_t)h0 * HD + lane * EPL;
   T *kc = (T *)a.kc + (size_t)b * a.S_max * KV + (size_t)kvh * HD + lane * EPL;
@@ -213,11 +215,11 @@ template <class T, int EPL>
 int launch_gq(b200_ctx *ctx, const DecodeAttnArgs &a, int gq, dim3 grid) {
   switch (gq) {
     case 8:
-      if constexpr (EPL < 8) { attn_decode_kernel<T, EPL, 8><<<grid, WARPS * 32, 0, ctx->stream>>>(a); break; }
+      if constexpr (EPL < 8) { B200_CUDA(ctx, launch_k(ctx, attn_decode_kernel<T, EPL, 8>, grid, dim3(WARPS * 32), 0, 0, a)); break; }
       else return b200_fail(ctx, B200_ERR_INVALID, "attn_decode: 8 heads of dimension 256 per CTA exceed shared memory");
-    case 4: attn_decode_kernel<T, EPL, 4><<<grid, WARPS * 32, 0, ctx->stream>>>(a); break;
-    case 2: attn_decode_kernel<T, EPL, 2><<<grid, WARPS * 32, 0, ctx->stream>>>(a); break;
-    default: attn_decode_kernel<T, EPL, 1><<<grid, WARPS * 32, 0, ctx->stream>>>(a); break;
+    case 4: B200_CUDA(ctx, launch_k(ctx, attn_decode_kernel<T, EPL, 4>, grid, dim3(WARPS * 32), 0, 0, a)); break;
+    case 2: B200_CUDA(ctx, launch_k(ctx, attn_decode_kernel<T, EPL, 2>, grid, dim3(WARPS * 32), 0, 0, a)); break;
+    default: B200_CUDA(ctx, launch_k(ctx, attn_decode_kernel<T, EPL, 1>, grid, dim3(WARPS * 32), 0, 0, a)); break;
   }
   B200_LAUNCHED(ctx);
   return B200_OK;
@@ -258,7 +260,8 @@ int attn_decode(b200_ctx *ctx, const void *q, const void *k_new, const void *v_n
   a.scale = 1.0f / sqrtf((float)hd);
   // key runs: one wave of CTAs (two fit per SM), at least 4 keys per warp, at most 16 splits
   const size_t groups = B * (nH / gq);
-  size_t want = (2 * (size_t)ctx->sm_count + groups - 1) / groups;
+  size_t want = (2 * (size_t)ctx->sm_count) / groups;        // rounded down: one full wave, never a second, mostly empty one
+  if (want < 1) want = 1;
   if (want > (size_t)ATTN_DECODE_MAX_SPLITS) want = ATTN_DECODE_MAX_SPLITS;
   size_t chunk = (t_len + want - 1) / want;
   if (chunk < 32) chunk = 32;

@@ -580,6 +580,8 @@ extern "C" int b200_reshape_to_3d(b200_ctx *ctx, const void *src, void *dst, siz
 template <class T>
 __global__ void embedding_fwd_kernel(const uint32_t *__restrict__ ids, const T *__restrict__ table,
                                      T *__restrict__ out, size_t tokens, size_t H, size_t V, int *status) {
+  pdl_launch_dependents();
+  pdl_wait();
   for (size_t t = blockIdx.x; t < tokens; t += gridDim.x) {
     uint32_t id = ids[t];
     if (id >= V) { if (threadIdx.x == 0) atomicExch(status, 2); id = (uint32_t)(V - 1); }  // reference throws (Transformer.cpp:127-129)
@@ -600,8 +602,8 @@ extern "C" int b200_embedding_forward(b200_ctx *ctx, const uint32_t *ids, const 
   B200_REQUIRE(ctx, ids && table && out && H && V, "embedding_forward: bad arguments");
   if (!tokens) return B200_OK;
   int grid = (int)(tokens < (size_t)ctx->sm_count * 16 ? tokens : (size_t)ctx->sm_count * 16);
-  if (dt == B200_BF16) embedding_fwd_kernel<bf16><<<grid, 256, 0, ctx->stream>>>(ids, (const bf16 *)table, (bf16 *)out, tokens, H, V, ctx->dev_status);
-  else embedding_fwd_kernel<float><<<grid, 256, 0, ctx->stream>>>(ids, (const float *)table, (float *)out, tokens, H, V, ctx->dev_status);
+  if (dt == B200_BF16) B200_CUDA(ctx, launch_k(ctx, embedding_fwd_kernel<bf16>, dim3(grid), dim3(256), 0, 0, ids, (const bf16 *)table, (bf16 *)out, tokens, H, V, ctx->dev_status));
+  else B200_CUDA(ctx, launch_k(ctx, embedding_fwd_kernel<float>, dim3(grid), dim3(256), 0, 0, ids, (const float *)table, (float *)out, tokens, H, V, ctx->dev_status));
   B200_LAUNCHED(ctx);
   return B200_OK;
 }

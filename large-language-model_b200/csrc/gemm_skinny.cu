@@ -81,14 +81,24 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   const uint32_t tmem_base = sh->tmem_base;
   if (split > 1) cluster_sync_all();            // every CTA of the cluster is resident before remote stores
 
+  pdl_launch_dependents();
   if (warp == 0 && lane == 0) {
-    int stage = 0; uint32_t phase = 0;
-    for (int kb = kb_lo; kb < kb_hi; ++kb) {
-      if (!tc::mbar_wait(&sh->empty[stage], phase ^ 1, status, abort_flag, 401)) break;
+    // The weight tiles do not depend on the kernel before this one: the first ring of them is requested before waiting
+    // for it (programmatic dependent launch), the activation rows only after.
+    const int n_early = min(kb_hi - kb_lo, STAGES);
+    auto load_w = [&](int stage, int kb) {
       tc::mbar_expect_tx(&sh->full[stage], W_STAGE_BYTES + a_stage_bytes(NT));
       uint8_t *w = sW + stage * W_STAGE_BYTES;
       tc::tma_load_2d(w, &map_w, n0, kb * BK, &sh->full[stage]);
       tc::tma_load_2d(w + CHUNK_BYTES, &map_w, swiglu ? epi.swiglu_I + n0 : n0 + 64, kb * BK, &sh->full[stage]);
+    };
+    for (int i = 0; i < n_early; ++i) load_w(i, kb_lo + i);
+    pdl_wait();
+    for (int i = 0; i < n_early; ++i) tc::tma_load_2d(sA + i * a_stage_bytes(NT), &map_a, (kb_lo + i) * BK, 0, &sh->full[i]);
+    int stage = n_early == STAGES ? 0 : n_early; uint32_t phase = n_early == STAGES ? 1 : 0;
+    for (int kb = kb_lo + n_early; kb < kb_hi; ++kb) {
+      if (!tc::mbar_wait(&sh->empty[stage], phase ^ 1, status, abort_flag, 401)) break;
+      load_w(stage, kb);
       tc::tma_load_2d(sA + stage * a_stage_bytes(NT), &map_a, kb * BK, 0, &sh->full[stage]);
       if (++stage == STAGES) { stage = 0; phase ^= 1; }
     }
@@ -112,6 +122,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     if (ok) tc::umma_commit(&sh->acc_full);
   }
   __syncwarp();
+  pdl_wait();                                   // before any global store (and for the threads that did not load)
 
   // ---- epilogue: tensor memory -> the owning CTA's shared memory ------------------------------
   const int NL = FT / split;                    // features owned per CTA
@@ -175,7 +186,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         x0 += v.x; x1 += v.y;
       }
       if (epi.cos_t != nullptr && n < epi.cols) {
-        const int prow = epi.pos_dev ? __ldg(epi.pos_dev) : m % epi.S;
+        const int prow = epi.pos_dev ? *epi.pos_dev : m % epi.S;
         const size_t tab = (size_t)prow * (epi.hd >> 1) + ((n % epi.hd) >> 1);
         const float cv = __ldg(epi.cos_t + tab), sv = __ldg(epi.sin_t + tab);
         const float y0 = x0 * cv - x1 * sv, y1 = x0 * sv + x1 * cv;
@@ -206,18 +217,8 @@ int launch(b200_ctx *ctx, const CUtensorMap &mw, const CUtensorMap &ma, void *C,
     B200_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(NT)));
     attr_set = true;
   }
-  cudaLaunchConfig_t cfg = {};
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = split; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
   const int ft = epi.swiglu_I > 0 ? FT / 2 : FT;
-  cfg.gridDim = dim3(((N + ft - 1) / ft) * split);
-  cfg.blockDim = dim3(THREADS);
-  cfg.dynamicSmemBytes = smem_bytes(NT);
-  cfg.stream = ctx->stream;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  B200_CUDA(ctx, cudaLaunchKernelEx(&cfg, kern, mw, ma, (TO *)C, M, N, K, ldc, split, ctx->dev_status, epi));
+  B200_CUDA(ctx, launch_k(ctx, kern, dim3(((N + ft - 1) / ft) * split), dim3(THREADS), (size_t)smem_bytes(NT), split, mw, ma, (TO *)C, M, N, K, ldc, split, ctx->dev_status, epi));
   B200_LAUNCHED(ctx);
   return B200_OK;
 }

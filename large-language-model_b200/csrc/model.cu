@@ -768,7 +768,20 @@ static int layer_decode_core(b200_model *m, size_t l, const void *h_in, size_t B
   return B200_OK;
 }
 
+static int decode_step_impl(b200_model *m, const int32_t *tok, size_t B, size_t pos, void *logits, const int *pos_dev);
+// Every kernel of a decode step supports programmatic dependent launch (it waits before its first dependent access), so
+// the step is enqueued with that launch attribute: each kernel's launch and set-up, and the weight prefetch of the
+// few-row GEMMs, overlap the tail of the kernel before.  B200_DECODE_PDL=0 turns it off.
 static int decode_step_core(b200_model *m, const int32_t *tok, size_t B, size_t pos, void *logits, const int *pos_dev) {
+  b200_ctx *ctx = m->ctx;
+  const char *env = getenv("B200_DECODE_PDL");
+  const bool keep = ctx->pdl;
+  ctx->pdl = !(env && env[0] == '0') && m->dt == B200_BF16 && ctx->gemm_skinny && gemm_skinny_supported(B, 0, 0, 0);
+  const int rc = decode_step_impl(m, tok, B, pos, logits, pos_dev);
+  ctx->pdl = keep;
+  return rc;
+}
+static int decode_step_impl(b200_model *m, const int32_t *tok, size_t B, size_t pos, void *logits, const int *pos_dev) {
   b200_ctx *ctx = m->ctx;
   B200_REQUIRE(ctx, tok && logits && B > 0 && B <= m->cache_batch && pos < m->cache_len, "decode_step: bad arguments");
   const size_t H = m->H;
@@ -843,8 +856,11 @@ extern "C" int b200_model_generate(b200_model *m, const int32_t *host_prompt, si
       if (cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal) != cudaSuccess) { cudaGetLastError(); --t; continue; }
     }
     rc = decode_step_core(m, m->dec_next, B, P + t - 1, m->dec_logits, pos_dev);
+    const bool pdl_keep = ctx->pdl;
+    ctx->pdl = pos_dev != nullptr && !(getenv("B200_DECODE_PDL") && getenv("B200_DECODE_PDL")[0] == '0');
     if (!rc) rc = sample_launch(ctx, m->dec_logits, m->dt, B, m->V, m->dec_history, P + t, ld, 1, cfg, P + t, m->dec_next, nullptr, nullptr, pos_dev);
     if (!rc && pos_dev) rc = advance_pos(ctx, m->dec_pos);
+    ctx->pdl = pdl_keep;
     if (capturing) {
       cudaGraph_t graph = nullptr;
       const cudaError_t ce = cudaStreamEndCapture(ctx->stream, &graph);

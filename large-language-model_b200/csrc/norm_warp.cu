@@ -15,6 +15,8 @@ rms_fwd_warp_kernel(const T *x, T *h_out, const T *__restrict__ r, const T *__re
                     float *__restrict__ rstd_out, float eps, size_t rows, int D, const T *__restrict__ w2,
                     T *__restrict__ y2) {
   constexpr int N = Vec16<T>::N;
+  pdl_launch_dependents();
+  pdl_wait();
   const int lane = threadIdx.x & 31;
   const size_t warp_global = (size_t)blockIdx.x * WARPS_PER_CTA + (threadIdx.x >> 5);
   const size_t n_warps = (size_t)gridDim.x * WARPS_PER_CTA;
@@ -165,7 +167,7 @@ int rms_fwd_warp(b200_ctx *ctx, const void *x, void *h, const void *r, const voi
   if (D % (32 * N) || !aligned16({x, h, r, w, y, w2, y2})) return 0;
   const int vpl = (int)(D / (32 * N));
   const int grid = warp_grid(ctx, rows);
-#define FW(V, A) rms_fwd_warp_kernel<T, V, A><<<grid, WARPS_PER_CTA * 32, 0, ctx->stream>>>((const T *)x, (T *)h, (const T *)r, (const T *)w, (T *)y, rstd, eps, rows, (int)D, (const T *)w2, (T *)y2)
+#define FW(V, A) launch_k(ctx, rms_fwd_warp_kernel<T, V, A>, dim3(grid), dim3(WARPS_PER_CTA * 32), 0, 0, (const T *)x, (T *)h, (const T *)r, (const T *)w, (T *)y, rstd, eps, rows, (int)D, (const T *)w2, (T *)y2)
   switch (vpl) {
     case 1: if (add) FW(1, true); else FW(1, false); break;
     case 2: if (add) FW(2, true); else FW(2, false); break;

@@ -135,7 +135,9 @@ template <class T>
 __global__ void __launch_bounds__(THREADS)
 sample_kernel(const T *__restrict__ logits, int32_t *history, int32_t *__restrict__ out_tokens,
               float *__restrict__ out_threshold, int32_t *__restrict__ out_kept, SamplerArgs a, int append) {
-  if (a.pos_dev) { a.hist_len = __ldg(a.pos_dev) + 1; a.step = (uint64_t)a.hist_len; }
+  pdl_launch_dependents();
+  pdl_wait();
+  if (a.pos_dev) { a.hist_len = *a.pos_dev + 1; a.step = (uint64_t)a.hist_len; }
   extern __shared__ float keys[];                  // V penalised logits
   __shared__ Scratch sc;
   __shared__ int recent[WINDOW];
@@ -243,11 +245,15 @@ sample_kernel(const T *__restrict__ logits, int32_t *history, int32_t *__restric
   }
 }
 
-__global__ void advance_pos_kernel(int *pos) { *pos += 1; }
+__global__ void advance_pos_kernel(int *pos) {
+  pdl_launch_dependents();
+  pdl_wait();
+  *pos += 1;
+}
 }  // namespace
 
 int advance_pos(b200_ctx *ctx, int *pos) {
-  advance_pos_kernel<<<1, 1, 0, ctx->stream>>>(pos);
+  B200_CUDA(ctx, launch_k(ctx, advance_pos_kernel, dim3(1), dim3(1), 0, 0, pos));
   B200_LAUNCHED(ctx);
   return B200_OK;
 }
@@ -270,10 +276,10 @@ int sample_launch(b200_ctx *ctx, const void *logits, b200_dtype dt, size_t batch
   const size_t smem = (size_t)MAX_V * sizeof(float);
   if (dt == B200_BF16) {
     if (!attr[1]) { B200_CUDA(ctx, cudaFuncSetAttribute(sample_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); attr[1] = true; }
-    sample_kernel<bf16><<<(unsigned)batch, THREADS, smem, ctx->stream>>>((const bf16 *)logits, history, out_tokens, out_threshold, out_kept, a, append);
+    B200_CUDA(ctx, launch_k(ctx, sample_kernel<bf16>, dim3((unsigned)batch), dim3(THREADS), smem, 0, (const bf16 *)logits, history, out_tokens, out_threshold, out_kept, a, append));
   } else {
     if (!attr[0]) { B200_CUDA(ctx, cudaFuncSetAttribute(sample_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); attr[0] = true; }
-    sample_kernel<float><<<(unsigned)batch, THREADS, smem, ctx->stream>>>((const float *)logits, history, out_tokens, out_threshold, out_kept, a, append);
+    B200_CUDA(ctx, launch_k(ctx, sample_kernel<float>, dim3((unsigned)batch), dim3(THREADS), smem, 0, (const float *)logits, history, out_tokens, out_threshold, out_kept, a, append));
   }
   B200_LAUNCHED(ctx);
   return B200_OK;
