@@ -35,6 +35,40 @@ template <class T, int EPL> struct RowLoad {
   }
 };
 
+// Sums each of NV per-lane values over the 32 lanes and leaves every total in every lane.  Instead of NV butterflies
+// (5 NV shuffles) the values are folded: at each step a lane keeps half of its values and hands the other half to its
+// partner, so the totals end up spread over the lanes (NV - 1 + a few shuffles), then each is broadcast (NV shuffles).
+template <int NV>
+__device__ __forceinline__ void warp_sum_all(float (&v)[NV], int lane) {
+  static_assert(NV == 1 || NV == 2 || NV == 4 || NV == 8 || NV == 16 || NV == 32, "value count must be a power of two");
+  float w[NV];
+#pragma unroll
+  for (int i = 0; i < NV; ++i) w[i] = v[i];
+  int n = NV;
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) {
+    if (n > 1) {
+      const bool up = (lane & off) != 0;
+#pragma unroll
+      for (int i = 0; i < NV / 2; ++i) {
+        if (i < n / 2) {
+          const float a = w[2 * i], b = w[2 * i + 1];
+          w[i] = (up ? b : a) + __shfl_xor_sync(0xffffffffu, up ? a : b, off);
+        }
+      }
+      n >>= 1;
+    } else {
+      w[0] += __shfl_xor_sync(0xffffffffu, w[0], off);
+    }
+  }
+  // the total of value t sits in the lanes whose bits 4,3,2,... spell t's bits 0,1,2,...
+#pragma unroll
+  for (int t = 0; t < NV; ++t) {
+    const int src = ((t & 1) << 4) | ((t & 2) << 2) | (t & 4) | ((t & 8) >> 2) | ((t & 16) >> 4);
+    v[t] = __shfl_sync(0xffffffffu, w[0], src);
+  }
+}
+
 struct DecodeAttnArgs {
   const void *q, *k_new, *v_new;     // rows of the fused projection output (row stride ldq elements)
   void *kc, *vc, *o;                 // caches [B, S_max, nKV*hd]; output [B, ldo]
@@ -101,7 +135,7 @@ attn_decode_kernel(DecodeAttnArgs a) {
         if (ji == t_len - 1) { RowLoad<T, EPL>::stg(kc + (size_t)ji * KV, kr[i]); RowLoad<T, EPL>::stg(vc + (size_t)ji * KV, vr[i]); }
       }
     }
-    float s[KB][GQ];
+    float sv[KB * GQ];
 #pragma unroll
     for (int i = 0; i < KB; ++i) {
       float kf[EPL];
@@ -111,16 +145,15 @@ attn_decode_kernel(DecodeAttnArgs a) {
         float d = 0.f;
 #pragma unroll
         for (int e = 0; e < EPL; ++e) d += qf[g][e] * kf[e];
-        s[i][g] = d;
+        sv[i * GQ + g] = d;
       }
     }
+    warp_sum_all<KB * GQ>(sv, lane);
+    float s[KB][GQ];
 #pragma unroll
-    for (int off = 16; off > 0; off >>= 1) {
+    for (int i = 0; i < KB; ++i) {
 #pragma unroll
-      for (int i = 0; i < KB; ++i) {
-#pragma unroll
-        for (int g = 0; g < GQ; ++g) s[i][g] += __shfl_xor_sync(0xffffffffu, s[i][g], off);
-      }
+      for (int g = 0; g < GQ; ++g) s[i][g] = sv[i * GQ + g];
     }
     float corr[GQ];
 #pragma unroll
