@@ -9,7 +9,8 @@
 //   dimension (coalesced row reads), scores are reduced with shuffles and folded into an online softmax.
 //   Warps merge through shared memory, splits merge through a small fp32 workspace: the CTA that
 //   arrives last at a per-(sequence, group) ticket does the final merge (no waiting anywhere).
-// The new token's K/V row is taken from the projection output and appended to the cache here.
+// The new token's K/V row is taken from the projection output and appended to the cache here (when the query heads of a
+// KV head share a CTA; otherwise the caller appends it first).
 #include "common.cuh"
 
 namespace {
@@ -107,19 +108,27 @@ attn_decode_kernel(DecodeAttnArgs a) {
     for (int e = 0; e < EPL; ++e) { qf[g][e] *= a.scale; acc[g][e] = 0.f; }
   }
   constexpr int KB = 4;                            // keys per warp step
-  const bool fused_append = a.k_new != nullptr;
-  const T *k_new = (const T *)a.k_new + (size_t)b * a.ldq + (size_t)kvh * HD + lane * EPL;
-  const T *v_new = (const T *)a.v_new + (size_t)b * a.ldq + (size_t)kvh * HD + lane * EPL;
   typedef typename RowLoad<T, EPL>::Raw Raw;
+  // The token being decoded: its K/V rows come from the projection output and are appended to the cache by the CTA whose
+  // key run holds the last position, before that CTA reads them back (the host passes k_new only when one CTA serves all
+  // query heads of the KV head, so nobody else reads that cache row in this launch).
+  if (a.k_new != nullptr && k0 <= t_len - 1 && t_len - 1 < k1) {
+    if (warp == 0) {
+      const size_t src = (size_t)b * a.ldq + (size_t)kvh * HD + lane * EPL, dst = (size_t)(t_len - 1) * KV;
+      RowLoad<T, EPL>::stg(kc + dst, RowLoad<T, EPL>::ldg((const T *)a.k_new + src));
+      RowLoad<T, EPL>::stg(vc + dst, RowLoad<T, EPL>::ldg((const T *)a.v_new + src));
+    }
+    __syncthreads();
+  }
   // Raw loads of the KB rows of one step, branch-free (rows past the run re-read the step's first row and are masked in
   // the softmax).  The next step's rows are requested before this step's maths, so two steps of rows are in flight.
   auto load_rows = [&](int j, Raw *kr, Raw *vr) {
 #pragma unroll
     for (int i = 0; i < KB; ++i) {
-      const int ji = j + i * WARPS, jc = ji < k1 ? ji : j;
-      const bool from_proj = fused_append && jc == t_len - 1;      // the token being decoded: rows of the projection output
-      kr[i] = RowLoad<T, EPL>::ldg(from_proj ? k_new : kc + (size_t)jc * KV);
-      vr[i] = RowLoad<T, EPL>::ldg(from_proj ? v_new : vc + (size_t)jc * KV);
+      const int ji = j + i * WARPS;
+      const size_t off = (size_t)(ji < k1 ? ji : j) * KV;
+      kr[i] = RowLoad<T, EPL>::ldg(kc + off);
+      vr[i] = RowLoad<T, EPL>::ldg(vc + off);
     }
   };
   Raw kr[KB], vr[KB];
@@ -128,13 +137,6 @@ attn_decode_kernel(DecodeAttnArgs a) {
     Raw kn[KB], vn[KB];
     const int jn = j + WARPS * KB;
     if (jn < k1) load_rows(jn, kn, vn);
-    if (fused_append && h0 % G == 0) {                             // ... which are appended to the cache here
-#pragma unroll
-      for (int i = 0; i < KB; ++i) {
-        const int ji = j + i * WARPS;
-        if (ji == t_len - 1) { RowLoad<T, EPL>::stg(kc + (size_t)ji * KV, kr[i]); RowLoad<T, EPL>::stg(vc + (size_t)ji * KV, vr[i]); }
-      }
-    }
     float sv[KB * GQ];
 #pragma unroll
     for (int i = 0; i < KB; ++i) {
@@ -286,6 +288,7 @@ int attn_decode(b200_ctx *ctx, const void *q, const void *k_new, const void *v_n
   if (hd == 256 && gq > 4) gq = 1;
   DecodeAttnArgs a;
   a.q = q; a.k_new = k_new; a.v_new = v_new; a.kc = kc; a.vc = vc; a.o = o;
+  B200_REQUIRE(ctx, !k_new || (size_t)gq == G, "attn_decode: the fused cache append needs one CTA per KV-head group");
   a.pos_dev = pos_dev;
   if (pos_dev) t_len = S_max;                      // the grid is sized for the longest length so that it never changes
   a.ws_o = ws; a.ws_ml = ws + B * nH * ATTN_DECODE_MAX_SPLITS * hd; a.tickets = tickets;

@@ -751,7 +751,13 @@ static int layer_decode_core(b200_model *m, size_t l, const void *h_in, size_t B
     TRY(rope_strided(ctx, a.qkv, cos_p, sin_p, B, m->nH + m->nKV, 1, m->hd, (long long)m->QKV, (long long)m->hd, (long long)m->QKV, dt, false));
   }
   // attention over the cache; the new token's K/V rows go from the projection output into the cache in the same kernel
-  TRY(attn_decode(ctx, a.qkv, (const char *)a.qkv + m->Q * es, (const char *)a.qkv + (m->Q + m->KV) * es, m->k_cache[l], m->v_cache[l],
+  // when one CTA serves all query heads of a KV head (group sizes 1, 2, 4, 8), else in a copy kernel first
+  const size_t Gq = m->nH / m->nKV;
+  const bool fused_append = (Gq == 1 || Gq == 2 || Gq == 4 || Gq == 8) && !(m->hd == 256 && Gq > 4);
+  B200_REQUIRE(ctx, !pos_dev || fused_append, "decode: device-side positions need the cache append fused into the attention kernel");
+  if (!fused_append) TRY(kv_append(ctx, a.qkv, m->k_cache[l], m->v_cache[l], B, 1, pos, m->cache_len, m->Q, m->KV, m->QKV, dt));
+  TRY(attn_decode(ctx, a.qkv, fused_append ? (const char *)a.qkv + m->Q * es : nullptr,
+                  fused_append ? (const char *)a.qkv + (m->Q + m->KV) * es : nullptr, m->k_cache[l], m->v_cache[l],
                   a.o, B, m->nH, m->nKV, m->hd, m->cache_len, pos + 1, m->QKV, m->Q, m->dec_attn_ws, m->dec_attn_tickets, dt, pos_dev));
   TRY(b200_gemm_ld(ctx, a.o, m->P(m->off_o(l)), m->tmpH, B, H, m->Q, 0, 0, 0, dt, dt, m->Q, H, H));
   TRY(add_norm_oop(ctx, h_in, m->tmpH, a.h_mid, m->P(m->off_ffn_norm(l)), a.ffn_in, B, H, eps, dt));
@@ -833,6 +839,10 @@ extern "C" int b200_model_generate(b200_model *m, const int32_t *host_prompt, si
   const char *genv = getenv("B200_DECODE_GRAPH");
   bool use_graph = !(genv && genv[0] == '0') && new_tokens > 3 && m->dt == B200_BF16 && ctx->gemm_skinny &&
                    gemm_skinny_supported(B, 0, 0, 0) && m->hd % 32 == 0 && m->H % 8 == 0 && m->QKV % 8 == 0 && m->L > 0;
+  {
+    const size_t Gq = m->nH / m->nKV;              // group sizes whose cache append is fused into the attention kernel
+    use_graph = use_graph && (Gq == 1 || Gq == 2 || Gq == 4 || Gq == 8) && !(m->hd == 256 && Gq > 4);
+  }
   cudaGraphExec_t exec = nullptr;
   bool capture_tried = false;
   if (use_graph && !rc) {

@@ -105,7 +105,7 @@ def test_fp32_greedy_decode_is_bit_exact_against_the_checker(ctx, orc):
     model.close()
 
 
-@pytest.mark.parametrize("hd,nH,nKV", [(128, 4, 2), (64, 4, 1)])
+@pytest.mark.parametrize("hd,nH,nKV", [(128, 4, 2), (64, 4, 1), (64, 6, 2), (32, 8, 8)])   # groups of 2, 4, 3 (separate cache append), 1
 def test_bf16_cache_decode_matches_full_context_forward(ctx, hd, nH, nKV):
     B, P, NEW = 4, 40, 6
     shape = dict(H=nH * hd, I=768, nH=nH, nKV=nKV, hd=hd, V=1024, L=2)
