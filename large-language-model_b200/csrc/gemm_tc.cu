@@ -37,8 +37,9 @@ struct SharedTail {
 template <bool A_MN, bool B_MN, class TO, bool ACC>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-               TO *__restrict__ C, int M, int N, int K, size_t ldc, int *status, uint32_t mn_lbo, uint32_t mn_sbo,
-               uint32_t mn_kadv, GemmEpilogue epi) {
+               TO *__restrict__ C, int M, int N, int K, size_t ldc, int *status, GemmEpilogue epi) {
+  // MN-major descriptor fields (bytes): stride between 64-wide chunks, 8-row group stride, advance per 16-deep MMA
+  constexpr uint32_t mn_lbo = CHUNK_BYTES, mn_sbo = 1024, mn_kadv = 2048;
   extern __shared__ uint8_t smem_raw[];
   uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t *sA = smem, *sB = smem + STAGES * A_STAGE_BYTES;
@@ -214,8 +215,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   }
 }
 
-// MN-major descriptor fields (bytes): chunk stride, 8-row group stride, advance per 16-deep MMA.
-uint32_t g_mn_lbo = CHUNK_BYTES, g_mn_sbo = 1024, g_mn_kadv = 2048;
 PFN_cuTensorMapEncodeTiled_v12000 g_encode = nullptr;
 std::once_flag g_encode_once;
 
@@ -244,7 +243,7 @@ int launch_variant(b200_ctx *ctx, const CUtensorMap &ma, const CUtensorMap &mb, 
     tm.start = ev(); tm.stop = ev(); tm.flops = 2.0 * M * N * K;
     cudaEventRecord(tm.start, ctx->stream);
   }
-  kern<<<grid, THREADS, SMEM_BYTES, ctx->stream>>>(ma, mb, (TO *)C, M, N, K, ldc, ctx->dev_status, g_mn_lbo, g_mn_sbo, g_mn_kadv, epi);
+  kern<<<grid, THREADS, SMEM_BYTES, ctx->stream>>>(ma, mb, (TO *)C, M, N, K, ldc, ctx->dev_status, epi);
   B200_LAUNCHED(ctx);
   if (ctx->time_gemm) { cudaEventRecord(tm.stop, ctx->stream); ctx->timed.push_back(tm); }
   return B200_OK;
@@ -259,9 +258,6 @@ int launch_out(b200_ctx *ctx, const CUtensorMap &ma, const CUtensorMap &mb, void
 }
 
 }  // namespace
-
-// Bring-up hook (not part of the public header): override the MN-major descriptor fields.
-extern "C" void b200_internal_set_mn_desc(uint32_t lbo, uint32_t sbo, uint32_t kadv) { g_mn_lbo = lbo; g_mn_sbo = sbo; g_mn_kadv = kadv; }
 
 int tc_make_map_2d(CUtensorMap *map, const void *base, uint64_t inner, uint64_t outer, uint64_t row_stride_bytes,
                    uint32_t box_inner, uint32_t box_outer) {

@@ -69,10 +69,10 @@ __device__ __forceinline__ void tmem_dealloc_2sm(uint32_t taddr, uint32_t ncols)
   asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
 }
 
-// One 32-column chunk of one accumulator row -> global memory (optional rotary embedding, accumulate).
 __device__ __forceinline__ void red_add_v4(float *p, float a, float b, float c, float d) {
   asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
 }
+// One 32-column chunk of one accumulator row -> global memory (optional rotary embedding, accumulate).
 // `red`: this tile is one K-split of several -> add into C with vector reductions instead of storing.
 template <class TO, bool ACC>
 __device__ __forceinline__ void store_chunk(uint32_t (&r)[32], TO *crow, int row, int col, int N, const GemmEpilogue &epi,
