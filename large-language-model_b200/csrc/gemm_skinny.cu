@@ -40,6 +40,8 @@ __device__ __forceinline__ uint32_t cluster_rank() { uint32_t r; asm volatile("m
 __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
+__device__ __forceinline__ void cluster_arrive_all() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait_all() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
 __device__ __forceinline__ void st_cluster_f32(uint32_t local_addr, uint32_t cta, float v) {
   uint32_t remote;
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(cta));
@@ -79,7 +81,9 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   __syncthreads();
   tc::tc_fence_after();
   const uint32_t tmem_base = sh->tmem_base;
-  if (split > 1) cluster_sync_all();            // every CTA of the cluster is resident before remote stores
+  // every CTA of the cluster must be resident before the remote stores of the epilogue: arrive now, wait only there,
+  // so the barrier's latency hides behind the main loop
+  if (split > 1) cluster_arrive_all();
 
   pdl_launch_dependents();
   if (warp == 0 && lane == 0) {
@@ -123,6 +127,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   }
   __syncwarp();
   pdl_wait();                                   // before any global store (and for the threads that did not load)
+  if (split > 1) cluster_wait_all();
 
   // ---- epilogue: tensor memory -> the owning CTA's shared memory ------------------------------
   const int NL = FT / split;                    // features owned per CTA
