@@ -248,22 +248,50 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
   }
 }
 
-// D[b,h,s] = sum_d dO * O : one warp per (b,h,s) row.
-__global__ void attn_dsum_kernel(const bf16 *__restrict__ O, const bf16 *__restrict__ dO, float *__restrict__ D,
-                                 int B, int nH, int S, int hd, long long o_b, long long o_h, long long o_s) {
-  const int lane = threadIdx.x & 31;
+// D[b,h,s] = sum_d dO * O.  Eight lanes per (b,s,h) row (16-byte loads for head_dim 128), rows visited with the head
+// index fastest so that a token-major tensor is read as one contiguous stream; two rows per lane group in flight.
+template <int HD>
+__global__ void __launch_bounds__(256)
+attn_dsum_kernel(const bf16 *__restrict__ O, const bf16 *__restrict__ dO, float *__restrict__ D, int B, int nH, int S,
+                 long long o_b, long long o_h, long long o_s) {
+  constexpr int VEC = HD / 8;                       // elements per lane: 16 (32 bytes) or 8 (16 bytes)
+  typedef typename std::conditional<VEC == 16, uint4, uint2>::type Raw;   // loaded in 16- or 8-byte pieces
+  constexpr int PIECES = VEC * 2 / (int)sizeof(Raw);
+  const int sub = threadIdx.x & 7;
   const long long rows = (long long)B * nH * S;
-  for (long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); row < rows;
-       row += (long long)gridDim.x * (blockDim.x >> 5)) {
-    const int s = (int)(row % S), h = (int)((row / S) % nH), b = (int)(row / ((long long)S * nH));
-    const long long off = b * o_b + h * o_h + (long long)s * o_s;
-    float acc = 0.f;
-    for (int d = lane * 2; d < hd; d += 64) {
-      __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162 *>(O + off + d), c = *reinterpret_cast<const __nv_bfloat162 *>(dO + off + d);
-      acc += __bfloat162float(a.x) * __bfloat162float(c.x) + __bfloat162float(a.y) * __bfloat162float(c.y);
+  const long long group = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 3, n_groups = ((long long)gridDim.x * blockDim.x) >> 3;
+  auto dot_row = [&](long long r, Raw (&a)[PIECES], Raw (&c)[PIECES]) {
+    const int h = (int)(r % nH), s = (int)((r / nH) % S), b = (int)(r / ((long long)nH * S));
+    const long long off = b * o_b + h * o_h + (long long)s * o_s + sub * VEC;
+#pragma unroll
+    for (int p = 0; p < PIECES; ++p) {
+      a[p] = *reinterpret_cast<const Raw *>(O + off + p * (sizeof(Raw) / 2));
+      c[p] = *reinterpret_cast<const Raw *>(dO + off + p * (sizeof(Raw) / 2));
     }
-    acc = warp_sum(acc);
-    if (lane == 0) D[row] = acc;
+  };
+  auto reduce_store = [&](long long r, const Raw (&a)[PIECES], const Raw (&c)[PIECES]) {
+    float acc = 0.f;
+    const __nv_bfloat162 *pa = reinterpret_cast<const __nv_bfloat162 *>(a), *pc = reinterpret_cast<const __nv_bfloat162 *>(c);
+#pragma unroll
+    for (int i = 0; i < VEC / 2; ++i) {
+      const float2 x = __bfloat1622float2(pa[i]), y = __bfloat1622float2(pc[i]);
+      acc += x.x * y.x + x.y * y.y;
+    }
+    acc += __shfl_xor_sync(0xffffffffu, acc, 4);
+    acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+    acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+    if (sub == 0 && r < rows) {
+      const int h = (int)(r % nH), s = (int)((r / nH) % S), b = (int)(r / ((long long)nH * S));
+      D[((long long)b * nH + h) * S + s] = acc;
+    }
+  };
+  for (long long r0 = group * 2; r0 < rows; r0 += n_groups * 2) {      // the shuffles need every lane: rows past the end are clamped
+    const long long r1 = r0 + 1 < rows ? r0 + 1 : r0;
+    Raw a0[PIECES], c0[PIECES], a1[PIECES], c1[PIECES];
+    dot_row(r0, a0, c0);
+    dot_row(r1, a1, c1);
+    reduce_store(r0, a0, c0);
+    reduce_store(r0 + 1, a1, c1);
   }
 }
 // fp32 [B,nH,S,hd] accumulator -> strided bf16 dQ
@@ -301,9 +329,9 @@ int bwd_launch_t(b200_ctx *ctx, const void *Q, const void *K, const void *V, con
   float *Dsum = scr, *dQacc = scr + d_elems;
   B200_CUDA(ctx, cudaMemsetAsync(dQacc, 0, rows * HD * sizeof(float), ctx->stream));
   {
-    size_t blocks = (rows + 7) / 8, cap = (size_t)ctx->sm_count * 16;
-    attn_dsum_kernel<<<(int)(blocks < cap ? blocks : cap), 256, 0, ctx->stream>>>((const bf16 *)O, (const bf16 *)dO, Dsum, (int)B, (int)nH, (int)S, HD,
-                                                                                  st.o_b, st.o_h, st.o_s);
+    size_t blocks = (rows + 63) / 64, cap = (size_t)ctx->sm_count * 16;      // 32 lane groups x 2 rows per block pass
+    attn_dsum_kernel<HD><<<(int)(blocks < cap ? blocks : cap), 256, 0, ctx->stream>>>((const bf16 *)O, (const bf16 *)dO, Dsum, (int)B, (int)nH, (int)S,
+                                                                                      st.o_b, st.o_h, st.o_s);
     B200_LAUNCHED(ctx);
   }
   CUtensorMap mq, mk, mv, mdo, mdq;
