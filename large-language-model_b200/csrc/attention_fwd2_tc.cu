@@ -1,0 +1,278 @@
+// Causal grouped-query attention forward, second tensor-core form: one CTA works on TWO adjacent 128-query tiles
+// of a head at once and keeps both the probabilities and the output accumulators in tensor memory.
+// Replaces metal_bridge::flash_attn_fwd (cpp/include/gpu_kernel/MetalBridge.hpp:49-51); maths of
+// cpp/src/Attention.cpp:236-280.  Same interface and numerics contract as attention_tc.cu.
+//
+// Why: with one query tile per CTA the tensor cores wait for the softmax of every key tile and back.  Here
+//   * two independent softmax streams (query tiles A and B, one warpgroup each, one thread per query row, so no
+//     cross-thread exchange) alternate on the tensor pipe: while A's scores are exponentiated, B's products run;
+//   * P is written back over the scores in tensor memory as packed bf16 and is the A operand of the P V product
+//     (tcgen05.mma with A from tensor memory): no shared-memory round trip, no proxy fence;
+//   * O is accumulated by the MMA itself in tensor memory; it is rescaled only when a row's running maximum grew by
+//     more than 2^8 since the value in use (the stale maximum stays exact: numerator and denominator share it);
+//   * each K / V tile is loaded once for both query tiles.
+// Tensor memory: [S_A 128 | O_A 128 | S_B 128 | O_B 128] columns.  Shared memory: Q_A, Q_B, K x2, V x2.
+//   warps 0-3 softmax of tile A, warps 4-7 softmax of tile B, warp 8 MMA issue, warp 9 TMA.
+// tcgen05.mma operations of one thread execute in issue order, which is what lets S(j+1) overwrite the columns that
+// P(j) occupied right after the P(j) V(j) product has been issued.
+#include "attention_tc.cuh"
+
+using namespace attn;
+
+namespace {
+
+struct Fwd2Shared {
+  uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], p_full[2], o_full[2];
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+__device__ __forceinline__ void tmem_st_32x16(uint32_t taddr, const uint32_t *r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%16], {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15};"
+      ::"r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+        "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(taddr)
+      : "memory");
+}
+
+constexpr float RESCALE_THRESHOLD = 8.0f;      // log2 units: P stays below 2^8
+
+template <int HD>
+__global__ void __launch_bounds__(THREADS, 1)
+attn_fwd2_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                    const __grid_constant__ CUtensorMap map_v, bf16 *__restrict__ O, float *__restrict__ lse,
+                    int nH, int nKV, int S, long long o_b, long long o_h, long long o_s, float scale, int *status) {
+  constexpr int TILE_BYTES = 128 * HD * 2;
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t *smem = smem_raw;
+  uint8_t *sQ = smem, *sK = sQ + 2 * TILE_BYTES, *sV = sK + 2 * TILE_BYTES;
+  Fwd2Shared *sh = (Fwd2Shared *)(sV + 2 * TILE_BYTES);
+  if (tc::smem_u32(smem) & 1023u) {           // swizzled tiles need 1024-byte alignment: refuse rather than corrupt
+    if (threadIdx.x == 0) atomicCAS(status, 0, 298);
+    return;
+  }
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n_qt = (S + TQ - 1) / TQ, n_pairs = (n_qt + 1) / 2;
+  const int pr = n_pairs - 1 - (int)blockIdx.y;          // heaviest pairs are dispatched first
+  const int qA = 2 * pr, qB = 2 * pr + 1;
+  const bool validB = qB < n_qt;
+  const int nA = qA + 1, nB = validB ? qB + 1 : 0, n_kt = validB ? nB : nA;   // causal: key tiles 0..q
+  const int h = blockIdx.x % nH, b = blockIdx.x / nH, kvh = h / (nH / nKV);
+  volatile int *abort_flag = &sh->abort_flag;
+
+  if (threadIdx.x == 0) {
+    tc::mbar_init(&sh->q_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      tc::mbar_init(&sh->k_full[i], 1); tc::mbar_init(&sh->k_empty[i], 1);
+      tc::mbar_init(&sh->v_full[i], 1); tc::mbar_init(&sh->v_empty[i], 1);
+      tc::mbar_init(&sh->s_full[i], 1); tc::mbar_init(&sh->p_full[i], 4); tc::mbar_init(&sh->o_full[i], 1);
+    }
+    sh->abort_flag = 0;
+    tc::fence_barrier_init();
+    tc::fence_proxy_async();
+  }
+  if (warp == MMA_WARP) tc::tmem_alloc(&sh->tmem_base, 512);
+  tc::tc_fence_before();
+  __syncthreads();
+  tc::tc_fence_after();
+  const uint32_t tmem_base = sh->tmem_base;
+
+  if (warp == TMA_WARP) {
+    if (lane == 0) {
+      tc::mbar_expect_tx(&sh->q_full, validB ? 2 * TILE_BYTES : TILE_BYTES);
+      load_tile<HD>(sQ, &map_q, qA * TQ, h, b, &sh->q_full);
+      if (validB) load_tile<HD>(sQ + TILE_BYTES, &map_q, qB * TQ, h, b, &sh->q_full);
+      for (int j = 0; j < n_kt; ++j) {
+        const int s = j & 1; const uint32_t ph = (j >> 1) & 1;
+        if (!tc::mbar_wait(&sh->k_empty[s], ph ^ 1, status, abort_flag, 221)) break;
+        tc::mbar_expect_tx(&sh->k_full[s], TILE_BYTES);
+        load_tile<HD>(sK + s * TILE_BYTES, &map_k, j * TK, kvh, b, &sh->k_full[s]);
+        if (!tc::mbar_wait(&sh->v_empty[s], ph ^ 1, status, abort_flag, 222)) break;
+        tc::mbar_expect_tx(&sh->v_full[s], TILE_BYTES);
+        load_tile<HD>(sV + s * TILE_BYTES, &map_v, j * TK, kvh, b, &sh->v_full[s]);
+      }
+      if (*abort_flag) { long long t0 = clock64(); while (clock64() - t0 < 2000000ll) {} }
+    }
+  } else if (warp == MMA_WARP) {
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = tc::make_idesc_bf16(128, 128, false, false);
+      constexpr uint32_t idesc_o = tc::make_idesc_bf16(128, HD, false, true);
+      const uint32_t q_addr[2] = {tc::smem_u32(sQ), tc::smem_u32(sQ + TILE_BYTES)};
+      bool ok = tc::mbar_wait(&sh->q_full, 0, status, abort_flag, 223);
+      // S_X(j) = Q_X K_j^T into tile X's score columns; the K buffer is released after its last reader
+      auto issue_s = [&](int X, int j) -> bool {
+        const int s = j & 1; const uint32_t ph = (j >> 1) & 1;
+        if (!tc::mbar_wait(&sh->k_full[s], ph, status, abort_flag, 224)) return false;
+        tc::tc_fence_after();
+        const uint32_t k_addr = tc::smem_u32(sK + s * TILE_BYTES);
+#pragma unroll
+        for (int k = 0; k < HD / 16; ++k)
+          tc::umma_ss(tmem_base + X * 256, desc_kmajor(q_addr[X], k), desc_kmajor(k_addr, k), idesc_s, k ? 1u : 0u);
+        tc::umma_commit(&sh->s_full[X]);
+        const bool last_reader = X == 1 || j >= nB;      // B reads every key tile A reads, after A
+        if (last_reader) tc::umma_commit(&sh->k_empty[s]);
+        return true;
+      };
+      // O_X (+)= P_X(j) V_j with P read from tensor memory (packed bf16 over the first 64 score columns)
+      auto issue_pv = [&](int X, int j) -> bool {
+        const int s = j & 1; const uint32_t ph = (j >> 1) & 1;
+        if (!tc::mbar_wait(&sh->p_full[X], j & 1, status, abort_flag, 225)) return false;
+        if (!tc::mbar_wait(&sh->v_full[s], ph, status, abort_flag, 226)) return false;
+        tc::tc_fence_after();
+        const uint32_t v_addr = tc::smem_u32(sV + s * TILE_BYTES);
+#pragma unroll
+        for (int k = 0; k < TK / 16; ++k)
+          tc::umma_ts(tmem_base + X * 256 + 128, tmem_base + X * 256 + k * 8, desc_mnmajor(v_addr, k), idesc_o, (j > 0 || k > 0) ? 1u : 0u);
+        tc::umma_commit(&sh->o_full[X]);
+        const bool last_reader = X == 1 || j >= nB;
+        if (last_reader) tc::umma_commit(&sh->v_empty[s]);
+        return true;
+      };
+      if (ok) ok = issue_s(0, 0);
+      if (ok && validB) ok = issue_s(1, 0);
+      for (int j = 0; j < n_kt && ok; ++j) {
+        if (j < nA) { ok = issue_pv(0, j); if (ok && j + 1 < nA) ok = issue_s(0, j + 1); }
+        if (ok && j < nB) { ok = issue_pv(1, j); if (ok && j + 1 < nB) ok = issue_s(1, j + 1); }
+      }
+    }
+  } else {
+    // ---- softmax: warpgroup X owns query tile X, one thread per query row ------------------------------------
+    const int X = warp >> 2, quarter = warp & 3;
+    const int qt = X ? qB : qA, nX = X ? nB : nA;
+    const int r = quarter * 32 + lane;
+    const int q_idx = qt * TQ + r;
+    const int q_eff = min(q_idx, S - 1);               // rows past the end behave like the last row (never stored)
+    const float sl2 = scale * LOG2E;
+    const uint32_t tS = tmem_base + ((uint32_t)(quarter * 32) << 16) + X * 256, tO = tS + 128;
+    float m_used = -INFINITY, l = 0.f;
+    bool ok = true;
+    for (int j = 0; j < nX && ok; ++j) {
+      ok = tc::mbar_wait(&sh->s_full[X], j & 1, status, abort_flag, 228);
+      if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }        // the tensor-memory accesses below are warp-collective
+      tc::tc_fence_after();
+      const bool masked = (j == qt) || ((j + 1) * TK > S);   // diagonal tile, or keys past the end of the sequence
+      const int k0 = j * TK;
+      // pass 1: row maximum
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        tc::tmem_ld_32x32(tS + c * 32, v);
+        tc::tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          float x = __uint_as_float(v[i]);
+          if (masked && (k0 + c * 32 + i > q_eff)) x = -INFINITY;
+          mx4[i & 3] = fmaxf(mx4[i & 3], x);
+        }
+      }
+      const float m_new = fmaxf(m_used, fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * sl2);
+      const bool need = (m_new - m_used) > RESCALE_THRESHOLD;
+      if (j == 0) {
+        m_used = m_new;                                  // nothing accumulated yet
+      } else if (__any_sync(0xffffffffu, need)) {
+        // a row of this warp outgrew the maximum in use: rescale its output accumulator in tensor memory
+        // (the product of tile j-1 must have landed; the product of tile j cannot start before p_full below)
+        ok = tc::mbar_wait(&sh->o_full[X], (j - 1) & 1, status, abort_flag, 229);
+        if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
+        tc::tc_fence_after();
+        const float f = need ? fast_exp2(m_used - m_new) : 1.0f;
+#pragma unroll
+        for (int c = 0; c < HD / 32; ++c) {
+          uint32_t v[32];
+          tc::tmem_ld_32x32(tO + c * 32, v);
+          tc::tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * f);
+          tc::tmem_st_32x32(tO + c * 32, v);
+        }
+        tc::tmem_st_wait();
+        l *= f;
+        if (need) m_used = m_new;
+      }
+      // pass 2: probabilities, packed bf16 written over the first half of the score columns
+      float rs4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32], w[16];
+        tc::tmem_ld_32x32(tS + c * 32, v);
+        tc::tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          float e0 = fast_exp2(__uint_as_float(v[i]) * sl2 - m_used), e1 = fast_exp2(__uint_as_float(v[i + 1]) * sl2 - m_used);
+          if (masked) {
+            if (k0 + c * 32 + i > q_eff) e0 = 0.f;
+            if (k0 + c * 32 + i + 1 > q_eff) e1 = 0.f;
+          }
+          rs4[(i >> 1) & 3] += e0 + e1;
+          w[i >> 1] = pack_bf16(e0, e1);
+        }
+        tmem_st_32x16(tS + c * 16, w);                   // columns [16c, 16c+16) were read in this or an earlier chunk
+      }
+      tc::tmem_st_wait();
+      l += (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
+      tc::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) tc::mbar_arrive(&sh->p_full[X]);
+    }
+    if (ok && nX > 0) {
+      ok = __all_sync(0xffffffffu, tc::mbar_wait(&sh->o_full[X], (nX - 1) & 1, status, abort_flag, 230));
+      tc::tc_fence_after();
+      if (ok) {
+        const float inv = 1.0f / l;
+        bf16 *orow = O + (long long)b * o_b + (long long)h * o_h + (long long)q_idx * o_s;
+#pragma unroll
+        for (int c = 0; c < HD / 32; ++c) {
+          uint32_t v[32];
+          tc::tmem_ld_32x32(tO + c * 32, v);
+          tc::tmem_ld_wait();
+          if (q_idx < S) {
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              uint4 w;
+              w.x = pack_bf16(__uint_as_float(v[u * 8 + 0]) * inv, __uint_as_float(v[u * 8 + 1]) * inv);
+              w.y = pack_bf16(__uint_as_float(v[u * 8 + 2]) * inv, __uint_as_float(v[u * 8 + 3]) * inv);
+              w.z = pack_bf16(__uint_as_float(v[u * 8 + 4]) * inv, __uint_as_float(v[u * 8 + 5]) * inv);
+              w.w = pack_bf16(__uint_as_float(v[u * 8 + 6]) * inv, __uint_as_float(v[u * 8 + 7]) * inv);
+              *reinterpret_cast<uint4 *>(orow + c * 32 + u * 8) = w;
+            }
+          }
+        }
+        if (lse && q_idx < S) lse[((long long)b * nH + h) * S + q_idx] = (m_used + log2f(l)) * (1.0f / LOG2E);   // natural-log units
+      }
+      tc::tc_fence_before();
+    }
+  }
+  tc::tc_fence_before();
+  __syncthreads();
+  if (warp == MMA_WARP) {
+    __syncwarp();
+    tc::tc_fence_after();
+    tc::tmem_dealloc(tmem_base, 512);
+  }
+}
+
+template <int HD>
+int fwd2_launch_t(b200_ctx *ctx, const void *Q, const void *K, const void *V, void *O, float *lse, size_t B, size_t nH,
+                  size_t nKV, size_t S, const AttnStrides &st) {
+  CUtensorMap mq, mk, mv;
+  if (make_map_4d(&mq, Q, HD, S, nH, B, st.q_s, st.q_h, st.q_b) || make_map_4d(&mk, K, HD, S, nKV, B, st.k_s, st.k_h, st.k_b) ||
+      make_map_4d(&mv, V, HD, S, nKV, B, st.v_s, st.v_h, st.v_b))
+    return b200_fail(ctx, B200_ERR_CUDA, "cuTensorMapEncodeTiled failed for attention operands");
+  constexpr int smem = 6 * 128 * HD * 2 + (int)sizeof(Fwd2Shared);
+  static_assert(smem <= 232448, "forward attention tiles exceed the 227 KiB of shared memory per CTA");
+  static bool attr = false;
+  if (!attr) { B200_CUDA(ctx, cudaFuncSetAttribute(attn_fwd2_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)); attr = true; }
+  const size_t n_qt = (S + TQ - 1) / TQ;
+  dim3 grid((unsigned)(nH * B), (unsigned)((n_qt + 1) / 2), 1);
+  attn_fwd2_tc_kernel<HD><<<grid, THREADS, smem, ctx->stream>>>(mq, mk, mv, (bf16 *)O, lse, (int)nH, (int)nKV, (int)S, st.o_b, st.o_h,
+                                                               st.o_s, 1.0f / sqrtf((float)HD), ctx->dev_status);
+  B200_LAUNCHED(ctx);
+  return B200_OK;
+}
+}  // namespace
+
+int attn_fwd2_tc_launch(b200_ctx *ctx, const void *Q, const void *K, const void *V, void *O, float *lse, size_t B,
+                        size_t nH, size_t nKV, size_t S, size_t hd, const AttnStrides &st) {
+  return hd == 128 ? fwd2_launch_t<128>(ctx, Q, K, V, O, lse, B, nH, nKV, S, st) : fwd2_launch_t<64>(ctx, Q, K, V, O, lse, B, nH, nKV, S, st);
+}

@@ -3,6 +3,7 @@
 // calling convention (host buffers in, results visible on return).
 #include "common.cuh"
 #include <cstdarg>
+#include <cstdlib>
 #include <vector>
 
 int attn_fwd_simt_launch(b200_ctx *, const void *, const void *, const void *, void *, float *, size_t, size_t, size_t,
@@ -14,6 +15,8 @@ bool attn_tc_supported(size_t B, size_t nH, size_t nKV, size_t S, size_t hd, con
                        const void *Q, const void *K, const void *V, const void *O);
 int attn_fwd_tc_launch(b200_ctx *, const void *, const void *, const void *, void *, float *, size_t, size_t, size_t,
                        size_t, size_t, const AttnStrides &);
+int attn_fwd2_tc_launch(b200_ctx *, const void *, const void *, const void *, void *, float *, size_t, size_t, size_t,
+                        size_t, size_t, const AttnStrides &);
 int attn_bwd_tc_launch(b200_ctx *, const void *, const void *, const void *, const void *, const void *,
                        const float *, void *, void *, void *, size_t, size_t, size_t, size_t, size_t,
                        const AttnStrides &, const AttnStrides &, const float *, const float *);
@@ -72,6 +75,7 @@ extern "C" int b200_init(int device, b200_ctx **out) {
     return B200_ERR_CUDA;
   }
   ctx->stream = ctx->own_stream;
+  if (const char *e = getenv("B200_ATTN_FWD2")) ctx->attn_fwd2 = e[0] != '0';     // A/B switch for measurements
   cudaMemsetAsync(ctx->dev_status, 0, sizeof(int), ctx->stream);
   cudaStreamSynchronize(ctx->stream);
   *out = ctx;
@@ -118,6 +122,12 @@ extern "C" int b200_sync(b200_ctx *ctx) {
 extern "C" int b200_internal_set_gemm_2cta(b200_ctx *ctx, int enable) {
   if (!ctx) return B200_ERR_INVALID;
   ctx->gemm_2cta = enable != 0;
+  return B200_OK;
+}
+// Same kind of hook: 0 selects the one-query-tile forward attention kernel.
+extern "C" int b200_internal_set_attn_fwd2(b200_ctx *ctx, int enable) {
+  if (!ctx) return B200_ERR_INVALID;
+  ctx->attn_fwd2 = enable != 0;
   return B200_OK;
 }
 // Same kind of hook: 0 sends few-row GEMMs through the general tile kernel instead of the weight-streaming one.
@@ -261,7 +271,8 @@ int attn_fwd_launch(b200_ctx *ctx, const void *Q, const void *K, const void *V, 
   B200_REQUIRE(ctx, Q && K && V && O, "attention forward: null pointer");
   B200_REQUIRE(ctx, nKV > 0 && nH % nKV == 0, "attention: n_heads must be a multiple of n_kv (cpp/src/Attention.cpp:48-50)");
   if (attn_tc_supported(B, nH, nKV, S, hd, st, dt, Q, K, V, O))
-    return attn_fwd_tc_launch(ctx, Q, K, V, O, lse, B, nH, nKV, S, hd, st);
+    return ctx->attn_fwd2 ? attn_fwd2_tc_launch(ctx, Q, K, V, O, lse, B, nH, nKV, S, hd, st)
+                          : attn_fwd_tc_launch(ctx, Q, K, V, O, lse, B, nH, nKV, S, hd, st);
   return attn_fwd_simt_launch(ctx, Q, K, V, O, lse, B, nH, nKV, S, hd, st, dt);
 }
 int attn_bwd_launch(b200_ctx *ctx, const void *Q, const void *K, const void *V, const void *O, const void *dO,

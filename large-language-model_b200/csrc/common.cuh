@@ -30,6 +30,7 @@ struct b200_ctx {
   // 1: large bf16 GEMMs use the two-CTA (cta_group::2) kernel; 0: always the single-CTA kernel
   int gemm_2cta = 1;
   int gemm_skinny = 1;
+  int attn_fwd2 = 1;       // 1: forward attention works on two query tiles per CTA with P and O in tensor memory
   // decode step: kernels are launched with programmatic stream serialization, so a kernel's launch and set-up overlap the
   // tail of the one before it; each such kernel waits (griddepcontrol.wait) before it touches anything a predecessor wrote
   bool pdl = false;

@@ -11,6 +11,15 @@ pytestmark = pytest.mark.gpu
 SEED = 31
 
 
+@pytest.fixture(params=[1, 0], ids=["two_query_tiles_per_cta", "one_query_tile_per_cta"], autouse=True)
+def forward_kernel_choice(ctx, request):
+    """Every test runs with both forward kernels (internal A/B hook of the library)."""
+    ctx.lib.b200_internal_set_attn_fwd2.argtypes = [bridge._vp, bridge._i]
+    ctx.lib.b200_internal_set_attn_fwd2(ctx.h, request.param)
+    yield
+    ctx.lib.b200_internal_set_attn_fwd2(ctx.h, 1)
+
+
 def make(B, nH, nKV, S, hd, seed=SEED):
     q = synth.bf16_round(synth.normal(seed, "q", (B, nH, S, hd)))
     k = synth.bf16_round(synth.normal(seed, "k", (B, nKV, S, hd)))
