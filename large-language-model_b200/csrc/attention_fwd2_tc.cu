@@ -12,10 +12,11 @@
 //     more than 2^8 since the value in use (the stale maximum stays exact: numerator and denominator share it);
 //   * each K / V tile is loaded once for both query tiles.
 // Tensor memory: [S_A 128 | O_A 128 | S_B 128 | O_B 128] columns.  Shared memory: Q_A, Q_B, K x2, V x2.
-//   warps 0-3 softmax of tile A, warps 4-7 softmax of tile B, warp 8 MMA issue, warp 9 TMA.
+//   warps 0-3 softmax of tile A, warps 4-7 softmax of tile B, warp 8 MMA issue, warp 9 TMA (warps 10-11 only lend registers).
 // tcgen05.mma operations of one thread execute in issue order, which is what lets S(j+1) overwrite the columns that
 // P(j) occupied right after the P(j) V(j) product has been issued.
 #include "attention_tc.cuh"
+#include <type_traits>
 
 using namespace attn;
 
@@ -27,18 +28,22 @@ struct Fwd2Shared {
   int abort_flag;
 };
 
-__device__ __forceinline__ void tmem_st_32x16(uint32_t taddr, const uint32_t *r) {
-  asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%16], {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15};"
-      ::"r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
-        "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(taddr)
-      : "memory");
+constexpr float RESCALE_THRESHOLD = 8.0f;      // log2 units: P stays below 2^8
+// Three warpgroups: two of softmax (one thread per query row, the row's 128 scores stay in registers between the
+// maximum and the exponentials) and one holding the MMA and TMA warps, which gives most of its registers away.
+constexpr int FWD2_THREADS = 384;
+constexpr int REGS_SOFTMAX = 232, REGS_SERVICE = 40;
+template <int N> __device__ __forceinline__ void setmaxnreg_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
+template <int N> __device__ __forceinline__ void setmaxnreg_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
+
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
 }
 
-constexpr float RESCALE_THRESHOLD = 8.0f;      // log2 units: P stays below 2^8
-
 template <int HD>
-__global__ void __launch_bounds__(THREADS, 1)
+__global__ void __launch_bounds__(FWD2_THREADS, 1)
 attn_fwd2_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                     const __grid_constant__ CUtensorMap map_v, bf16 *__restrict__ O, float *__restrict__ lse,
                     int nH, int nKV, int S, long long o_b, long long o_h, long long o_s, float scale, int *status) {
@@ -77,7 +82,9 @@ attn_fwd2_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   tc::tc_fence_after();
   const uint32_t tmem_base = sh->tmem_base;
 
-  if (warp == TMA_WARP) {
+  if (warp >= 8) {
+   setmaxnreg_dec<REGS_SERVICE>();
+   if (warp == TMA_WARP) {
     if (lane == 0) {
       tc::mbar_expect_tx(&sh->q_full, validB ? 2 * TILE_BYTES : TILE_BYTES);
       load_tile<HD>(sQ, &map_q, qA * TQ, h, b, &sh->q_full);
@@ -135,7 +142,9 @@ attn_fwd2_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         if (ok && j < nB) { ok = issue_pv(1, j); if (ok && j + 1 < nB) ok = issue_s(1, j + 1); }
       }
     }
+   }
   } else {
+    setmaxnreg_inc<REGS_SOFTMAX>();
     // ---- softmax: warpgroup X owns query tile X, one thread per query row ------------------------------------
     const int X = warp >> 2, quarter = warp & 3;
     const int qt = X ? qB : qA, nX = X ? nB : nA;
@@ -152,19 +161,24 @@ attn_fwd2_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       tc::tc_fence_after();
       const bool masked = (j == qt) || ((j + 1) * TK > S);   // diagonal tile, or keys past the end of the sequence
       const int k0 = j * TK;
-      // pass 1: row maximum
+      // The row's 128 scores are read once and stay in registers.  Tiles below the diagonal (almost all of them)
+      // take the path without per-element bound checks.
+      uint32_t v[128];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tc::tmem_ld_32x32(tS + c * 32, v + c * 32);
+      tc::tmem_ld_wait();
+      if (masked) {
+#pragma unroll
+        for (int i = 0; i < 128; ++i)
+          if (k0 + i > q_eff) v[i] = 0xff800000u;        // -inf: exp2 gives exactly 0 below
+      }
       float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        tc::tmem_ld_32x32(tS + c * 32, v);
-        tc::tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float x = __uint_as_float(v[i]);
-          if (masked && (k0 + c * 32 + i > q_eff)) x = -INFINITY;
-          mx4[i & 3] = fmaxf(mx4[i & 3], x);
-        }
+      for (int i = 0; i < 128; i += 8) {
+        mx4[0] = max3(mx4[0], __uint_as_float(v[i]), __uint_as_float(v[i + 1]));
+        mx4[1] = max3(mx4[1], __uint_as_float(v[i + 2]), __uint_as_float(v[i + 3]));
+        mx4[2] = max3(mx4[2], __uint_as_float(v[i + 4]), __uint_as_float(v[i + 5]));
+        mx4[3] = max3(mx4[3], __uint_as_float(v[i + 6]), __uint_as_float(v[i + 7]));
       }
       const float m_new = fmaxf(m_used, fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * sl2);
       const bool need = (m_new - m_used) > RESCALE_THRESHOLD;
@@ -179,38 +193,30 @@ attn_fwd2_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         const float f = need ? fast_exp2(m_used - m_new) : 1.0f;
 #pragma unroll
         for (int c = 0; c < HD / 32; ++c) {
-          uint32_t v[32];
-          tc::tmem_ld_32x32(tO + c * 32, v);
+          uint32_t o[32];
+          tc::tmem_ld_32x32(tO + c * 32, o);
           tc::tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * f);
-          tc::tmem_st_32x32(tO + c * 32, v);
+          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * f);
+          tc::tmem_st_32x32(tO + c * 32, o);
         }
         tc::tmem_st_wait();
         l *= f;
         if (need) m_used = m_new;
       }
-      // pass 2: probabilities, packed bf16 written over the first half of the score columns
+      // probabilities, packed bf16 written over the first half of the score columns (all 128 were read above)
       float rs4[4] = {0.f, 0.f, 0.f, 0.f};
+      uint32_t w[64];
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t v[32], w[16];
-        tc::tmem_ld_32x32(tS + c * 32, v);
-        tc::tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          float e0 = fast_exp2(__uint_as_float(v[i]) * sl2 - m_used), e1 = fast_exp2(__uint_as_float(v[i + 1]) * sl2 - m_used);
-          if (masked) {
-            if (k0 + c * 32 + i > q_eff) e0 = 0.f;
-            if (k0 + c * 32 + i + 1 > q_eff) e1 = 0.f;
-          }
-          rs4[(i >> 1) & 3] += e0 + e1;
-          w[i >> 1] = pack_bf16(e0, e1);
-        }
-        tmem_st_32x16(tS + c * 16, w);                   // columns [16c, 16c+16) were read in this or an earlier chunk
+      for (int i = 0; i < 128; i += 2) {
+        const float e0 = fast_exp2(__uint_as_float(v[i]) * sl2 - m_used), e1 = fast_exp2(__uint_as_float(v[i + 1]) * sl2 - m_used);
+        rs4[(i >> 1) & 3] += e0 + e1;
+        w[i >> 1] = pack_bf16(e0, e1);
       }
-      tc::tmem_st_wait();
+      tc::tmem_st_32x32(tS, w);
+      tc::tmem_st_32x32(tS + 32, w + 32);
       l += (rs4[0] + rs4[1]) + (rs4[2] + rs4[3]);
+      tc::tmem_st_wait();
       tc::tc_fence_before();
       __syncwarp();
       if (lane == 0) tc::mbar_arrive(&sh->p_full[X]);
@@ -265,7 +271,7 @@ int fwd2_launch_t(b200_ctx *ctx, const void *Q, const void *K, const void *V, vo
   if (!attr) { B200_CUDA(ctx, cudaFuncSetAttribute(attn_fwd2_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)); attr = true; }
   const size_t n_qt = (S + TQ - 1) / TQ;
   dim3 grid((unsigned)(nH * B), (unsigned)((n_qt + 1) / 2), 1);
-  attn_fwd2_tc_kernel<HD><<<grid, THREADS, smem, ctx->stream>>>(mq, mk, mv, (bf16 *)O, lse, (int)nH, (int)nKV, (int)S, st.o_b, st.o_h,
+  attn_fwd2_tc_kernel<HD><<<grid, FWD2_THREADS, smem, ctx->stream>>>(mq, mk, mv, (bf16 *)O, lse, (int)nH, (int)nKV, (int)S, st.o_b, st.o_h,
                                                                st.o_s, 1.0f / sqrtf((float)HD), ctx->dev_status);
   B200_LAUNCHED(ctx);
   return B200_OK;
