@@ -151,29 +151,37 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
       if (!tc::mbar_wait(&sh->s_full, ph, status, abort_flag, 306)) { ok = false; break; }
       if (!tc::mbar_wait(&sh->dp_full, ph, status, abort_flag, 307)) { ok = false; break; }
       tc::tc_fence_after();
+      // P and dS for this thread's 64 key columns; tiles below the diagonal with all rows valid (almost all of them)
+      // take the path without per-element bound checks
+      auto p_and_ds = [&](auto masked_tag) {
+        constexpr bool MASKED = decltype(masked_tag)::value;
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t sv[32], dv[32];
-        tc::tmem_ld_32x32(t_s + lane_base + half * 64 + c * 32, sv);
-        tc::tmem_ld_32x32(t_dp + lane_base + half * 64 + c * 32, dv);
-        tc::tmem_ld_wait();
+        for (int c = 0; c < 2; ++c) {
+          uint32_t sv[32], dv[32];
+          tc::tmem_ld_32x32(t_s + lane_base + half * 64 + c * 32, sv);
+          tc::tmem_ld_32x32(t_dp + lane_base + half * 64 + c * 32, dv);
+          tc::tmem_ld_wait();
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          float p[8], ds[8];
+          for (int u = 0; u < 4; ++u) {
+            float p[8], ds[8];
 #pragma unroll
-          for (int x = 0; x < 8; ++x) {
-            float e = fast_exp2(__uint_as_float(sv[u * 8 + x]) * sl2 - L2);
-            if (!valid || (diag && (kc0 + c * 32 + u * 8 + x > q_idx))) e = 0.f;
-            p[x] = e;
-            ds[x] = e * (__uint_as_float(dv[u * 8 + x]) - Dr) * scale;
+            for (int x = 0; x < 8; ++x) {
+              float e = fast_exp2(__uint_as_float(sv[u * 8 + x]) * sl2 - L2);
+              if constexpr (MASKED) {
+                if (!valid || (diag && (kc0 + c * 32 + u * 8 + x > q_idx))) e = 0.f;
+              }
+              p[x] = e;
+              ds[x] = e * (__uint_as_float(dv[u * 8 + x]) - Dr) * scale;
+            }
+            uint4 w;
+            w.x = pack_bf16(p[0], p[1]); w.y = pack_bf16(p[2], p[3]); w.z = pack_bf16(p[4], p[5]); w.w = pack_bf16(p[6], p[7]);
+            *reinterpret_cast<uint4 *>(sP + swz_unit(r, half * 8 + c * 4 + u)) = w;
+            w.x = pack_bf16(ds[0], ds[1]); w.y = pack_bf16(ds[2], ds[3]); w.z = pack_bf16(ds[4], ds[5]); w.w = pack_bf16(ds[6], ds[7]);
+            *reinterpret_cast<uint4 *>(sdS + swz_unit(r, half * 8 + c * 4 + u)) = w;
           }
-          uint4 w;
-          w.x = pack_bf16(p[0], p[1]); w.y = pack_bf16(p[2], p[3]); w.z = pack_bf16(p[4], p[5]); w.w = pack_bf16(p[6], p[7]);
-          *reinterpret_cast<uint4 *>(sP + swz_unit(r, half * 8 + c * 4 + u)) = w;
-          w.x = pack_bf16(ds[0], ds[1]); w.y = pack_bf16(ds[2], ds[3]); w.z = pack_bf16(ds[4], ds[5]); w.w = pack_bf16(ds[6], ds[7]);
-          *reinterpret_cast<uint4 *>(sdS + swz_unit(r, half * 8 + c * 4 + u)) = w;
         }
-      }
+      };
+      if (diag || (i + 1) * TQ > S) p_and_ds(std::true_type{}); else p_and_ds(std::false_type{});
       tc::fence_proxy_async();
       tc::tc_fence_before();
       __syncwarp();
