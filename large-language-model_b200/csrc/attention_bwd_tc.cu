@@ -325,6 +325,14 @@ __global__ void attn_dq_store_kernel(const float *__restrict__ acc, bf16 *__rest
   }
 }
 
+}  // namespace
+
+bool attn_bwd2_supported(size_t S, size_t hd);
+int attn_bwd2_tc_run(b200_ctx *ctx, const void *Q, const void *K, const void *V, const void *dO, const float *lse, const float *Dsum,
+                     float *dQacc, void *dK, void *dV, size_t B, size_t nH, size_t nKV, size_t S, const AttnStrides &st,
+                     const AttnStrides &gst, const float *rope_cos, const float *rope_sin);
+
+namespace {
 template <int HD>
 int bwd_launch_t(b200_ctx *ctx, const void *Q, const void *K, const void *V, const void *O, const void *dO,
                  const float *lse, void *dQ, void *dK, void *dV, size_t B, size_t nH, size_t nKV, size_t S,
@@ -335,6 +343,7 @@ int bwd_launch_t(b200_ctx *ctx, const void *Q, const void *K, const void *V, con
   float *scr = (float *)b200_scratch(ctx, (d_elems + rows * HD) * sizeof(float));
   if (!scr) return B200_ERR_NOMEM;
   float *Dsum = scr, *dQacc = scr + d_elems;
+  const bool second_form = HD == 128 && ctx->attn_bwd2 && attn_bwd2_supported(S, HD) && (uintptr_t)lse % 16 == 0;
   B200_CUDA(ctx, cudaMemsetAsync(dQacc, 0, rows * HD * sizeof(float), ctx->stream));
   {
     size_t blocks = (rows + 63) / 64, cap = (size_t)ctx->sm_count * 16;      // 32 lane groups x 2 rows per block pass
@@ -342,19 +351,24 @@ int bwd_launch_t(b200_ctx *ctx, const void *Q, const void *K, const void *V, con
                                                                                       st.o_b, st.o_h, st.o_s);
     B200_LAUNCHED(ctx);
   }
-  CUtensorMap mq, mk, mv, mdo, mdq;
-  if (make_map_4d(&mq, Q, HD, S, nH, B, st.q_s, st.q_h, st.q_b) || make_map_4d(&mk, K, HD, S, nKV, B, st.k_s, st.k_h, st.k_b) ||
-      make_map_4d(&mv, V, HD, S, nKV, B, st.v_s, st.v_h, st.v_b) || make_map_4d(&mdo, dO, HD, S, nH, B, st.o_s, st.o_h, st.o_b) ||
-      tc_make_map_f32_3d(&mdq, dQacc, HD, S, B * nH, (uint64_t)HD * 4, (uint64_t)S * HD * 4, 32, 128))
-    return b200_fail(ctx, B200_ERR_CUDA, "cuTensorMapEncodeTiled failed for attention operands");
-  constexpr int smem = 4 * 128 * HD * 2 + 2 * 32768 + 1024 + (int)sizeof(BwdShared);
-  static bool attr = false;
-  if (!attr) { B200_CUDA(ctx, cudaFuncSetAttribute(attn_bwd_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)); attr = true; }
-  dim3 grid((unsigned)(nKV * B), (unsigned)((S + TK - 1) / TK), 1);
-  attn_bwd_tc_kernel<HD><<<grid, THREADS, smem, ctx->stream>>>(mq, mk, mv, mdo, mdq, lse, Dsum, (bf16 *)dK, (bf16 *)dV, (int)nH, (int)nKV, (int)S,
-                                                              gst.k_b, gst.k_h, gst.k_s, gst.v_b, gst.v_h, gst.v_s, 1.0f / sqrtf((float)HD),
-                                                              ctx->dev_status, rope_cos, rope_sin);
-  B200_LAUNCHED(ctx);
+  if (second_form) {
+    int rc = attn_bwd2_tc_run(ctx, Q, K, V, dO, lse, Dsum, dQacc, dK, dV, B, nH, nKV, S, st, gst, rope_cos, rope_sin);
+    if (rc != B200_OK) return rc;
+  } else {
+    CUtensorMap mq, mk, mv, mdo, mdq;
+    if (make_map_4d(&mq, Q, HD, S, nH, B, st.q_s, st.q_h, st.q_b) || make_map_4d(&mk, K, HD, S, nKV, B, st.k_s, st.k_h, st.k_b) ||
+        make_map_4d(&mv, V, HD, S, nKV, B, st.v_s, st.v_h, st.v_b) || make_map_4d(&mdo, dO, HD, S, nH, B, st.o_s, st.o_h, st.o_b) ||
+        tc_make_map_f32_3d(&mdq, dQacc, HD, S, B * nH, (uint64_t)HD * 4, (uint64_t)S * HD * 4, 32, 128))
+      return b200_fail(ctx, B200_ERR_CUDA, "cuTensorMapEncodeTiled failed for attention operands");
+    constexpr int smem = 4 * 128 * HD * 2 + 2 * 32768 + 1024 + (int)sizeof(BwdShared);
+    static bool attr = false;
+    if (!attr) { B200_CUDA(ctx, cudaFuncSetAttribute(attn_bwd_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)); attr = true; }
+    dim3 grid((unsigned)(nKV * B), (unsigned)((S + TK - 1) / TK), 1);
+    attn_bwd_tc_kernel<HD><<<grid, THREADS, smem, ctx->stream>>>(mq, mk, mv, mdo, mdq, lse, Dsum, (bf16 *)dK, (bf16 *)dV, (int)nH, (int)nKV, (int)S,
+                                                                gst.k_b, gst.k_h, gst.k_s, gst.v_b, gst.v_h, gst.v_s, 1.0f / sqrtf((float)HD),
+                                                                ctx->dev_status, rope_cos, rope_sin);
+    B200_LAUNCHED(ctx);
+  }
   {
     size_t items = rows * (HD / 8), blocks = (items + 255) / 256, cap = (size_t)ctx->sm_count * 16;
     attn_dq_store_kernel<<<(int)(blocks < cap ? blocks : cap), 256, 0, ctx->stream>>>(dQacc, (bf16 *)dQ, (int)B, (int)nH, (int)S, HD, gst.q_b, gst.q_h, gst.q_s, rope_cos, rope_sin);

@@ -76,6 +76,7 @@ extern "C" int b200_init(int device, b200_ctx **out) {
   }
   ctx->stream = ctx->own_stream;
   if (const char *e = getenv("B200_ATTN_FWD2")) ctx->attn_fwd2 = e[0] != '0';     // A/B switch for measurements
+  if (const char *e = getenv("B200_ATTN_BWD2")) ctx->attn_bwd2 = e[0] != '0';
   cudaMemsetAsync(ctx->dev_status, 0, sizeof(int), ctx->stream);
   cudaStreamSynchronize(ctx->stream);
   *out = ctx;
@@ -125,6 +126,11 @@ extern "C" int b200_internal_set_gemm_2cta(b200_ctx *ctx, int enable) {
   return B200_OK;
 }
 // Same kind of hook: 0 selects the one-query-tile forward attention kernel.
+extern "C" int b200_internal_set_attn_bwd2(b200_ctx *ctx, int enable) {
+  if (!ctx) return B200_ERR_INVALID;
+  ctx->attn_bwd2 = enable != 0;
+  return B200_OK;
+}
 extern "C" int b200_internal_set_attn_fwd2(b200_ctx *ctx, int enable) {
   if (!ctx) return B200_ERR_INVALID;
   ctx->attn_fwd2 = enable != 0;

@@ -11,13 +11,17 @@ pytestmark = pytest.mark.gpu
 SEED = 31
 
 
-@pytest.fixture(params=[1, 0], ids=["two_query_tiles_per_cta", "one_query_tile_per_cta"], autouse=True)
-def forward_kernel_choice(ctx, request):
-    """Every test runs with both forward kernels (internal A/B hook of the library)."""
-    ctx.lib.b200_internal_set_attn_fwd2.argtypes = [bridge._vp, bridge._i]
+@pytest.fixture(params=[1, 0], ids=["second_forms", "first_forms"], autouse=True)
+def kernel_choice(ctx, request):
+    """Every test runs with both forms of the forward and of the backward kernel (internal A/B hooks of the library)."""
+    default_bwd2 = 1
+    for name in ("b200_internal_set_attn_fwd2", "b200_internal_set_attn_bwd2"):
+        getattr(ctx.lib, name).argtypes = [bridge._vp, bridge._i]
     ctx.lib.b200_internal_set_attn_fwd2(ctx.h, request.param)
+    ctx.lib.b200_internal_set_attn_bwd2(ctx.h, request.param)
     yield
     ctx.lib.b200_internal_set_attn_fwd2(ctx.h, 1)
+    ctx.lib.b200_internal_set_attn_bwd2(ctx.h, default_bwd2)
 
 
 def make(B, nH, nKV, S, hd, seed=SEED):
