@@ -15,13 +15,14 @@
 // cores turn the scores of step s into P and dS, the tensor cores already compute the scores of step s+1, and while
 // they run the three products of step s the CUDA cores work on step s+1.
 //   warps 0-7 compute P^T / dS^T (and the final dK / dV rows), warp 8 issues MMAs, warp 9 loads Q_t / dO_t and the
-//   row statistics three steps ahead, warps 10-13 copy each finished dQ_t^T out of tensor memory (so that the slot is
+//   row statistics four steps ahead, warps 10-13 copy each finished dQ_t^T out of tensor memory (so that the slot is
 //   free for step s+2 without the compute warps being involved) and add it to the global accumulator straight from
 //   registers: a warp's 32 head_dim values of one query are one 128-byte line, so each red instruction is coalesced.
 //   (Shared memory bandwidth is what bounds this kernel - MMA operands, TMA writes and ordinary stores share it - so
 //   dQ does not take the detour through a staging buffer and a TMA reduce-add.)
-//   tensor memory: [S^T 64 | dP^T 64] x 2 slots | dV 128 | dK 128 columns; dQ_t^T lands in the slot's dP^T columns.
-//   shared memory: K, V, (Q, dO, lse and D of the step's queries) x 3, dS^T x 2 = 194 KiB.
+//   tensor memory: S^T x 2 steps | dP^T x 2 steps (64 columns each) | dV 128 | dK 128; dQ_t^T lands in the step's dP^T
+//   columns.  The scores of a pair of steps are one N = 128 product each (S^T, dP^T); everything else runs per step.
+//   shared memory: K, V, (Q, dO, lse and D of the step's queries) x 4, dS^T x 2 = 226 KiB.
 // dQ goes into the fp32 accumulator [B*nH*S][head_dim] that the first form fills with TMA reduce-adds.
 #include "attention_tc.cuh"
 #include <type_traits>
@@ -36,7 +37,8 @@ constexpr int KV_TILE = 128 * HD * 2;                   // 32 KiB
 constexpr int Q_TILE = SQ * HD * 2;                     // 16 KiB
 constexpr int DS_TILE = 128 * SQ * 2;                   // 16 KiB: [128 keys][64 queries] bf16, one swizzled chunk
 constexpr int STAT = 2 * SQ * 4;                        // lse and D of the 64 queries of a step
-constexpr int NQ = 3;                                   // Q / dO steps in flight
+constexpr int NQ = 4;                                   // Q / dO sub-tiles in flight: two pairs of consecutive steps
+constexpr int PAIR_TILE = 2 * Q_TILE;                   // [128 rows: step 2p, step 2p+1][128 columns] as two 64-column chunks
 constexpr int STAGE_WARPS = 4, BWD2_THREADS = THREADS + 32 * STAGE_WARPS;   // warps 10..13
 
 struct Bwd2Shared {
@@ -71,14 +73,14 @@ __device__ __forceinline__ void mma_ts(uint32_t d, uint32_t a_tmem, Desc b, uint
                "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}"
                ::"r"(d), "r"(a_tmem), "r"(b.lo + (b_off >> 4)), "r"(b.hi), "r"(idesc), "r"(acc) : "memory");
 }
-// [64 rows x 128 columns] bf16 sub-tile as two chunks of [64 rows][128 B] (box 64 x 64)
+// [64 rows x 128 columns] bf16 sub-tile: half of the rows of a pair tile, whose two 64-column chunks are 16 KiB apart
 __device__ __forceinline__ void bulk_load_1d(void *dst, const void *src, uint32_t bytes, uint64_t *bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                ::"r"(tc::smem_u32(dst)), "l"(src), "r"(bytes), "r"(tc::smem_u32(bar)) : "memory");
 }
 __device__ __forceinline__ void load_subtile(uint8_t *dst, const CUtensorMap *map, int row0, int head, int batch, uint64_t *bar) {
   tma_load_4d(dst, map, 0, row0, head, batch, bar);
-  tma_load_4d(dst + 8192, map, 64, row0, head, batch, bar);
+  tma_load_4d(dst + 16384, map, 64, row0, head, batch, bar);
 }
 
 __global__ void __launch_bounds__(BWD2_THREADS, 1)
@@ -134,8 +136,9 @@ attn_bwd2_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         const uint32_t stat_bytes = (uint32_t)min(SQ, S - q0) * 4;      // a multiple of 16: S is a multiple of 4
         const long long stat_off = ((long long)b * nH + h) * S + q0;
         tc::mbar_expect_tx(&sh->qdo_full[s], 2 * Q_TILE + 2 * stat_bytes);
-        load_subtile(sQ + s * Q_TILE, &map_q, q0, h, b, &sh->qdo_full[s]);
-        load_subtile(sdO + s * Q_TILE, &map_do, q0, h, b, &sh->qdo_full[s]);
+        const int sub_off = ((st >> 1) & 1) * PAIR_TILE + (st & 1) * 8192;
+        load_subtile(sQ + sub_off, &map_q, q0, h, b, &sh->qdo_full[s]);
+        load_subtile(sdO + sub_off, &map_do, q0, h, b, &sh->qdo_full[s]);
         bulk_load_1d(sStat + s * STAT, lse + stat_off, stat_bytes, &sh->qdo_full[s]);
         bulk_load_1d(sStat + s * STAT + SQ * 4, Dsum + stat_off, stat_bytes, &sh->qdo_full[s]);
       };
@@ -148,28 +151,31 @@ attn_bwd2_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     }
   } else if (warp == MMA_WARP) {
     if (lane == 0) {
-      constexpr uint32_t idesc_s = tc::make_idesc_bf16(128, SQ, false, false);    // S^T, dP^T: keys x queries
+      constexpr uint32_t idesc_s = tc::make_idesc_bf16(128, 2 * SQ, false, false);   // S^T, dP^T: keys x queries of a pair
       constexpr uint32_t idesc_kv = tc::make_idesc_bf16(128, HD, false, true);    // dV, dK: A from tensor memory
       constexpr uint32_t idesc_dq = tc::make_idesc_bf16(HD, SQ, true, true);      // dQ_t^T: head_dim x queries
       const Desc dk_k = desc_of(tc::smem_u32(sK), 16, 1024), dv_k = desc_of(tc::smem_u32(sV), 16, 1024), dk_mn = desc_of(tc::smem_u32(sK), 16384, 1024);
       bool ok = tc::mbar_wait(&sh->kv_full, 0, status, abort_flag, 333);
-      auto issue_scores = [&](int st) -> bool {
-        const int s = st & 1, sq = st % NQ;
-        if (!tc::mbar_wait(&sh->qdo_full[sq], (st / NQ) & 1, status, abort_flag, 334)) return false;
+      // scores of the pair of steps (2p, 2p+1): one N = 128 product each for S^T and dP^T (half the operand traffic of
+      // two N = 64 products); the second step may not exist, its columns are then never read
+      auto issue_scores = [&](int p) -> bool {
+        const int a = 2 * p;
+        if (!tc::mbar_wait(&sh->qdo_full[a % NQ], (a / NQ) & 1, status, abort_flag, 334)) return false;
+        if (a + 1 < n_steps && !tc::mbar_wait(&sh->qdo_full[(a + 1) % NQ], ((a + 1) / NQ) & 1, status, abort_flag, 334)) return false;
         tc::tc_fence_after();
-        const Desc dq_k = desc_of(tc::smem_u32(sQ + sq * Q_TILE), 16, 1024), ddo_k = desc_of(tc::smem_u32(sdO + sq * Q_TILE), 16, 1024);
-        const uint32_t t_s = tmem_base + s * 128, t_dp = t_s + 64;
-        mma_ss<false>(t_s, dk_k, 0, dq_k, 0, idesc_s);
+        const Desc dq_k = desc_of(tc::smem_u32(sQ + (p & 1) * PAIR_TILE), 16, 1024), ddo_k = desc_of(tc::smem_u32(sdO + (p & 1) * PAIR_TILE), 16, 1024);
+        mma_ss<false>(tmem_base, dk_k, 0, dq_k, 0, idesc_s);
 #pragma unroll
-        for (int k = 1; k < HD / 16; ++k) mma_ss<true>(t_s, dk_k, (k >> 2) * 16384 + (k & 3) * 32, dq_k, (k >> 2) * 8192 + (k & 3) * 32, idesc_s);
-        tc::umma_commit(&sh->s_full[s]);
-        // the dP^T columns held dQ^T of step st-2 until the staging warps copied it out
-        if (st >= 2 && !tc::mbar_wait(&sh->dq_consumed[s], ((st - 2) >> 1) & 1, status, abort_flag, 335)) return false;
+        for (int k = 1; k < HD / 16; ++k) mma_ss<true>(tmem_base, dk_k, (k >> 2) * 16384 + (k & 3) * 32, dq_k, (k >> 2) * 16384 + (k & 3) * 32, idesc_s);
+        tc::umma_commit(&sh->s_full[p & 1]);
+        // the dP^T columns held dQ^T of steps 2p-2 and 2p-1 until the dQ warps copied them out
+        if (p >= 1 && !(tc::mbar_wait(&sh->dq_consumed[0], (p - 1) & 1, status, abort_flag, 335) &&
+                        tc::mbar_wait(&sh->dq_consumed[1], (p - 1) & 1, status, abort_flag, 335))) return false;
         tc::tc_fence_after();
-        mma_ss<false>(t_dp, dv_k, 0, ddo_k, 0, idesc_s);
+        mma_ss<false>(tmem_base + 128, dv_k, 0, ddo_k, 0, idesc_s);
 #pragma unroll
-        for (int k = 1; k < HD / 16; ++k) mma_ss<true>(t_dp, dv_k, (k >> 2) * 16384 + (k & 3) * 32, ddo_k, (k >> 2) * 8192 + (k & 3) * 32, idesc_s);
-        tc::umma_commit(&sh->sdp_full[s]);
+        for (int k = 1; k < HD / 16; ++k) mma_ss<true>(tmem_base + 128, dv_k, (k >> 2) * 16384 + (k & 3) * 32, ddo_k, (k >> 2) * 16384 + (k & 3) * 32, idesc_s);
+        tc::umma_commit(&sh->sdp_full[p & 1]);
         return true;
       };
       auto issue_products = [&](int st) -> bool {
@@ -177,9 +183,10 @@ attn_bwd2_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         if (!tc::mbar_wait(&sh->pds_full[s], ph, status, abort_flag, 336)) return false;
         tc::tc_fence_after();
         const int sq = st % NQ;
-        const Desc dq_mn = desc_of(tc::smem_u32(sQ + sq * Q_TILE), 8192, 1024), ddo_mn = desc_of(tc::smem_u32(sdO + sq * Q_TILE), 8192, 1024),
+        const int sub_off = ((st >> 1) & 1) * PAIR_TILE + s * 8192;
+        const Desc dq_mn = desc_of(tc::smem_u32(sQ + sub_off), 16384, 1024), ddo_mn = desc_of(tc::smem_u32(sdO + sub_off), 16384, 1024),
                    dds_mn = desc_of(tc::smem_u32(sdS + s * DS_TILE), 16384, 1024);
-        const uint32_t t_s = tmem_base + s * 128, t_dp = t_s + 64;
+        const uint32_t t_s = tmem_base + s * 64, t_dp = t_s + 128;
         // dK += dS^T Q_t ; dV += P^T dO_t : A (keys x 64 queries, packed bf16) from tensor memory, 16 queries per MMA;
         // the packed values of queries [0,32) sit in columns [0,16) and those of queries [32,64) in columns [32,48).
         // The tensor pipe runs this thread's MMAs in order, so dQ_t^T may overwrite dS^T right after the dK product; it
@@ -198,15 +205,13 @@ attn_bwd2_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         tc::umma_commit(&sh->qdo_empty[sq]);
         return true;
       };
-      // Two chains (even and odd steps) alternate on the tensor pipe: scores(s) -> P/dS on the CUDA cores -> products(s) ->
-      // dQ^T copied out -> scores(s+2).  Issue order per pair of steps: products, products, scores, scores.
+      // Issue order: scores of pair p+1 follow the products of pair p; the CUDA cores work on step 2p+1 while the tensor
+      // pipe runs the products of step 2p.
       if (ok && n_steps > 0) ok = issue_scores(0);
-      if (ok && n_steps > 1) ok = issue_scores(1);
       for (int st = 0; st < n_steps && ok; st += 2) {
         ok = issue_products(st);
         if (ok && st + 1 < n_steps) ok = issue_products(st + 1);
-        if (ok && st + 2 < n_steps) ok = issue_scores(st + 2);
-        if (ok && st + 3 < n_steps) ok = issue_scores(st + 3);
+        if (ok && st + 2 < n_steps) ok = issue_scores((st >> 1) + 1);
       }
       if (ok) tc::umma_commit(&sh->done);
     }
@@ -214,19 +219,21 @@ attn_bwd2_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     // ---- dQ warps: dQ_t^T (rows = head_dim = this thread's lane, 64 queries) -> global fp32 accumulator --------------
     const int quarter = warp & 3;
     const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+    int sub = 0, head = kvh * G;                                   // step st: query sub-tile 2j + sub of this head
     for (int st = 0; st < n_steps; ++st) {
       const int s = st & 1; const uint32_t ph = (st >> 1) & 1;
       if (!__all_sync(0xffffffffu, tc::mbar_wait(&sh->dq_full[s], ph, status, abort_flag, 342))) break;
       tc::tc_fence_after();
       uint32_t v[64];
-      tc::tmem_ld_32x32(tmem_base + lane_base + s * 128 + 64, v);
-      tc::tmem_ld_32x32(tmem_base + lane_base + s * 128 + 96, v + 32);
+      tc::tmem_ld_32x32(tmem_base + lane_base + 128 + s * 64, v);
+      tc::tmem_ld_32x32(tmem_base + lane_base + 128 + s * 64 + 32, v + 32);
       tc::tmem_ld_wait();
       tc::tc_fence_before();
       __syncwarp();
       if (lane == 0) tc::mbar_arrive(&sh->dq_consumed[s]);        // the columns may take dP^T of step st+2
-      const int q0 = step_q0(st), nq = min(SQ, S - q0);
-      float *dst = dQacc + (((long long)b * nH + step_head(st)) * S + q0) * HD + quarter * 32 + lane;
+      const int q0 = (2 * j + sub) * SQ, nq = min(SQ, S - q0);
+      float *dst = dQacc + (((long long)b * nH + head) * S + q0) * HD + quarter * 32 + lane;
+      if (++sub == per_head) { sub = 0; ++head; }
 #pragma unroll
       for (int q = 0; q < SQ; ++q)
         if (q < nq) asm volatile("red.global.add.f32 [%0], %1;" ::"l"(dst + (size_t)q * HD), "f"(__uint_as_float(v[q])) : "memory");
@@ -239,17 +246,20 @@ attn_bwd2_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     const float sl2 = scale * LOG2E;
     const int key = j * TK + r;
     bool ok = true;
+    int sub = 0;                                                      // step st: query sub-tile 2j + sub (no division per step)
     for (int st = 0; st < n_steps && ok; ++st) {
-      const int s = st & 1; const uint32_t ph = (st >> 1) & 1;
-      const int q0 = step_q0(st) + half * 32;                          // this thread's first query
+      const int s = st & 1;
+      const int tile_q0 = (2 * j + sub) * SQ, q0 = tile_q0 + half * 32;     // this thread's first query
+      if (++sub == per_head) sub = 0;
       const float *st_l = reinterpret_cast<const float *>(sStat + (st % NQ) * STAT) + half * 32, *st_d = st_l + SQ;
       // bound checks only where the step touches the diagonal or an end of the sequence
-      const bool tile_masked = (step_q0(st) < (j + 1) * TK) || (step_q0(st) + SQ > S) || ((j + 1) * TK > S);
-      const uint32_t t_s = tmem_base + lane_base + s * 128, t_dp = t_s + 64;
+      const bool tile_masked = (tile_q0 < (j + 1) * TK) || (tile_q0 + SQ > S) || ((j + 1) * TK > S);
+      const uint32_t t_s = tmem_base + lane_base + s * 64, t_dp = t_s + 128;
+      const int pr = (st >> 1) & 1; const uint32_t pph = (st >> 2) & 1;      // the pair's score barriers
       uint32_t sv[32], wp[16], wd[16];
       float p[32];
       ok = tc::mbar_wait(&sh->qdo_full[st % NQ], (st / NQ) & 1, status, abort_flag, 346) &&      // lse, D of this step
-           tc::mbar_wait(&sh->s_full[s], ph, status, abort_flag, 343);
+           tc::mbar_wait(&sh->s_full[pr], pph, status, abort_flag, 343);
       if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
       tc::tc_fence_after();
       tc::tmem_ld_32x32(t_s + half * 32, sv);
@@ -274,7 +284,7 @@ attn_bwd2_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 #pragma unroll
       for (int x = 0; x < 16; ++x) wp[x] = pack_bf16(p[2 * x], p[2 * x + 1]);
       tmem_st_32x16(t_s + half * 32, wp);
-      ok = tc::mbar_wait(&sh->sdp_full[s], ph, status, abort_flag, 345);
+      ok = tc::mbar_wait(&sh->sdp_full[pr], pph, status, abort_flag, 345);
       if (!__all_sync(0xffffffffu, ok)) { ok = false; break; }
       tc::tc_fence_after();
       tc::tmem_ld_32x32(t_dp + half * 32, sv);
