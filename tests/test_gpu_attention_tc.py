@@ -33,7 +33,9 @@ def make(B, nH, nKV, S, hd, seed=SEED):
 
 
 @pytest.mark.parametrize("B,nH,nKV,S,hd", [(1, 1, 1, 128, 128), (1, 2, 1, 256, 128), (2, 4, 2, 384, 128),
-                                           (1, 4, 1, 200, 128), (2, 4, 4, 72, 64), (1, 8, 2, 520, 64), (1, 2, 2, 1, 128)])
+                                           (1, 4, 1, 200, 128), (2, 4, 4, 72, 64), (1, 8, 2, 520, 64), (1, 2, 2, 1, 128),
+                                           # odd numbers of 64-query steps per key tile, a lone step, a ragged last step
+                                           (1, 1, 1, 192, 128), (1, 3, 3, 64, 128), (2, 2, 2, 320, 128), (1, 3, 1, 84, 128)])
 def test_forward_and_backward_match_the_checker(ctx, orc, B, nH, nKV, S, hd):
     q, k, v, dO = make(B, nH, nKV, S, hd)
     dq_, dk_, dv_ = ctx.array(q, "bf16"), ctx.array(k, "bf16"), ctx.array(v, "bf16")
