@@ -77,6 +77,7 @@ extern "C" int b200_init(int device, b200_ctx **out) {
   ctx->stream = ctx->own_stream;
   if (const char *e = getenv("B200_ATTN_FWD2")) ctx->attn_fwd2 = e[0] != '0';     // A/B switch for measurements
   if (const char *e = getenv("B200_ATTN_BWD2")) ctx->attn_bwd2 = e[0] != '0';
+  if (const char *e = getenv("B200_DECODE_ATTN_TC")) ctx->attn_decode_tc = e[0] != '0';
   cudaMemsetAsync(ctx->dev_status, 0, sizeof(int), ctx->stream);
   cudaStreamSynchronize(ctx->stream);
   *out = ctx;
@@ -126,6 +127,11 @@ extern "C" int b200_internal_set_gemm_2cta(b200_ctx *ctx, int enable) {
   return B200_OK;
 }
 // Same kind of hook: 0 selects the one-query-tile forward attention kernel.
+extern "C" int b200_internal_set_attn_decode_tc(b200_ctx *ctx, int enable) {
+  if (!ctx) return B200_ERR_INVALID;
+  ctx->attn_decode_tc = enable != 0;
+  return B200_OK;
+}
 extern "C" int b200_internal_set_attn_bwd2(b200_ctx *ctx, int enable) {
   if (!ctx) return B200_ERR_INVALID;
   ctx->attn_bwd2 = enable != 0;

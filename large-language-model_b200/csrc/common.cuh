@@ -31,6 +31,7 @@ struct b200_ctx {
   int gemm_2cta = 1;
   int gemm_skinny = 1;
   int attn_fwd2 = 1;       // 1: forward attention works on two query tiles per CTA with P and O in tensor memory
+  int attn_decode_tc = 1;  // 1: decode attention on the tensor cores when one CTA per (sequence, KV head) fills the GPU
   int attn_bwd2 = 1;       // 1: backward attention (head_dim 128) in its transposed form, P and dS in tensor memory
   // decode step: kernels are launched with programmatic stream serialization, so a kernel's launch and set-up overlap the
   // tail of the one before it; each such kernel waits (griddepcontrol.wait) before it touches anything a predecessor wrote

@@ -273,6 +273,11 @@ int launch_hd(b200_ctx *ctx, const DecodeAttnArgs &a, int hd, int gq, dim3 grid)
 
 constexpr int ATTN_DECODE_MAX_SPLITS = 16;
 
+bool attn_decode_tc_supported(const b200_ctx *ctx, const void *q, const void *kc, const void *vc, const void *o, size_t B, size_t nH,
+                              size_t nKV, size_t hd, size_t S_max, size_t ldq, size_t ldo, b200_dtype dt);
+int attn_decode_tc(b200_ctx *ctx, const void *q, const void *k_new, const void *v_new, void *kc, void *vc, void *o, size_t B,
+                   size_t nH, size_t nKV, size_t S_max, size_t t_len, size_t ldq, size_t ldo, const int *pos_dev);
+
 size_t attn_decode_workspace_floats(size_t B, size_t nH, size_t hd) { return B * nH * ATTN_DECODE_MAX_SPLITS * (hd + 2); }
 
 // q/k_new/v_new: rows of the fused projection (stride ldq); k_new/v_new may be null when the cache already
@@ -283,6 +288,8 @@ int attn_decode(b200_ctx *ctx, const void *q, const void *k_new, const void *v_n
   B200_REQUIRE(ctx, (hd == 32 || hd == 64 || hd == 128 || hd == 256) && t_len >= 1 && t_len <= S_max && nKV > 0 && nH % nKV == 0,
                "attn_decode: head_dim must be 32, 64, 128 or 256 and 1 <= length <= cache length");
   B200_REQUIRE(ctx, ws && tickets && B <= 65535, "attn_decode: workspace missing");
+  if (ctx->attn_decode_tc && attn_decode_tc_supported(ctx, q, kc, vc, o, B, nH, nKV, hd, S_max, ldq, ldo, dt))
+    return attn_decode_tc(ctx, q, k_new, v_new, kc, vc, o, B, nH, nKV, S_max, t_len, ldq, ldo, pos_dev);
   const size_t G = nH / nKV;
   int gq = (G == 2 || G == 4 || G == 8) ? (int)G : 1;
   if (hd == 256 && gq > 4) gq = 1;

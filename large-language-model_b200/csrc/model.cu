@@ -700,7 +700,11 @@ extern "C" int b200_model_decode_begin(b200_model *m, size_t batch, size_t max_t
   B200_REQUIRE(ctx, m->k_cache.empty(), "decode_begin: caches already allocated with a smaller shape");
   const size_t es = dtype_size(m->dt), bytes = batch * max_total_len * m->KV * es;
   m->k_cache.assign(m->L, nullptr); m->v_cache.assign(m->L, nullptr);
-  for (size_t l = 0; l < m->L; ++l) { TRY(dalloc(m, &m->k_cache[l], bytes)); TRY(dalloc(m, &m->v_cache[l], bytes)); }
+  for (size_t l = 0; l < m->L; ++l) {
+    TRY(dalloc(m, &m->k_cache[l], bytes)); TRY(dalloc(m, &m->v_cache[l], bytes));
+    // positions not yet written are read by whole-tile loads and multiplied by a zero weight: they must be finite
+    TRY(b200_fill_zero(ctx, m->k_cache[l], bytes)); TRY(b200_fill_zero(ctx, m->v_cache[l], bytes));
+  }
   TRY(dalloc(m, &m->dec_logits, batch * m->V * es));
   TRY(dalloc(m, &m->dec_h, batch * m->H * es));
   TRY(dalloc(m, (void **)&m->dec_history, batch * max_total_len * sizeof(int32_t)));

@@ -127,6 +127,54 @@ def test_bf16_cache_decode_matches_full_context_forward(ctx, hd, nH, nKV):
         ctxt = np.concatenate([ctxt, nxt[:, None]], 1)
     model.close()
 
+@pytest.mark.parametrize("nH,nKV,P", [(4, 2, 150), (8, 2, 700), (8, 1, 130)])   # groups of 2, 4, 8; 2, 6 and 2 cache tiles
+def test_tensor_core_decode_attention(ctx, nH, nKV, P, monkeypatch):
+    """With enough (sequence, KV head) pairs to fill the GPU, head_dim 128 decode attention runs on the tensor cores
+    (whole-tile TMA reads of the cache, ring reuse beyond five tiles, a ragged last tile, a cache length that is not
+    a multiple of the tile).  Checked against the engine's full-context forward, against the CUDA-core kernel, and
+    captured (position on the device) against eagerly enqueued."""
+    hd, NEW = 128, 5
+    import torch
+    B = torch.cuda.get_device_properties(0).multi_processor_count // (2 * nKV) + 1      # just enough pairs to qualify
+    shape = dict(H=nH * hd, I=512, nH=nH, nKV=nKV, hd=hd, V=512, L=2)
+    S = P + NEW
+    model = bridge.Model(ctx, bridge.Shape(B=B, S=S, **shape), "bf16", with_optimizer=False)
+    model.init_synthetic(6, 0.05)
+    prompt = synth.token_ids(6, "prompt", (B, P), shape["V"])
+    ctx.lib.b200_internal_set_attn_decode_tc.argtypes = [bridge._vp, bridge._i]
+
+    def run(tc):
+        ctx.lib.b200_internal_set_attn_decode_tc(ctx.h, tc)
+        model.decode_begin(B, S)
+        logits = model.prefill(ctx.array(prompt, "i32"), B, P).download()
+        out, ctxt = [], prompt.copy()
+        for t in range(NEW):
+            nxt = logits.argmax(-1).astype(np.int32) if tc else forced[t]
+            out.append((logits, nxt))
+            logits = model.decode_step(ctx.array(nxt, "i32"), B, P + t).download()
+            ctxt = np.concatenate([ctxt, nxt[:, None]], 1)
+        out.append((logits, None))
+        return out, ctxt
+
+    try:
+        n0 = ctx.launch_count()
+        tc_out, ctxt = run(1)
+        forced = [nxt for _, nxt in tc_out[:-1]]
+        core_out, _ = run(0)
+        for t, ((a, _), (b, _)) in enumerate(zip(tc_out, core_out)):
+            assert rel(a, b) < BF16_TOL, (t, rel(a, b))       # two bf16 kernels: P rounded to bf16 here, fp32 there
+        full = model.forward(ctx.array(ctxt, "i32"), B, ctxt.shape[1]).download().reshape(B, ctxt.shape[1], -1)[:, -1]
+        assert rel(tc_out[-1][0], full) < BF16_TOL
+        ctx.lib.b200_internal_set_attn_decode_tc(ctx.h, 1)
+        cfg = bridge.SamplerConfig.make(temperature=0.0, top_p=1.0, repetition_penalty=1.0, top_k=0)
+        graph_ids, _, _ = model.generate(prompt, NEW, cfg)
+        monkeypatch.setenv("B200_DECODE_GRAPH", "0")
+        eager_ids, _, _ = model.generate(prompt, NEW, cfg)
+        np.testing.assert_array_equal(graph_ids, eager_ids)
+    finally:
+        ctx.lib.b200_internal_set_attn_decode_tc(ctx.h, 1)
+        model.close()
+
 
 @pytest.mark.parametrize("temperature", [0.0, 0.8])
 def test_captured_decode_step_equals_the_eagerly_enqueued_one(ctx, temperature, monkeypatch):
