@@ -8,6 +8,7 @@
 
 namespace {
 constexpr int WARPS_PER_CTA = 8;
+constexpr int ROW_THREADS = 256;                    // CTA-per-row kernel for few rows
 
 template <class T, int VPL, bool ADD>
 __global__ void __launch_bounds__(WARPS_PER_CTA * 32)
@@ -75,6 +76,85 @@ rms_fwd_warp_kernel(const T *x, T *h_out, const T *__restrict__ r, const T *__re
         for (int j = 0; j < N; ++j) o[j] = v[i][j] * rstd2 * wf[j];
         Vec16<T> ov; ov.pack(o); ov.store(y2 + base + (lane + 32 * i) * N);
       }
+    }
+  }
+}
+
+// Few rows (a decode step normalises one row per sequence): one CTA per row, one 16-byte vector per thread and chunk,
+// every load of the row in flight at once and the weights requested before the wait on the previous kernel, so that the
+// kernel is one memory round trip plus two block reductions instead of a chain of dependent loads in a single warp.
+template <class T, int CH, bool ADD>
+__global__ void __launch_bounds__(ROW_THREADS)
+rms_fwd_row_kernel(const T *x, T *h_out, const T *__restrict__ r, const T *__restrict__ w, T *__restrict__ y,
+                   float *__restrict__ rstd_out, float eps, int D, const T *__restrict__ w2, T *__restrict__ y2) {
+  constexpr int N = Vec16<T>::N;
+  __shared__ float red[2][ROW_THREADS / 32];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  pdl_launch_dependents();
+  Vec16<T> wv[CH], w2v[CH];                          // parameters: no kernel of the stream writes them
+#pragma unroll
+  for (int i = 0; i < CH; ++i) {
+    wv[i].load(w + (tid + ROW_THREADS * i) * N);
+    if (y2) w2v[i].load(w2 + (tid + ROW_THREADS * i) * N);
+  }
+  pdl_wait();
+  const size_t base = (size_t)blockIdx.x * (size_t)D;
+  Vec16<T> a[CH], b[CH];
+#pragma unroll
+  for (int i = 0; i < CH; ++i) a[i].load(x + base + (tid + ROW_THREADS * i) * N);
+  if (ADD) {
+#pragma unroll
+    for (int i = 0; i < CH; ++i) b[i].load(r + base + (tid + ROW_THREADS * i) * N);
+  }
+  float v[CH][N], ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < CH; ++i) {
+    a[i].unpack(v[i]);
+    if (ADD) {
+      float rb[N];
+      b[i].unpack(rb);
+#pragma unroll
+      for (int j = 0; j < N; ++j) v[i][j] += rb[j];
+      Vec16<T> o; o.pack(v[i]); o.store(h_out + base + (tid + ROW_THREADS * i) * N); o.unpack(v[i]);   // normalise what is stored
+    }
+#pragma unroll
+    for (int j = 0; j < N; ++j) ss += v[i][j] * v[i][j];
+  }
+  auto block_sum = [&](float t, float *buf) {
+    t = warp_sum(t);
+    if (lane == 0) buf[warp] = t;
+    __syncthreads();
+    float s = 0.f;
+#pragma unroll
+    for (int k = 0; k < ROW_THREADS / 32; ++k) s += buf[k];
+    return s;
+  };
+  const float rstd = rsqrtf(block_sum(ss, red[0]) / (float)D + eps);
+  if (rstd_out && tid == 0) rstd_out[blockIdx.x] = rstd;
+  float ss2 = 0.f;
+#pragma unroll
+  for (int i = 0; i < CH; ++i) {
+    float wf[N], o[N];
+    wv[i].unpack(wf);
+#pragma unroll
+    for (int j = 0; j < N; ++j) o[j] = v[i][j] * rstd * wf[j];
+    Vec16<T> ov; ov.pack(o);
+    if (y) ov.store(y + base + (tid + ROW_THREADS * i) * N);
+    if (y2) {                                       // the second norm reads the first one's output as stored
+      ov.unpack(v[i]);
+#pragma unroll
+      for (int j = 0; j < N; ++j) ss2 += v[i][j] * v[i][j];
+    }
+  }
+  if (y2) {
+    const float rstd2 = rsqrtf(block_sum(ss2, red[1]) / (float)D + eps);
+#pragma unroll
+    for (int i = 0; i < CH; ++i) {
+      float wf[N], o[N];
+      w2v[i].unpack(wf);
+#pragma unroll
+      for (int j = 0; j < N; ++j) o[j] = v[i][j] * rstd2 * wf[j];
+      Vec16<T> ov; ov.pack(o); ov.store(y2 + base + (tid + ROW_THREADS * i) * N);
     }
   }
 }
@@ -165,6 +245,16 @@ int rms_fwd_warp(b200_ctx *ctx, const void *x, void *h, const void *r, const voi
                  size_t rows, size_t D, bool add, const void *w2, void *y2) {
   constexpr int N = Vec16<T>::N;
   if (D % (32 * N) || !aligned16({x, h, r, w, y, w2, y2})) return 0;
+  if (rows <= (size_t)ctx->sm_count && D % (ROW_THREADS * N) == 0 && D / (ROW_THREADS * N) <= 2) {
+    // fewer rows than SMs: a CTA per row
+#define FR(C, A) launch_k(ctx, rms_fwd_row_kernel<T, C, A>, dim3((unsigned)rows), dim3(ROW_THREADS), 0, 0, (const T *)x, (T *)h, (const T *)r, (const T *)w, (T *)y, rstd, eps, (int)D, (const T *)w2, (T *)y2)
+    if (D / (ROW_THREADS * N) == 1) { if (add) FR(1, true); else FR(1, false); }
+    else { if (add) FR(2, true); else FR(2, false); }
+#undef FR
+    ctx->launches++;
+    if (cudaGetLastError() != cudaSuccess) return b200_fail(ctx, B200_ERR_CUDA, "rms_norm forward launch failed");
+    return 1;
+  }
   const int vpl = (int)(D / (32 * N));
   const int grid = warp_grid(ctx, rows);
 #define FW(V, A) launch_k(ctx, rms_fwd_warp_kernel<T, V, A>, dim3(grid), dim3(WARPS_PER_CTA * 32), 0, 0, (const T *)x, (T *)h, (const T *)r, (const T *)w, (T *)y, rstd, eps, rows, (int)D, (const T *)w2, (T *)y2)
