@@ -1,5 +1,5 @@
 // Causal grouped-query attention backward, second tensor-core form (head_dim 128): keys in the tensor-memory lanes,
-// 64-query steps, two steps in flight.  Replaces metal_bridge::fused_attn_bwd
+// 64-query steps handled in pairs.  Replaces metal_bridge::fused_attn_bwd
 // (cpp/include/gpu_kernel/MetalBridge.hpp:54-57); maths of cpp/src/Attention.cpp:292-348.  Same contract as
 // attention_bwd_tc.cu, which stays for head_dim 64 and for sequence lengths that are not a multiple of 4.
 //
@@ -11,9 +11,8 @@
 //                                                                    written back over S^T / dP^T as packed bf16)
 //     dQ_t^T = K_j^T dS^T                                            (dS^T also goes to shared memory, as the B operand)
 // The transposition is what lets P and dS feed the two accumulating products without a shared-memory round trip, and
-// with 64-query steps the score buffers take only a quarter of tensor memory, so there are two sets: while the CUDA
-// cores turn the scores of step s into P and dS, the tensor cores already compute the scores of step s+1, and while
-// they run the three products of step s the CUDA cores work on step s+1.
+// with 64-query steps the scores of TWO steps fit beside the dK / dV accumulators: while the tensor cores run the
+// products of the pair's first step, the CUDA cores turn the second step's scores into P and dS.
 //   warps 0-7 compute P^T / dS^T (and the final dK / dV rows), warp 8 issues MMAs, warp 9 loads Q_t / dO_t and the
 //   row statistics four steps ahead, warps 10-13 copy each finished dQ_t^T out of tensor memory (so that the slot is
 //   free for step s+2 without the compute warps being involved) and add it to the global accumulator straight from
@@ -25,7 +24,6 @@
 //   shared memory: K, V, (Q, dO, lse and D of the step's queries) x 4, dS^T x 2 = 226 KiB.
 // dQ goes into the fp32 accumulator [B*nH*S][head_dim] that the first form fills with TMA reduce-adds.
 #include "attention_tc.cuh"
-#include <type_traits>
 
 using namespace attn;
 
@@ -39,7 +37,7 @@ constexpr int DS_TILE = 128 * SQ * 2;                   // 16 KiB: [128 keys][64
 constexpr int STAT = 2 * SQ * 4;                        // lse and D of the 64 queries of a step
 constexpr int NQ = 4;                                   // Q / dO sub-tiles in flight: two pairs of consecutive steps
 constexpr int PAIR_TILE = 2 * Q_TILE;                   // [128 rows: step 2p, step 2p+1][128 columns] as two 64-column chunks
-constexpr int STAGE_WARPS = 4, BWD2_THREADS = THREADS + 32 * STAGE_WARPS;   // warps 10..13
+constexpr int DQ_WARPS = 4, BWD2_THREADS = THREADS + 32 * DQ_WARPS;         // warps 10..13 add dQ to global memory
 
 struct Bwd2Shared {
   uint64_t kv_full, qdo_full[NQ], qdo_empty[NQ], s_full[2], sdp_full[2], pds_full[2], dq_full[2], dq_consumed[2], done;
@@ -111,7 +109,7 @@ attn_bwd2_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     for (int i = 0; i < NQ; ++i) { tc::mbar_init(&sh->qdo_full[i], 1); tc::mbar_init(&sh->qdo_empty[i], 1); }
     for (int i = 0; i < 2; ++i) {
       tc::mbar_init(&sh->s_full[i], 1); tc::mbar_init(&sh->sdp_full[i], 1); tc::mbar_init(&sh->pds_full[i], COMPUTE_WARPS);
-      tc::mbar_init(&sh->dq_full[i], 1); tc::mbar_init(&sh->dq_consumed[i], STAGE_WARPS);
+      tc::mbar_init(&sh->dq_full[i], 1); tc::mbar_init(&sh->dq_consumed[i], DQ_WARPS);
     }
     sh->abort_flag = 0;
     tc::fence_barrier_init();
@@ -190,7 +188,7 @@ attn_bwd2_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         // dK += dS^T Q_t ; dV += P^T dO_t : A (keys x 64 queries, packed bf16) from tensor memory, 16 queries per MMA;
         // the packed values of queries [0,32) sit in columns [0,16) and those of queries [32,64) in columns [32,48).
         // The tensor pipe runs this thread's MMAs in order, so dQ_t^T may overwrite dS^T right after the dK product; it
-        // is issued before the dV product so that the staging warps get it as early as possible.
+        // is issued before the dV product so that the dQ warps get it as early as possible.
 #pragma unroll
         for (int k = 0; k < SQ / 16; ++k)
           mma_ts(t_dk, t_dp + (k >> 1) * 32 + (k & 1) * 8, dq_mn, k * 2048, idesc_kv, (st | k) ? 1u : 0u);
