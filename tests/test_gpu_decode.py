@@ -127,7 +127,7 @@ def test_bf16_cache_decode_matches_full_context_forward(ctx, hd, nH, nKV):
         ctxt = np.concatenate([ctxt, nxt[:, None]], 1)
     model.close()
 
-@pytest.mark.parametrize("nH,nKV,P", [(4, 2, 150), (8, 2, 700), (8, 1, 130)])   # groups of 2, 4, 8; 2, 6 and 2 cache tiles
+@pytest.mark.parametrize("nH,nKV,P", [(4, 2, 150), (8, 2, 700), (8, 1, 130), (4, 2, 1100)])   # groups of 2, 4, 8, 2; 2, 6, 2 and 9 cache tiles
 def test_tensor_core_decode_attention(ctx, nH, nKV, P, monkeypatch):
     """With enough (sequence, KV head) pairs to fill the GPU, head_dim 128 decode attention runs on the tensor cores
     (whole-tile TMA reads of the cache, ring reuse beyond five tiles, a ragged last tile, a cache length that is not
