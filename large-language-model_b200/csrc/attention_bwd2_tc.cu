@@ -6,7 +6,9 @@
 // One CTA per (128-key tile j, kv head, batch) owns dK_j and dV_j in tensor memory and walks the query heads of
 // its kv head and their 64-query sub-tiles t >= 2j.  Everything is computed TRANSPOSED, keys as rows:
 //     S^T  = K_j Q_t^T          dP^T = V_j dO_t^T                    (128 keys x 64 queries each, tensor memory)
-//     P^T  = exp(S^T*scale - lse[q]),  dS^T = P^T (dP^T - D[q]) scale   (CUDA cores, two threads per key row)
+//     P^T  = exp(S^T*scale - lse[q]),  dS^T = P^T (dP^T - D[q])         (CUDA cores, two threads per key row; the factor
+//                                                                    `scale` of dS is applied to dK at the end and to dQ by
+//                                                                    the kernel that stores it; lse comes in base-2 units)
 //     dV_j += P^T dO_t          dK_j += dS^T Q_t                     (P^T, dS^T are read FROM tensor memory: they are
 //                                                                    written back over S^T / dP^T as packed bf16)
 //     dQ_t^T = K_j^T dS^T                                            (dS^T also goes to shared memory, as the B operand)
@@ -84,7 +86,7 @@ __device__ __forceinline__ void load_subtile(uint8_t *dst, const CUtensorMap *ma
 __global__ void __launch_bounds__(BWD2_THREADS, 1)
 attn_bwd2_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                     const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
-                    float *__restrict__ dQacc, const float *__restrict__ lse,
+                    float *__restrict__ dQacc, const float *__restrict__ lse2,
                     const float *__restrict__ Dsum, bf16 *__restrict__ dK, bf16 *__restrict__ dV, int nH, int nKV, int S,
                     long long dk_b, long long dk_h, long long dk_s, long long dv_b, long long dv_h, long long dv_s,
                     float scale, int *status, const float *__restrict__ rope_cos, const float *__restrict__ rope_sin) {
@@ -137,7 +139,7 @@ attn_bwd2_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         const int sub_off = ((st >> 1) & 1) * PAIR_TILE + (st & 1) * 8192;
         load_subtile(sQ + sub_off, &map_q, q0, h, b, &sh->qdo_full[s]);
         load_subtile(sdO + sub_off, &map_do, q0, h, b, &sh->qdo_full[s]);
-        bulk_load_1d(sStat + s * STAT, lse + stat_off, stat_bytes, &sh->qdo_full[s]);
+        bulk_load_1d(sStat + s * STAT, lse2 + stat_off, stat_bytes, &sh->qdo_full[s]);
         bulk_load_1d(sStat + s * STAT + SQ * 4, Dsum + stat_off, stat_bytes, &sh->qdo_full[s]);
       };
       for (int st = 0; st < NQ && st < n_steps; ++st) load_qdo(st);
@@ -266,17 +268,17 @@ attn_bwd2_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 #pragma unroll
         for (int u = 0; u < 8; ++u) {
           const float4 L = *reinterpret_cast<const float4 *>(st_l + u * 4);
-          p[u * 4 + 0] = fast_exp2(__uint_as_float(sv[u * 4 + 0]) * sl2 - L.x * LOG2E);
-          p[u * 4 + 1] = fast_exp2(__uint_as_float(sv[u * 4 + 1]) * sl2 - L.y * LOG2E);
-          p[u * 4 + 2] = fast_exp2(__uint_as_float(sv[u * 4 + 2]) * sl2 - L.z * LOG2E);
-          p[u * 4 + 3] = fast_exp2(__uint_as_float(sv[u * 4 + 3]) * sl2 - L.w * LOG2E);
+          p[u * 4 + 0] = fast_exp2(fmaf(__uint_as_float(sv[u * 4 + 0]), sl2, -L.x));
+          p[u * 4 + 1] = fast_exp2(fmaf(__uint_as_float(sv[u * 4 + 1]), sl2, -L.y));
+          p[u * 4 + 2] = fast_exp2(fmaf(__uint_as_float(sv[u * 4 + 2]), sl2, -L.z));
+          p[u * 4 + 3] = fast_exp2(fmaf(__uint_as_float(sv[u * 4 + 3]), sl2, -L.w));
         }
       } else {
 #pragma unroll
         for (int x = 0; x < 32; ++x) {
           const int q = q0 + x;
           const bool live = q < S && key < S && q >= key;
-          p[x] = live ? fast_exp2(__uint_as_float(sv[x]) * sl2 - st_l[x] * LOG2E) : 0.f;
+          p[x] = live ? fast_exp2(fmaf(__uint_as_float(sv[x]), sl2, -st_l[x])) : 0.f;
         }
       }
 #pragma unroll
@@ -291,16 +293,16 @@ attn_bwd2_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 #pragma unroll
         for (int u = 0; u < 8; ++u) {
           const float4 D = *reinterpret_cast<const float4 *>(st_d + u * 4);
-          const float d0 = p[u * 4 + 0] * (__uint_as_float(sv[u * 4 + 0]) - D.x) * scale, d1 = p[u * 4 + 1] * (__uint_as_float(sv[u * 4 + 1]) - D.y) * scale,
-                      d2 = p[u * 4 + 2] * (__uint_as_float(sv[u * 4 + 2]) - D.z) * scale, d3 = p[u * 4 + 3] * (__uint_as_float(sv[u * 4 + 3]) - D.w) * scale;
+          const float d0 = p[u * 4 + 0] * (__uint_as_float(sv[u * 4 + 0]) - D.x), d1 = p[u * 4 + 1] * (__uint_as_float(sv[u * 4 + 1]) - D.y),
+                      d2 = p[u * 4 + 2] * (__uint_as_float(sv[u * 4 + 2]) - D.z), d3 = p[u * 4 + 3] * (__uint_as_float(sv[u * 4 + 3]) - D.w);
           wd[u * 2] = pack_bf16(d0, d1); wd[u * 2 + 1] = pack_bf16(d2, d3);
         }
       } else {
 #pragma unroll
         for (int x = 0; x < 32; x += 2) {
           // p is zero wherever the entry is masked; the statistics of queries past the end are never loaded
-          const float d0 = p[x] != 0.f ? p[x] * (__uint_as_float(sv[x]) - st_d[x]) * scale : 0.f;
-          const float d1 = p[x + 1] != 0.f ? p[x + 1] * (__uint_as_float(sv[x + 1]) - st_d[x + 1]) * scale : 0.f;
+          const float d0 = p[x] != 0.f ? p[x] * (__uint_as_float(sv[x]) - st_d[x]) : 0.f;
+          const float d1 = p[x + 1] != 0.f ? p[x + 1] * (__uint_as_float(sv[x + 1]) - st_d[x + 1]) : 0.f;
           wd[x >> 1] = pack_bf16(d0, d1);
         }
       }
@@ -332,6 +334,8 @@ attn_bwd2_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         tc::tmem_ld_32x32(t_dv + lane_base + col, g);
         tc::tmem_ld_wait();
         if (key < S) {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) a[e] = __float_as_uint(__uint_as_float(a[e]) * scale);       // dS was left unscaled
           if (rope_cos != nullptr) {
             // gradient of the rotary embedding (inverse rotation, cpp/src/Positional.cpp:207-231) on dK, position = key
             const float *cp = rope_cos + (size_t)key * (HD / 2) + (col >> 1), *sp = rope_sin + (size_t)key * (HD / 2) + (col >> 1);
@@ -373,9 +377,10 @@ attn_bwd2_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
 
 bool attn_bwd2_supported(size_t S, size_t hd) { return hd == 128 && S % 4 == 0 && S >= 4; }
 
-// Dsum must hold rowsum(dO * O) (attn_dsum_kernel of attention_bwd_tc.cu); dQacc: the zeroed fp32 accumulator
+// Dsum must hold rowsum(dO * O) and lse2 the log-sum-exp times log2(e) (attn_dsum_kernel of attention_bwd_tc.cu); dQ comes
+// out WITHOUT the softmax scale (the caller's store kernel multiplies it in); dQacc: the zeroed fp32 accumulator
 // [B*nH*S][128] that the caller afterwards turns into dQ rows.
-int attn_bwd2_tc_run(b200_ctx *ctx, const void *Q, const void *K, const void *V, const void *dO, const float *lse, const float *Dsum,
+int attn_bwd2_tc_run(b200_ctx *ctx, const void *Q, const void *K, const void *V, const void *dO, const float *lse2, const float *Dsum,
                      float *dQacc, void *dK, void *dV, size_t B, size_t nH, size_t nKV, size_t S, const AttnStrides &st,
                      const AttnStrides &gst, const float *rope_cos, const float *rope_sin) {
   CUtensorMap mq, mk, mv, mdo;
@@ -388,7 +393,7 @@ int attn_bwd2_tc_run(b200_ctx *ctx, const void *Q, const void *K, const void *V,
   static bool attr = false;
   if (!attr) { B200_CUDA(ctx, cudaFuncSetAttribute(attn_bwd2_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)); attr = true; }
   dim3 grid((unsigned)(nKV * B), (unsigned)((S + TK - 1) / TK), 1);
-  attn_bwd2_tc_kernel<<<grid, BWD2_THREADS, smem, ctx->stream>>>(mq, mk, mv, mdo, dQacc, lse, Dsum, (bf16 *)dK, (bf16 *)dV, (int)nH, (int)nKV, (int)S,
+  attn_bwd2_tc_kernel<<<grid, BWD2_THREADS, smem, ctx->stream>>>(mq, mk, mv, mdo, dQacc, lse2, Dsum, (bf16 *)dK, (bf16 *)dV, (int)nH, (int)nKV, (int)S,
                                                           gst.k_b, gst.k_h, gst.k_s, gst.v_b, gst.v_h, gst.v_s, 1.0f / sqrtf((float)HD),
                                                           ctx->dev_status, rope_cos, rope_sin);
   B200_LAUNCHED(ctx);

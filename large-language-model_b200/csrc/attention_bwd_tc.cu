@@ -256,12 +256,12 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
   }
 }
 
-// D[b,h,s] = sum_d dO * O.  Eight lanes per (b,s,h) row (16-byte loads for head_dim 128), rows visited with the head
+// D[b,h,s] = sum_d dO * O (and, when asked, lse * log2(e) beside it).  Eight lanes per (b,s,h) row (16-byte loads for head_dim 128), rows visited with the head
 // index fastest so that a token-major tensor is read as one contiguous stream; two rows per lane group in flight.
 template <int HD>
 __global__ void __launch_bounds__(256)
 attn_dsum_kernel(const bf16 *__restrict__ O, const bf16 *__restrict__ dO, float *__restrict__ D, int B, int nH, int S,
-                 long long o_b, long long o_h, long long o_s) {
+                 long long o_b, long long o_h, long long o_s, const float *__restrict__ lse, float *__restrict__ lse2) {
   constexpr int VEC = HD / 8;                       // elements per lane: 16 (32 bytes) or 8 (16 bytes)
   typedef typename std::conditional<VEC == 16, uint4, uint2>::type Raw;   // loaded in 16- or 8-byte pieces
   constexpr int PIECES = VEC * 2 / (int)sizeof(Raw);
@@ -290,7 +290,9 @@ attn_dsum_kernel(const bf16 *__restrict__ O, const bf16 *__restrict__ dO, float 
     acc += __shfl_xor_sync(0xffffffffu, acc, 1);
     if (sub == 0 && r < rows) {
       const int h = (int)(r % nH), s = (int)((r / nH) % S), b = (int)(r / ((long long)nH * S));
-      D[((long long)b * nH + h) * S + s] = acc;
+      const long long at = ((long long)b * nH + h) * S + s;
+      D[at] = acc;
+      if (lse2) lse2[at] = lse[at] * LOG2E;             // the row's log-sum-exp in base-2 units for the second backward form
     }
   };
   for (long long r0 = group * 2; r0 < rows; r0 += n_groups * 2) {      // the shuffles need every lane: rows past the end are clamped
@@ -305,13 +307,14 @@ attn_dsum_kernel(const bf16 *__restrict__ O, const bf16 *__restrict__ dO, float 
 // fp32 [B,nH,S,hd] accumulator -> strided bf16 dQ
 __global__ void attn_dq_store_kernel(const float *__restrict__ acc, bf16 *__restrict__ dQ, int B, int nH, int S,
                                      int hd, long long q_b, long long q_h, long long q_s,
-                                     const float *__restrict__ rope_cos, const float *__restrict__ rope_sin) {
+                                     const float *__restrict__ rope_cos, const float *__restrict__ rope_sin, float mul) {
   const size_t total = (size_t)B * nH * S * (hd / 8);
   for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
     const int u = (int)(idx % (hd / 8)); size_t r = idx / (hd / 8);
     const int s = (int)(r % S); r /= S;
     const int h = (int)(r % nH), b = (int)(r / nH);
     float4 x = *reinterpret_cast<const float4 *>(acc + idx * 8), y = *reinterpret_cast<const float4 *>(acc + idx * 8 + 4);
+    x.x *= mul; x.y *= mul; x.z *= mul; x.w *= mul; y.x *= mul; y.y *= mul; y.z *= mul; y.w *= mul;   // 1, or the softmax scale
     if (rope_cos != nullptr) {   // gradient of the rotary embedding on dQ: inverse rotation at position s
       const float4 c = *reinterpret_cast<const float4 *>(rope_cos + (size_t)s * (hd / 2) + u * 4);
       const float4 n = *reinterpret_cast<const float4 *>(rope_sin + (size_t)s * (hd / 2) + u * 4);
@@ -328,7 +331,7 @@ __global__ void attn_dq_store_kernel(const float *__restrict__ acc, bf16 *__rest
 }  // namespace
 
 bool attn_bwd2_supported(size_t S, size_t hd);
-int attn_bwd2_tc_run(b200_ctx *ctx, const void *Q, const void *K, const void *V, const void *dO, const float *lse, const float *Dsum,
+int attn_bwd2_tc_run(b200_ctx *ctx, const void *Q, const void *K, const void *V, const void *dO, const float *lse2, const float *Dsum,
                      float *dQacc, void *dK, void *dV, size_t B, size_t nH, size_t nKV, size_t S, const AttnStrides &st,
                      const AttnStrides &gst, const float *rope_cos, const float *rope_sin);
 
@@ -340,19 +343,19 @@ int bwd_launch_t(b200_ctx *ctx, const void *Q, const void *K, const void *V, con
   const size_t rows = B * nH * S;
   // scratch: D [rows] fp32, dQ accumulator [rows, HD] fp32 (zeroed here, added to by TMA reduce)
   const size_t d_elems = ((rows + 63) / 64) * 64;
-  float *scr = (float *)b200_scratch(ctx, (d_elems + rows * HD) * sizeof(float));
+  float *scr = (float *)b200_scratch(ctx, (2 * d_elems + rows * HD) * sizeof(float));
   if (!scr) return B200_ERR_NOMEM;
-  float *Dsum = scr, *dQacc = scr + d_elems;
-  const bool second_form = HD == 128 && ctx->attn_bwd2 && attn_bwd2_supported(S, HD) && (uintptr_t)lse % 16 == 0;
+  float *Dsum = scr, *lse2 = scr + d_elems, *dQacc = scr + 2 * d_elems;
+  const bool second_form = HD == 128 && ctx->attn_bwd2 && attn_bwd2_supported(S, HD);
   B200_CUDA(ctx, cudaMemsetAsync(dQacc, 0, rows * HD * sizeof(float), ctx->stream));
   {
     size_t blocks = (rows + 63) / 64, cap = (size_t)ctx->sm_count * 16;      // 32 lane groups x 2 rows per block pass
     attn_dsum_kernel<HD><<<(int)(blocks < cap ? blocks : cap), 256, 0, ctx->stream>>>((const bf16 *)O, (const bf16 *)dO, Dsum, (int)B, (int)nH, (int)S,
-                                                                                      st.o_b, st.o_h, st.o_s);
+                                                                                      st.o_b, st.o_h, st.o_s, lse, second_form ? lse2 : nullptr);
     B200_LAUNCHED(ctx);
   }
   if (second_form) {
-    int rc = attn_bwd2_tc_run(ctx, Q, K, V, dO, lse, Dsum, dQacc, dK, dV, B, nH, nKV, S, st, gst, rope_cos, rope_sin);
+    int rc = attn_bwd2_tc_run(ctx, Q, K, V, dO, lse2, Dsum, dQacc, dK, dV, B, nH, nKV, S, st, gst, rope_cos, rope_sin);
     if (rc != B200_OK) return rc;
   } else {
     CUtensorMap mq, mk, mv, mdo, mdq;
@@ -371,7 +374,8 @@ int bwd_launch_t(b200_ctx *ctx, const void *Q, const void *K, const void *V, con
   }
   {
     size_t items = rows * (HD / 8), blocks = (items + 255) / 256, cap = (size_t)ctx->sm_count * 16;
-    attn_dq_store_kernel<<<(int)(blocks < cap ? blocks : cap), 256, 0, ctx->stream>>>(dQacc, (bf16 *)dQ, (int)B, (int)nH, (int)S, HD, gst.q_b, gst.q_h, gst.q_s, rope_cos, rope_sin);
+    attn_dq_store_kernel<<<(int)(blocks < cap ? blocks : cap), 256, 0, ctx->stream>>>(dQacc, (bf16 *)dQ, (int)B, (int)nH, (int)S, HD, gst.q_b, gst.q_h, gst.q_s, rope_cos, rope_sin,
+                                                                                      second_form ? 1.0f / sqrtf((float)HD) : 1.0f);
     B200_LAUNCHED(ctx);
   }
   return B200_OK;

@@ -121,8 +121,16 @@ def test_optimizer_in_backward_order_gives_the_same_update(ctx, monkeypatch):
         m.close()
     (l0, p0, (m0, v0, s0)), (l1, p1, (m1, v1, s1)) = results
     assert s0 == s1 == 4
-    # gradients are not bit-reproducible between runs (fp32 atomics in the embedding and attention gradients) and AdamW
-    # normalises them, so near-zero gradients can move a weight by a fraction of lr; a bucket that missed or doubled an
-    # update would differ by ~1e-1 here
-    np.testing.assert_allclose(l0, l1, rtol=1e-3)
-    assert rel(p1, p0) < 1e-3 and rel(m1, m0) < 1e-3 and rel(v1, v0) < 1e-3
+    # Gradients are not bit-reproducible between runs (fp32 atomics in the embedding and attention gradients) and AdamW
+    # normalises them: a gradient near zero can flip its sign and move that weight by a whole lr step, and its moments
+    # with it.  So the check counts elements instead of taking a norm: a bucket that missed or doubled one of the four
+    # updates would move EVERY weight of the bucket (>= 5 % of the model) by about lr and its moments by about a quarter.
+    lr = 1e-2
+    np.testing.assert_allclose(l0, l1, rtol=5e-3)
+    moved = np.mean(np.abs(p1 - p0) > 0.25 * lr)
+    # (bf16 activations turn a reordered fp32 sum into an occasional different rounding, so moments of typical size agree
+    # to a fraction of a percent while those near zero can be off by more than their own size: hence the absolute floor)
+    rms = lambda a: float(np.sqrt(np.mean(np.square(a, dtype=np.float64))))
+    m_off = np.mean(np.abs(m1 - m0) > 0.1 * np.abs(m0) + 0.05 * rms(m0))
+    v_off = np.mean(np.abs(v1 - v0) > 0.1 * np.abs(v0) + 0.05 * rms(v0))
+    assert moved < 0.01 and m_off < 0.01 and v_off < 0.01, (moved, m_off, v_off)
