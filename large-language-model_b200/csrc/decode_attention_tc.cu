@@ -31,6 +31,7 @@ struct DecTcArgs {
   bf16 *kc, *vc, *o;                   // caches [B, S_max, nKV*128]; output rows [B, ldo]
   const int *pos_dev;                  // when set: the new token's position is *pos_dev instead of t_len - 1
   int nKV, G, S_max, t_len, ldq, ldo;
+  int early_tiles;                     // K tiles that hold only positions written before this step's kernels started
   float scale;
   int *status;
 };
@@ -89,6 +90,17 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
   tc::tc_fence_after();
   const uint32_t tmem_base = sh->tmem_base, t_o = tmem_base + 16 * NT;
   pdl_launch_dependents();
+  // Cache tiles of positions that were complete before this token step began depend on no kernel still running: their
+  // loads go out before the wait on the previous kernel (with a captured step the host-side length is a lower bound:
+  // replays only move forward).
+  const int n_early = min(a.early_tiles, NS);
+  if (warp == TMA_W && lane == 0) {
+    for (int i = 0; i < n_early; ++i) {
+      tc::mbar_expect_tx(&sh->full[i], TILE);
+      tma_load_4d(ring + i * TILE, &map_k, 0, i * KEYS, kvh, b, &sh->full[i]);
+      tma_load_4d(ring + i * TILE + 16384, &map_k, 64, i * KEYS, kvh, b, &sh->full[i]);
+    }
+  }
   pdl_wait();
 
   const int pos = a.pos_dev ? *a.pos_dev : a.t_len - 1;        // position of the new token
@@ -98,7 +110,7 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
 
   if (warp == TMA_W) {
     if (lane == 0) {
-      for (int i = 0; i < 2 * nt; ++i) {                          // K tiles, then V tiles
+      for (int i = n_early; i < 2 * nt; ++i) {                    // K tiles, then V tiles
         const int slot = i % NS;
         if (i >= NS && !tc::mbar_wait(&sh->empty[slot], ((i / NS) - 1) & 1, a.status, abort_flag, 351)) break;
         const CUtensorMap *map = i < nt ? &map_k : &map_v;
@@ -307,6 +319,10 @@ int attn_decode_tc(b200_ctx *ctx, const void *q, const void *k_new, const void *
   a.nKV = (int)nKV; a.G = (int)G; a.S_max = (int)S_max; a.t_len = (int)t_len; a.ldq = (int)ldq; a.ldo = (int)ldo;
   a.scale = 1.0f / sqrtf((float)HD);
   a.status = ctx->dev_status;
+  {
+    const size_t cached_at_least = k_new ? t_len - 1 : t_len;     // positions in the cache (a lower bound when pos_dev is set)
+    a.early_tiles = (int)(cached_at_least / KEYS);
+  }
   dim3 grid((unsigned)nKV, (unsigned)B, 1);
   if (G > 4) return launch_tc<8, 8>(ctx, mk, mv, a, grid);
   if (S_max <= 1024) return launch_tc<4, 8>(ctx, mk, mv, a, grid);
