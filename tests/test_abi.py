@@ -31,6 +31,13 @@ def test_library_exports_every_declared_symbol(lib):
     assert not missing, missing
 
 
+def test_kernel_choice_hooks_of_the_gpu_tests_exist(lib):
+    """The GPU parity tests run both forms of a kernel through these undeclared A/B hooks."""
+    for name in ("b200_internal_set_gemm_2cta", "b200_internal_set_gemm_skinny", "b200_internal_set_attn_fwd2",
+                 "b200_internal_set_attn_bwd2", "b200_internal_set_attn_decode_tc"):
+        assert hasattr(lib, name), name
+
+
 def test_python_binding_covers_the_header():
     assert sorted(bridge.EXPORTED_SYMBOLS) == header_symbols()
 
