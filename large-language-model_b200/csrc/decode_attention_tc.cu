@@ -119,6 +119,9 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
         tma_load_4d(ring + slot * TILE, map, 0, key0, kvh, b, &sh->full[slot]);
         tma_load_4d(ring + slot * TILE + 16384, map, 64, key0, kvh, b, &sh->full[slot]);
       }
+      // early loads nobody will consume (only if a captured step were replayed at an earlier position than it was
+      // captured at) must still land before the CTA gives its shared memory back
+      for (int i = nt; i < n_early; ++i) tc::mbar_wait(&sh->full[i], 0, a.status, abort_flag, 358);
     }
   } else if (warp == MMA_W) {
     if (lane == 0) {
