@@ -153,6 +153,13 @@ int b200_fused_attn_bwd(b200_ctx *ctx, const void *Q, const void *K, const void 
                         void *dK, void *dV, size_t batch, size_t n_heads, size_t n_kv, size_t seq_len,
                         size_t head_dim, b200_dtype dtype);
 
+/* The same backward for callers that kept the forward call's output O and lse (b200_flash_attn_fwd): nothing is
+ * recomputed and nothing is allocated.  The reference has no such entry (its shader recomputes the forward,
+ * cpp/src/gpu_kernel/fused_attn_bwd.metal:26-254); this is the form the engine and the benchmark use. */
+int b200_flash_attn_bwd(b200_ctx *ctx, const void *Q, const void *K, const void *V, const void *O, const void *dO,
+                        const float *lse, void *dQ, void *dK, void *dV, size_t batch, size_t n_heads, size_t n_kv,
+                        size_t seq_len, size_t head_dim, b200_dtype dtype);
+
 /* ---- embedding gather: metal_bridge::embedding_forward (MetalBridge.hpp:86-88) */
 int b200_embedding_forward(b200_ctx *ctx, const uint32_t *token_ids, const void *table, void *output,
                            size_t total_tokens, size_t hidden_dim, size_t vocab_size, b200_dtype dtype);
@@ -165,6 +172,25 @@ int b200_embedding_backward(b200_ctx *ctx, const uint32_t *token_ids, const void
  * grad_logits has dtype `dtype` and may alias logits. */
 int b200_cross_entropy(b200_ctx *ctx, const void *logits, const uint32_t *targets, float *loss_out,
                        void *grad_logits, size_t total_tokens, size_t vocab_size, b200_dtype dtype);
+
+/* ---- vocabulary projection fused with cross-entropy: the tail of Transformer::forward (logits = x * W,
+ * cpp/src/Transformer.cpp:190-196) + CrossEntropyLoss::forward (cpp/src/Loss.cpp:43-135) in one call.
+ * x [tokens, hidden], w [hidden, vocab] ([in,out] like every weight).  loss_out (device float) receives the mean loss,
+ * lse_out (device fp32 [tokens]) the log-sum-exp of every row.  bf16: one tensor-core GEMM whose epilogue reduces the
+ * fp32 accumulators to per-row softmax statistics; with logits_out == NULL the logits are never written to memory.
+ * logits_out (optional, [tokens, vocab], dtype) additionally receives the logits.  fp32 inputs, or shapes the tensor-core
+ * kernel does not take (vocab or hidden not a multiple of 8), run GEMM + statistics with the logits in logits_out or in
+ * the context workspace. */
+int b200_vocab_ce_forward(b200_ctx *ctx, const void *x, const void *w, const uint32_t *targets, float *loss_out,
+                          float *lse_out, void *logits_out, size_t tokens, size_t vocab, size_t hidden, b200_dtype dtype);
+/* CrossEntropyLoss::backward + the output-projection gradients (cpp/src/Loss.cpp:147-197,
+ * cpp/src/Transformer.cpp:515-521, 607-627).  dlogits [tokens, vocab] (dtype) is a caller-owned work array that
+ * receives (softmax - onehot)/tokens: with logits_in_place != 0 it must hold the logits written by the forward call
+ * and is converted in one pass; otherwise the projection is run again with the gradient as its epilogue.
+ * grad_w (optional, fp32 [hidden, vocab]) = x^T * dlogits; grad_x (optional, dtype, [tokens, hidden]) = dlogits * w^T. */
+int b200_vocab_ce_backward(b200_ctx *ctx, const void *x, const void *w, const uint32_t *targets, const float *lse,
+                           void *dlogits, int logits_in_place, float *grad_w, void *grad_x, size_t tokens, size_t vocab,
+                           size_t hidden, b200_dtype dtype);
 
 /* ---- cross-entropy for callers that must not allocate device memory.
  * No counterpart in the reference.  Same inputs, outputs and results as b200_cross_entropy, but the
@@ -304,6 +330,9 @@ int b200_metrics_append(const char *path, size_t step, double train_loss, double
 int b200_dp_unique_id(void *out128);                     /* rank 0: ncclGetUniqueId */
 int b200_dp_init(b200_model *m, const void *unique_id128, int rank, int world);
 int b200_dp_shutdown(b200_model *m);
+/* Order-fixed fp64 sum and sum of squares of the model's fp32 master weights (host outputs; synchronises).  Replicas
+ * that hold identical weights return bit-identical values: the check that data-parallel ranks have not drifted. */
+int b200_model_param_checksum(b200_model *m, double *sum, double *sum_sq);
 
 /* ======================= host-pointer calls (the reference's calling convention) =========
  * Same semantics as the device calls, but every pointer is a HOST pointer:

@@ -92,10 +92,13 @@ _SIGS = {
     "b200_reshape_to_3d": (_i, [_vp, _vp, _vp, _sz, _sz, _sz, _sz, _i]),
     "b200_flash_attn_fwd": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _sz, _sz, _sz, _sz, _sz, _i]),
     "b200_fused_attn_bwd": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _sz, _sz, _sz, _sz, _i]),
+    "b200_flash_attn_bwd": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _sz, _sz, _sz, _sz, _i]),
     "b200_embedding_forward": (_i, [_vp, _vp, _vp, _vp, _sz, _sz, _sz, _i]),
     "b200_embedding_backward": (_i, [_vp, _vp, _vp, _vp, _sz, _sz, _sz, _i]),
     "b200_cross_entropy": (_i, [_vp, _vp, _vp, _vp, _vp, _sz, _sz, _i]),
     "b200_cross_entropy_noalloc": (_i, [_vp, _vp, _vp, _vp, _vp, _sz, _sz, _i]),
+    "b200_vocab_ce_forward": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _sz, _sz, _i]),
+    "b200_vocab_ce_backward": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _sz, _sz, _sz, _i]),
     "b200_adamw_step": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _sz, C.POINTER(AdamWParams)]),
     "b200_model_create": (_i, [_vp, C.POINTER(ModelConfig), _i, _sz, _i, C.POINTER(_vp)]),
     "b200_model_destroy": (_i, [_vp]),
@@ -132,6 +135,7 @@ _SIGS = {
     "b200_dp_unique_id": (_i, [_vp]),
     "b200_dp_init": (_i, [_vp, _vp, _i, _i]),
     "b200_dp_shutdown": (_i, [_vp]),
+    "b200_model_param_checksum": (_i, [_vp, C.POINTER(C.c_double), C.POINTER(C.c_double)]),
     "b200_host_gemm": (_i, [_vp, _vp, _vp, _vp, _sz, _sz, _sz, _i, _i, _i]),
     "b200_host_rms_norm_forward": (_i, [_vp, _vp, _vp, _vp, _f, _sz, _sz]),
     "b200_host_flash_attn_fwd": (_i, [_vp, _vp, _vp, _vp, _vp, _sz, _sz, _sz, _sz, _sz]),
@@ -361,6 +365,14 @@ class Context:
                                                  k.shape[1], S, hd, q.code))
         return dq, dk, dv
 
+    def flash_attn_bwd(self, q, k, v, o, dO, lse, out=None):
+        """Backward from the forward call's saved output and log-sum-exp; returns (dq, dk, dv)."""
+        B, nH, S, hd = q.shape
+        dq, dk, dv = out if out is not None else (self.empty(q.shape, q.dtype), self.empty(k.shape, q.dtype), self.empty(v.shape, q.dtype))
+        self._check(self.lib.b200_flash_attn_bwd(self.h, q.ptr, k.ptr, v.ptr, o.ptr, dO.ptr, lse.ptr, dq.ptr, dk.ptr, dv.ptr,
+                                                 B, nH, k.shape[1], S, hd, q.code))
+        return dq, dk, dv
+
     def embedding_forward(self, ids, table):
         V, H = table.shape
         out = self.empty((ids.size, H), table.dtype)
@@ -373,13 +385,33 @@ class Context:
         self._check(self.lib.b200_embedding_backward(self.h, ids.ptr, gh.ptr, gt.ptr, ids.size, H, V, gh.code))
         return gt
 
-    def cross_entropy(self, logits, targets, want_grad=True):
+    def cross_entropy(self, logits, targets, want_grad=True, in_place=False):
+        """Mean loss and (softmax - onehot)/tokens; in_place writes the gradient over the logits."""
         T, V = logits.size // logits.shape[-1], logits.shape[-1]
         loss = self.empty((1,), "f32")
-        grad = self.empty(logits.shape, logits.dtype) if want_grad else None
+        grad = (logits if in_place else self.empty(logits.shape, logits.dtype)) if want_grad else None
         self._check(self.lib.b200_cross_entropy(self.h, logits.ptr, targets.ptr, loss.ptr, grad.ptr if grad else None,
                                                 T, V, logits.code))
         return loss, grad
+
+    def vocab_ce_forward(self, x, w, targets, want_logits=False):
+        """Vocabulary projection + mean cross-entropy in one call: (loss, lse[, logits]) device arrays."""
+        (T, H), V = x.shape, w.shape[1]
+        loss, lse = self.empty((1,), "f32"), self.empty((T,), "f32")
+        logits = self.empty((T, V), x.dtype) if want_logits else None
+        self._check(self.lib.b200_vocab_ce_forward(self.h, x.ptr, w.ptr, targets.ptr, loss.ptr, lse.ptr,
+                                                   logits.ptr if want_logits else None, T, V, H, x.code))
+        return (loss, lse, logits) if want_logits else (loss, lse)
+
+    def vocab_ce_backward(self, x, w, targets, lse, logits=None):
+        """Gradients of the mean loss: (dlogits, grad_w fp32 [H,V], grad_x [T,H]).  `logits` (from the forward call) is
+        converted in place; without it the projection is run again with the gradient as its epilogue."""
+        (T, H), V = x.shape, w.shape[1]
+        dl = logits if logits is not None else self.empty((T, V), x.dtype)
+        gw, gx = self.empty((H, V), "f32"), self.empty((T, H), x.dtype)
+        self._check(self.lib.b200_vocab_ce_backward(self.h, x.ptr, w.ptr, targets.ptr, lse.ptr, dl.ptr, int(logits is not None),
+                                                    gw.ptr, gx.ptr, T, V, H, x.code))
+        return dl, gw, gx
 
     def cross_entropy_noalloc(self, logits, targets, loss, grad=None):
         """Cross-entropy through the entry point that allocates nothing: the caller supplies every
@@ -561,6 +593,12 @@ class Model:
         self.ctx._check(self.ctx.lib.b200_model_generate(self.h, _np_ptr(prompt), B, P, new_tokens, C.byref(sampler),
                                                          _np_ptr(out), C.byref(pm), C.byref(dm)))
         return out, float(pm.value), float(dm.value)
+
+    def param_checksum(self):
+        """(sum, sum of squares) of the fp32 master weights, fixed summation order (replica-drift check)."""
+        a, b = C.c_double(), C.c_double()
+        self.ctx._check(self.ctx.lib.b200_model_param_checksum(self.h, C.byref(a), C.byref(b)))
+        return a.value, b.value
 
     def dp_init(self, unique_id: bytes, rank: int, world: int):
         buf = C.create_string_buffer(unique_id, 128)

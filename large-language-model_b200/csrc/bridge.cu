@@ -344,6 +344,16 @@ extern "C" int b200_fused_attn_bwd(b200_ctx *ctx, const void *Q, const void *K, 
   return rc;
 }
 
+// Backward from what the forward call left behind (its output and log-sum-exp): what a training engine calls,
+// no recomputation and no temporaries.
+extern "C" int b200_flash_attn_bwd(b200_ctx *ctx, const void *Q, const void *K, const void *V, const void *O, const void *dO,
+                                   const float *lse, void *dQ, void *dK, void *dV, size_t B, size_t nH, size_t nKV,
+                                   size_t S, size_t hd, b200_dtype dt) {
+  if (!ctx) return B200_ERR_INVALID;
+  AttnStrides st = ref_layout(nH, nKV, S, hd);
+  return attn_bwd_launch(ctx, Q, K, V, O, dO, lse, dQ, dK, dV, B, nH, nKV, S, hd, st, st, dt);
+}
+
 // --------------------------------------------------- host-pointer calls --
 namespace {
 struct DevBuf {

@@ -147,7 +147,20 @@ struct GemmEpilogue {
   int swiglu_I = 0;
   void *act_out = nullptr;
   size_t ld_act = 0;
+  // Cross-entropy over the columns of C = A*W (the vocabulary projection), two-CTA kernel only.  Row r has target
+  // column ce_targets[r]; a "tile" is one 256-column block of C (gemm_tc2_ce_tiles(N) of them).
+  //   ce_mode 1: C is NOT stored.  For every (row, tile) the epilogue writes max_j(x*log2e) to ce_part_max[tile*M + r]
+  //              and sum_j exp2(x*log2e - max) to ce_part_sum[tile*M + r]; the tile that holds the target column also
+  //              writes that logit to ce_tgt_logit[r].
+  //   ce_mode 2: the same statistics, taken from the bf16-rounded values, and C is stored as usual.
+  //   ce_mode 3: C = (exp(x - ce_lse[r]) - [column == target]) * ce_scale  (the gradient of the mean loss).
+  int ce_mode = 0;
+  const uint32_t *ce_targets = nullptr;
+  float *ce_part_max = nullptr, *ce_part_sum = nullptr, *ce_tgt_logit = nullptr;
+  const float *ce_lse = nullptr;
+  float ce_scale = 0.f;
 };
+size_t gemm_tc2_ce_tiles(size_t N);   // number of column tiles the cross-entropy epilogue reports per row
 int gemm_tc_launch(b200_ctx *ctx, const void *A, const void *B, void *C, size_t M, size_t N, size_t K, int ta, int tb,
                    int acc, b200_dtype out_dt, size_t lda, size_t ldb, size_t ldc, const GemmEpilogue *epi = nullptr);
 int gemm_tc2_launch(b200_ctx *ctx, const void *A, const void *B, void *C, size_t M, size_t N, size_t K, int ta, int tb,

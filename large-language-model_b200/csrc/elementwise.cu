@@ -623,16 +623,22 @@ extern "C" int b200_embedding_backward(b200_ctx *ctx, const uint32_t *ids, const
 // One CTA per token: max, sum-exp, then (softmax - onehot)/tokens; per-token
 // loss = -log(max(p_target, 1e-15)) (cpp/src/Loss.cpp:84-119, 163-194).  The
 // mean is a second, deterministic single-CTA reduction (no float atomics).
+// grad may be the same array as logits (neither pointer is __restrict__): a thread overwrites only
+// elements it has read itself in the same pass, and the target logit is read before the first
+// block-wide barrier, i.e. before any thread can have reached the gradient pass of this row.
 template <class T>
 __global__ void __launch_bounds__(512)
-ce_token_kernel(const T *__restrict__ logits, const uint32_t *__restrict__ targets, float *__restrict__ tok_loss,
-                T *__restrict__ grad, size_t tokens, size_t V) {
+ce_token_kernel(const T *logits, const uint32_t *__restrict__ targets, float *__restrict__ tok_loss,
+                T *grad, size_t tokens, size_t V) {
   __shared__ float red[32];
   constexpr int N = Vec16<T>::N;
   const bool vec = (V % N == 0) && ((uintptr_t)logits % 16 == 0) && (!grad || (uintptr_t)grad % 16 == 0);
   const float inv_tokens = 1.0f / (float)tokens;
   for (size_t t = blockIdx.x; t < tokens; t += gridDim.x) {
     const T *lr = logits + t * V;
+    const uint32_t tgt = targets[t];
+    float tgt_logit = 0.f;
+    if (threadIdx.x == 0 && tgt < V) tgt_logit = to_f(lr[tgt]);
     float mx = -INFINITY;
     if (vec) {
       for (size_t v = threadIdx.x; v < V / N; v += blockDim.x) {
@@ -651,9 +657,8 @@ ce_token_kernel(const T *__restrict__ logits, const uint32_t *__restrict__ targe
       }
     } else for (size_t v = threadIdx.x; v < V; v += blockDim.x) sum += __expf(to_f(lr[v]) - mx);
     sum = block_sum(sum, red);
-    uint32_t tgt = targets[t];
     if (threadIdx.x == 0) {
-      float pt = (tgt < V) ? __expf(to_f(lr[tgt]) - mx) / sum : 0.f;
+      float pt = (tgt < V) ? __expf(tgt_logit - mx) / sum : 0.f;
       tok_loss[t] = -logf(fmaxf(pt, 1e-15f));
     }
     if (grad) {
@@ -684,6 +689,12 @@ __global__ void mean_kernel(const float *__restrict__ v, float *__restrict__ out
   for (size_t i = threadIdx.x; i < n; i += blockDim.x) s += v[i];
   s = block_sum(s, red);
   if (threadIdx.x == 0) *out = s / (float)n;
+}
+// Deterministic mean of n floats into *out (one CTA, fixed summation order).
+int mean_launch(b200_ctx *ctx, const float *v, float *out, size_t n) {
+  mean_kernel<<<1, 1024, 0, ctx->stream>>>(v, out, n);
+  B200_LAUNCHED(ctx);
+  return B200_OK;
 }
 extern "C" int b200_cross_entropy(b200_ctx *ctx, const void *logits, const uint32_t *targets, float *loss_out,
                                   void *grad, size_t tokens, size_t V, b200_dtype dt) {
@@ -857,10 +868,17 @@ extern "C" int b200_cross_entropy_noalloc(b200_ctx *ctx, const void *logits, con
   if (!tokens) return B200_OK;
   B200_REQUIRE(ctx, ctx->device >= 0 && ctx->device < 64, "cross_entropy_noalloc: device ordinal out of range");
   if (!g_ce_noalloc_dev_ptr[ctx->device]) {
-    // The array's name is only a host-side handle here; kernels need its device address.
-    B200_CUDA(ctx, cudaSetDevice(ctx->device));
+    // The array's name is only a host-side handle here; kernels need its device address.  The lookup
+    // answers for the CURRENT device, so the context's device is made current for it and the
+    // caller's own choice of device is put back afterwards.
+    int prev = -1;
+    B200_CUDA(ctx, cudaGetDevice(&prev));
+    if (prev != ctx->device) B200_CUDA(ctx, cudaSetDevice(ctx->device));
     float *p = nullptr;
-    B200_CUDA(ctx, cudaGetSymbolAddress((void **)&p, g_ce_noalloc_token_loss));
+    const cudaError_t e = cudaGetSymbolAddress((void **)&p, g_ce_noalloc_token_loss);
+    if (prev != ctx->device) cudaSetDevice(prev);
+    if (e != cudaSuccess || !p)
+      return b200_fail(ctx, B200_ERR_CUDA, "cross_entropy_noalloc: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
     g_ce_noalloc_dev_ptr[ctx->device] = p;
   }
   float *tok_loss = g_ce_noalloc_dev_ptr[ctx->device];

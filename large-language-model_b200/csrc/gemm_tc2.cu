@@ -133,6 +133,73 @@ __device__ __forceinline__ void store_chunk(uint32_t (&r)[32], TO *crow, int row
   }
 }
 
+__device__ __forceinline__ float ex2(float x) { float y; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
+constexpr float LOG2E = 1.4426950408889634f;
+
+// Cross-entropy epilogue of one accumulator row (one thread) over the 256 columns of a tile; see GemmEpilogue::ce_mode.
+// Softmax statistics are kept in base-2 units (x * log2e): one FMA and one ex2 per element.
+__device__ __forceinline__ void ce_row_epilogue(uint32_t taddr, bf16 *crow, int row, int tn, int M, int N, const GemmEpilogue &epi) {
+  const bool row_ok = row < M;
+  const uint32_t tgt = row_ok ? __ldg(epi.ce_targets + row) : 0xffffffffu;
+  const int col0 = tn * BN;
+  if (epi.ce_mode == 3) {
+    const float lse2 = row_ok ? __ldg(epi.ce_lse + row) * LOG2E : 0.f;
+#pragma unroll 1
+    for (int c = 0; c < BN / 32; ++c) {
+      uint32_t r[32];
+      __syncwarp();                 // rows past M skip the arithmetic below; the tensor-memory load wants the whole warp
+      tc::tmem_ld_32x32(taddr + c * 32, r);
+      tc::tmem_ld_wait();
+      const int col = col0 + c * 32;
+      if (row_ok && col < N) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          float p = ex2(fmaf(__uint_as_float(r[j]), LOG2E, -lse2));
+          if ((uint32_t)(col + j) == tgt) p -= 1.0f;
+          r[j] = __float_as_uint(p * epi.ce_scale);
+        }
+        store_chunk<bf16, false>(r, crow, row, col, N, epi, false);
+      }
+    }
+    return;
+  }
+  float m2 = -1e30f, s = 0.f, tl = 0.f;
+#pragma unroll 1
+  for (int c = 0; c < BN / 32; ++c) {
+    uint32_t r[32];
+    __syncwarp();
+    tc::tmem_ld_32x32(taddr + c * 32, r);
+    tc::tmem_ld_wait();
+    const int col = col0 + c * 32;
+    if (!(row_ok && col < N)) continue;
+    if (epi.ce_mode == 2) {
+      // the stored logits are bf16: take the statistics from the rounded values, which is what a later pass reads back
+#pragma unroll
+      for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__bfloat162float(__float2bfloat16_rn(__uint_as_float(r[j]))));
+    }
+    if (tgt - (uint32_t)col < 32u) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) if ((uint32_t)(col + j) == tgt) tl = __uint_as_float(r[j]);
+    }
+    float t[32], cm = -1e30f;
+    const int valid = N - col;      // columns past N hold the zero fill of the weight tile: not part of the softmax
+#pragma unroll
+    for (int j = 0; j < 32; ++j) { t[j] = (j < valid) ? __uint_as_float(r[j]) * LOG2E : -1e30f; cm = fmaxf(cm, t[j]); }
+    const float mn = fmaxf(m2, cm);
+    float acc = 0.f;
+#pragma unroll
+    for (int j = 0; j < 32; ++j) acc += ex2(t[j] - mn);
+    s = s * ex2(m2 - mn) + acc;
+    m2 = mn;
+    if (epi.ce_mode == 2) store_chunk<bf16, false>(r, crow, row, col, N, epi, false);
+  }
+  if (row_ok) {
+    epi.ce_part_max[(size_t)tn * M + row] = m2;
+    epi.ce_part_sum[(size_t)tn * M + row] = s;
+    if (tgt - (uint32_t)col0 < (uint32_t)BN && tgt < (uint32_t)N) epi.ce_tgt_logit[row] = tl;
+  }
+}
+
 template <bool A_MN, bool B_MN, class TO, bool ACC>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
@@ -250,6 +317,14 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN;
       TO *crow = C + (size_t)row * ldc;
       if constexpr (sizeof(TO) == 2 && !ACC) {
+        if (epi.ce_mode) {
+          ce_row_epilogue(taddr, (bf16 *)crow, row, tn, M, N, epi);
+          tc::tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive_cluster(tc::smem_u32(&sh->acc_empty[acc]) & LEADER_MASK);
+          if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+          continue;
+        }
         if (swiglu) {
           bf16 *arow = (bf16 *)epi.act_out + (size_t)row * epi.ld_act;
 #pragma unroll 1
@@ -341,7 +416,6 @@ int launch_variant(b200_ctx *ctx, const CUtensorMap &ma, const CUtensorMap &mb, 
     double best = eff(1);
     for (int s = 2; s <= 4; ++s)
       if (num_kb / s >= 16 && eff(s) > best + 0.08) { best = eff(s); splits = s; }
-    if (splits > 1 && !ACC) B200_CUDA(ctx, cudaMemsetAsync(C, 0, (size_t)M * N * sizeof(float), ctx->stream));
   }
   const int items = pairs * splits;
   const int clusters = items < max_clusters ? items : max_clusters;
@@ -352,6 +426,8 @@ int launch_variant(b200_ctx *ctx, const CUtensorMap &ma, const CUtensorMap &mb, 
     tm.start = ev(); tm.stop = ev(); tm.flops = 2.0 * M * N * K;
     cudaEventRecord(tm.start, ctx->stream);
   }
+  // the clear that split-K needs is part of the GEMM's cost: it sits inside the timed interval
+  if (splits > 1 && !ACC) B200_CUDA(ctx, cudaMemsetAsync(C, 0, (size_t)M * N * sizeof(float), ctx->stream));
   B200_CUDA(ctx, cudaLaunchKernelEx(&cfg, kern, ma, mb, (TO *)C, M, N, K, ldc, ctx->dev_status, epi, splits));
   ctx->launches++;
   if (ctx->time_gemm) { cudaEventRecord(tm.stop, ctx->stream); ctx->timed.push_back(tm); }
@@ -377,6 +453,11 @@ int gemm_tc2_launch(b200_ctx *ctx, const void *A, const void *B, void *C, size_t
     B200_REQUIRE(ctx, out_dt == B200_BF16 && !acc && !ta && !tb && !epi.cos_t && epi.act_out && (size_t)epi.swiglu_I * 2 == N &&
                  epi.swiglu_I % 32 == 0 && (epi.ld_act * 2) % 16 == 0 && (uintptr_t)epi.act_out % 16 == 0,
                  "gemm: the fused SwiGLU output needs a bf16 forward GEMM on W = [gate | up] with I a multiple of 32");
+  } else if (epi_in && epi_in->ce_mode) {
+    epi = *epi_in;
+    B200_REQUIRE(ctx, out_dt == B200_BF16 && !acc && !epi.cos_t && epi.ce_mode >= 1 && epi.ce_mode <= 3 && epi.ce_targets &&
+                 (epi.ce_mode == 3 ? epi.ce_lse != nullptr : (epi.ce_part_max && epi.ce_part_sum && epi.ce_tgt_logit)),
+                 "gemm: the cross-entropy epilogue needs a bf16 product, the target ids and its statistics arrays");
   } else if (epi_in) {
     epi = *epi_in;
     B200_REQUIRE(ctx, out_dt == B200_BF16 && epi.cos_t && epi.sin_t && epi.S > 0 && epi.hd % 32 == 0 && epi.cols % 32 == 0 &&
@@ -397,6 +478,8 @@ int gemm_tc2_launch(b200_ctx *ctx, const void *A, const void *B, void *C, size_t
   if (!a_mn && b_mn) return launch_out<false, true>(ctx, ma, mb, C, m, n, k, ldc, out_dt, acc, epi);
   return launch_out<false, false>(ctx, ma, mb, C, m, n, k, ldc, out_dt, acc, epi);
 }
+
+size_t gemm_tc2_ce_tiles(size_t N) { return (N + BN - 1) / BN; }
 
 bool gemm_tc2_swiglu_eligible(const b200_ctx *ctx, size_t M, size_t I) {
   const size_t pairs = ((M + 2 * BM - 1) / (2 * BM)) * ((I + BN / 2 - 1) / (BN / 2));

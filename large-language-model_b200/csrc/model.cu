@@ -27,6 +27,9 @@ int add_norm_oop(b200_ctx *, const void *, const void *, void *, const void *, v
                  b200_dtype);
 int convert2d(b200_ctx *, const void *, b200_dtype, void *, b200_dtype, size_t, size_t, size_t, size_t);
 int fill_const(b200_ctx *, void *, b200_dtype, size_t, float);
+bool vocab_ce_is_fused(const void *x, const void *w, size_t tokens, size_t V, size_t H, b200_dtype dt);
+int vocab_ce_dlogits(b200_ctx *ctx, const void *x, const void *w, const uint32_t *targets, const float *lse, void *dlogits,
+                     int in_place, size_t tokens, size_t V, size_t H, b200_dtype dt);
 
 // ---- NCCL, resolved at run time from the library already in the process (or libnccl.so.2) ----
 namespace nccl {
@@ -93,6 +96,10 @@ struct b200_model {
        *fh = nullptr;
   int32_t *d_tokens = nullptr, *d_targets = nullptr;
   float *d_loss = nullptr;
+  float *ce_lse = nullptr;        // [M] log-sum-exp of every token's logits, kept from the loss for its gradient
+  // 1: the loss GEMM stores no logits and the gradient of the logits comes from a second run of the projection;
+  // 0: the loss GEMM also stores bf16 logits and one in-place pass turns them into their gradient
+  int vocab_ce_recompute = 0;
   int32_t *pin_tokens = nullptr, *pin_targets = nullptr; float *pin_loss = nullptr;
   std::vector<void *> allocs;
   // decode: per-layer K/V caches [cache_batch, cache_len, KV] (keys stored after RoPE), generation buffers
@@ -187,6 +194,8 @@ extern "C" int b200_model_create(b200_ctx *ctx, const b200_model_config *cfg, b2
   A(&m->g_a1, M * H * es); A(&m->g_ping, M * H * es); A(&m->g_pong, M * H * es); A(&m->logits, M * m->V * es);
   A(&m->fh, M * H * es);
   A((void **)&m->d_tokens, M * 4); A((void **)&m->d_targets, M * 4); A((void **)&m->d_loss, 4);
+  A((void **)&m->ce_lse, M * 4);
+  if (const char *e = getenv("B200_VOCAB_CE")) m->vocab_ce_recompute = (e[0] == 'r' || e[0] == '1');   // "recompute" | "store"
   if (rc == B200_OK && (cudaMallocHost(&m->pin_tokens, M * 4) != cudaSuccess || cudaMallocHost(&m->pin_targets, M * 4) != cudaSuccess ||
                         cudaMallocHost(&m->pin_loss, 4) != cudaSuccess))
     rc = b200_fail(ctx, B200_ERR_NOMEM, "pinned host allocation failed");
@@ -550,9 +559,12 @@ extern "C" int b200_model_loss_and_grads(b200_model *m, const int32_t *tok, cons
   const float eps = m->cfg.rms_norm_eps;
   const b200_dtype dt = m->dt;
   TRY(forward_all(m, tok, B, S));
-  TRY(b200_gemm_ld(ctx, m->fh, m->P(m->off_out()), m->logits, M, V, H, 0, 0, 0, dt, dt, H, V, V));
-  // loss + dlogits in place (cpp/src/Loss.cpp:77-134, 163-194)
-  TRY(b200_cross_entropy(ctx, m->logits, (const uint32_t *)tgt, dev_loss, m->logits, M, V, dt));
+  // vocabulary projection + loss in one GEMM: per-row softmax statistics leave the epilogue (cpp/src/Transformer.cpp:190-196,
+  // cpp/src/Loss.cpp:77-134); then d(loss)/d(logits) in m->logits (cpp/src/Loss.cpp:163-194), either from stored logits in
+  // one in-place pass or from a second run of the projection with the gradient epilogue
+  const bool keep_logits = !m->vocab_ce_recompute || !vocab_ce_is_fused(m->fh, m->P(m->off_out()), M, V, H, dt);
+  TRY(b200_vocab_ce_forward(ctx, m->fh, m->P(m->off_out()), (const uint32_t *)tgt, dev_loss, m->ce_lse, keep_logits ? m->logits : nullptr, M, V, H, dt));
+  TRY(vocab_ce_dlogits(ctx, m->fh, m->P(m->off_out()), (const uint32_t *)tgt, m->ce_lse, m->logits, keep_logits, M, V, H, dt));
   // output projection (cpp/src/Transformer.cpp:515-521, 607-627) and final norm (:632)
   TRY(b200_gemm_ld(ctx, m->fh, m->logits, m->G(m->off_out()), H, V, M, 1, 0, 0, dt, B200_F32, H, V, V));
   TRY(allreduce_async(m, m->G(m->off_out()), H * V));
@@ -669,6 +681,56 @@ extern "C" int b200_dp_init(b200_model *m, const void *id128, int rank, int worl
   B200_CUDA(ctx, cudaEventCreateWithFlags(&m->ev_comm_done, cudaEventDisableTiming));
   return B200_OK;
 }
+// Order-fixed fp64 sum and sum of squares of the fp32 master weights: replicas that hold the same weights report
+// bit-identical numbers, so comparing two doubles per rank shows whether data-parallel replicas have drifted apart.
+namespace {
+__global__ void __launch_bounds__(256) checksum_partial_kernel(const float *__restrict__ v, size_t n, double *__restrict__ part) {
+  __shared__ double s1[256], s2[256];
+  double a = 0.0, b = 0.0;
+  for (size_t i = (size_t)blockIdx.x * 256 + threadIdx.x; i < n; i += (size_t)gridDim.x * 256) { const double x = v[i]; a += x; b += x * x; }
+  s1[threadIdx.x] = a; s2[threadIdx.x] = b;
+  __syncthreads();
+  for (int o = 128; o > 0; o >>= 1) {
+    if ((int)threadIdx.x < o) { s1[threadIdx.x] += s1[threadIdx.x + o]; s2[threadIdx.x] += s2[threadIdx.x + o]; }
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) { part[2 * blockIdx.x] = s1[0]; part[2 * blockIdx.x + 1] = s2[0]; }
+}
+__global__ void checksum_final_kernel(const double *__restrict__ part, int blocks, double *__restrict__ out) {
+  if (threadIdx.x == 0 && blockIdx.x == 0) {
+    double a = 0.0, b = 0.0;
+    for (int i = 0; i < blocks; ++i) { a += part[2 * i]; b += part[2 * i + 1]; }
+    out[0] = a; out[1] = b;
+  }
+}
+}  // namespace
+extern "C" int b200_model_param_checksum(b200_model *m, double *sum, double *sum_sq) {
+  if (!m) return B200_ERR_INVALID;
+  b200_ctx *ctx = m->ctx;
+  B200_REQUIRE(ctx, sum && sum_sq, "param_checksum: null pointer");
+  constexpr int BLOCKS = 1024;
+  double *d = (double *)b200_scratch(ctx, (2 * BLOCKS + 2) * sizeof(double));
+  if (!d) return B200_ERR_NOMEM;
+  double host[2] = {0, 0};
+  if (m->master) {
+    checksum_partial_kernel<<<BLOCKS, 256, 0, ctx->stream>>>(m->master, m->n_total, d);
+  } else {   // model without optimizer state in bf16: widen first
+    float *tmp = nullptr;
+    TRY(b200_malloc(ctx, m->n_total * 4, (void **)&tmp));
+    int rc = b200_convert(ctx, m->params, m->dt, tmp, B200_F32, m->n_total);
+    if (!rc) checksum_partial_kernel<<<BLOCKS, 256, 0, ctx->stream>>>(tmp, m->n_total, d);
+    b200_free(ctx, tmp);
+    if (rc) return rc;
+  }
+  B200_LAUNCHED(ctx);
+  checksum_final_kernel<<<1, 32, 0, ctx->stream>>>(d, BLOCKS, d + 2 * BLOCKS);
+  B200_LAUNCHED(ctx);
+  TRY(b200_memcpy_d2h(ctx, host, d + 2 * BLOCKS, sizeof(host)));
+  TRY(b200_sync(ctx));
+  *sum = host[0]; *sum_sq = host[1];
+  return B200_OK;
+}
+
 extern "C" int b200_dp_shutdown(b200_model *m) {
   if (!m || !m->comm) return B200_OK;
   cudaStreamSynchronize(m->comm_stream);

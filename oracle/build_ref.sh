@@ -22,10 +22,10 @@
 #     The fixed variant makes the writer prefer the element's own `owned_data`; the file layout is unchanged.
 set -e
 HERE="$(cd "$(dirname "$0")" && pwd)"
-REF="${REFERENCE_ROOT:-/root/reference}"
+REF="${REFERENCE_ROOT:-$HERE/../../reference}"   # default: a checkout named "reference" beside this repository
 ALIAS_FIX="${ALIAS_FIX:-1}"
 CXX_BIN="${ORC_CXX:-g++}"
-[ -d "$REF/cpp/src" ] || { echo "reference checkout not found at $REF" >&2; exit 3; }
+[ -d "$REF/cpp/src" ] || { echo "reference checkout not found at $REF: set REFERENCE_ROOT to the directory that holds its cpp/src" >&2; exit 3; }
 OUT="$HERE/_ref"
 SRC="$OUT/src_fix$ALIAS_FIX"
 mkdir -p "$SRC"

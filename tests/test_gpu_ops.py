@@ -135,6 +135,21 @@ def test_cross_entropy(ctx, orc, dtype, T, V):
     assert rel(grad.download(), eg) < _tol(dtype)
 
 
+@pytest.mark.parametrize("dtype", ["f32", "bf16"])
+@pytest.mark.parametrize("T,V", [(64, 4096), (7, 1001), (300, 32000)])
+def test_cross_entropy_in_place_matches_out_of_place(ctx, dtype, T, V):
+    # the engine's calling form: the gradient overwrites the logits (allowed by the header)
+    lg = _in(synth.normal(SEED, "logits_ip", (T, V), 3.0), dtype)
+    tg = ctx.array(synth.token_ids(SEED, "tg_ip", (T,), V).astype(np.uint32), "u32")
+    loss, grad = ctx.cross_entropy(ctx.array(lg, dtype), tg)
+    buf = ctx.array(lg, dtype)
+    for _ in range(3):          # a stale read of an already overwritten target logit would change the loss
+        buf.upload(lg)
+        loss_ip, grad_ip = ctx.cross_entropy(buf, tg, in_place=True)
+        assert float(loss_ip.download()[0]) == float(loss.download()[0])
+        np.testing.assert_array_equal(grad_ip.download(), grad.download())
+
+
 def test_cross_entropy_known_answers(ctx):
     # cpp/tests/test_loss.cpp:56-101
     loss, grad = ctx.cross_entropy(ctx.array(np.zeros((1, 4), np.float32)), ctx.array(np.array([2], np.uint32), "u32"))
