@@ -67,6 +67,13 @@ uint64_t b200_launch_count(const b200_ctx *ctx);
 int b200_profile_gemm(b200_ctx *ctx, int enable);
 int b200_profile_gemm_read(b200_ctx *ctx, double *total_ms, double *total_flops, uint64_t *launches);
 
+/* Device time of a batch of enqueued work: _begin records a CUDA event on the context's stream, _end records a second
+ * one, waits for it and returns the milliseconds between them.  This is what the reference accumulates into
+ * accum_gpu_time_ms around commit + waitUntilCompleted in end_scope (cpp/src/gpu_kernel/MetalBridge.mm:2195-2207),
+ * measured on the device instead of the host clock. */
+int b200_batch_timer_begin(b200_ctx *ctx);
+int b200_batch_timer_end(b200_ctx *ctx, float *elapsed_ms);
+
 /* ---- device memory (the reference wraps host pages zero-copy; a discrete GPU needs mirrors) */
 int b200_malloc(b200_ctx *ctx, size_t bytes, void **dptr);
 int b200_free(b200_ctx *ctx, void *dptr);
@@ -279,14 +286,17 @@ typedef struct {
   int n_whitespace_ids;            /* ids never penalised (sampler.py:27-28), at most 8 */
   int whitespace_ids[8];
 } b200_sampler_config;
-/* One sampling step for `batch` rows of device logits [batch, vocab] (vocab <= 32768).  history is a device
+/* One sampling step for `batch` rows of device logits [batch, vocab] (any vocabulary size; rows of more than 32768
+ * entries are worked on in the context workspace instead of shared memory).  history is a device
  * int32 [batch, hist_ld] array whose first hist_len entries per row are the ids seen so far; with append != 0
  * the drawn id is also stored at history[b, hist_len].  out_threshold / out_kept (optional, device) receive
  * the logit threshold and the number of surviving ids per row, for checking the filters. */
 int b200_sample(b200_ctx *ctx, const void *logits, b200_dtype dtype, size_t batch, size_t vocab, int32_t *history,
                 size_t hist_len, size_t hist_ld, int append, const b200_sampler_config *cfg, uint64_t step,
                 int32_t *out_tokens, float *out_threshold, int32_t *out_kept);
-/* Allocates K/V caches for `batch` sequences of up to max_total_len positions (<= max_seq_len of the model). */
+/* Allocates K/V caches for `batch` sequences of up to max_total_len positions (<= max_seq_len of the model).  A later
+ * call that asks for more sequences or positions re-allocates (the cached keys/values of the earlier generation are
+ * dropped); a call that fits the existing caches keeps them. */
 int b200_model_decode_begin(b200_model *m, size_t batch, size_t max_total_len);
 /* Runs the prompt [batch, prompt_len] (device ids), fills the caches, writes the logits of the last prompt
  * position to logits_last (device, compute dtype, [batch, vocab]). */

@@ -67,6 +67,8 @@ _SIGS = {
     "b200_launch_count": (C.c_uint64, [_vp]),
     "b200_profile_gemm": (_i, [_vp, _i]),
     "b200_profile_gemm_read": (_i, [_vp, C.POINTER(C.c_double), C.POINTER(C.c_double), C.POINTER(C.c_uint64)]),
+    "b200_batch_timer_begin": (_i, [_vp]),
+    "b200_batch_timer_end": (_i, [_vp, C.POINTER(_f)]),
     "b200_malloc": (_i, [_vp, _sz, C.POINTER(_vp)]),
     "b200_free": (_i, [_vp, _vp]),
     "b200_memcpy_h2d": (_i, [_vp, _vp, _vp, _sz]),

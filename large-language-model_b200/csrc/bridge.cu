@@ -91,6 +91,7 @@ extern "C" int b200_destroy(b200_ctx *ctx) {
   if (ctx->scratch) cudaFree(ctx->scratch);
   for (auto &t : ctx->timed) { cudaEventDestroy(t.start); cudaEventDestroy(t.stop); }
   for (auto e : ctx->event_pool) cudaEventDestroy(e);
+  if (ctx->batch_t0) { cudaEventDestroy(ctx->batch_t0); cudaEventDestroy(ctx->batch_t1); }
   cudaFree(ctx->dev_status);
   cudaFreeHost(ctx->host_status);
   cudaStreamDestroy(ctx->own_stream);
@@ -164,6 +165,23 @@ extern "C" int b200_profile_gemm_read(b200_ctx *ctx, double *total_ms, double *t
     ctx->event_pool.push_back(t.start); ctx->event_pool.push_back(t.stop);
   }
   ctx->timed.clear();
+  return B200_OK;
+}
+
+extern "C" int b200_batch_timer_begin(b200_ctx *ctx) {
+  if (!ctx) return B200_ERR_INVALID;
+  if (!ctx->batch_t0) { B200_CUDA(ctx, cudaEventCreate(&ctx->batch_t0)); B200_CUDA(ctx, cudaEventCreate(&ctx->batch_t1)); }
+  B200_CUDA(ctx, cudaEventRecord(ctx->batch_t0, ctx->stream));
+  ctx->batch_timing = true;
+  return B200_OK;
+}
+extern "C" int b200_batch_timer_end(b200_ctx *ctx, float *elapsed_ms) {
+  if (!ctx) return B200_ERR_INVALID;
+  B200_REQUIRE(ctx, elapsed_ms && ctx->batch_timing, "batch_timer_end: no timer running");
+  ctx->batch_timing = false;
+  B200_CUDA(ctx, cudaEventRecord(ctx->batch_t1, ctx->stream));
+  B200_CUDA(ctx, cudaEventSynchronize(ctx->batch_t1));
+  B200_CUDA(ctx, cudaEventElapsedTime(elapsed_ms, ctx->batch_t0, ctx->batch_t1));
   return B200_OK;
 }
 

@@ -40,6 +40,8 @@ struct b200_ctx {
   struct Timed { cudaEvent_t start, stop; double flops; };
   std::vector<Timed> timed;
   std::vector<cudaEvent_t> event_pool;
+  cudaEvent_t batch_t0 = nullptr, batch_t1 = nullptr;   // b200_batch_timer_begin / _end
+  bool batch_timing = false;
 };
 
 int b200_fail(b200_ctx *ctx, int code, const char *fmt, ...);

@@ -350,3 +350,28 @@ int gemm_tc_launch(b200_ctx *ctx, const void *A, const void *B, void *C, size_t 
   if (!a_mn && b_mn) return launch_out<false, true>(ctx, ma, mb, C, m, n, k, ldc, out_dt, acc, epi);
   return launch_out<false, false>(ctx, ma, mb, C, m, n, k, ldc, out_dt, acc, epi);
 }
+
+// ---- test hook for the bounded-wait error path (not part of the public header) -----------------------------------
+// One thread waits on an mbarrier that nothing ever arrives on, with a limit of `limit_cycles` SM clocks (about a
+// millisecond in the test).  The wait gives up, records code 199 in the context's device status word and the kernel
+// returns normally: the next b200_sync reports B200_ERR_DEVICE_WAIT and the context stays usable.  This is the same
+// mbar_wait every tensor-core kernel uses, so the test covers the give-up path without faulting or hanging anything.
+namespace {
+__global__ void wait_probe_kernel(int *status, long long limit_cycles) {
+  __shared__ uint64_t bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    tc::mbar_init(&bar, 1);
+    abort_flag = 0;
+    tc::fence_barrier_init();
+    tc::mbar_wait(&bar, 0, status, &abort_flag, 199, limit_cycles);
+  }
+}
+}  // namespace
+extern "C" int b200_internal_wait_probe(b200_ctx *ctx, long long limit_cycles) {
+  if (!ctx) return B200_ERR_INVALID;
+  B200_REQUIRE(ctx, limit_cycles > 0 && limit_cycles <= 200000000ll, "wait_probe: limit must be at most 2e8 cycles");
+  wait_probe_kernel<<<1, 32, 0, ctx->stream>>>(ctx->dev_status, limit_cycles);
+  B200_LAUNCHED(ctx);
+  return B200_OK;
+}

@@ -181,10 +181,13 @@ __device__ __forceinline__ void ce_row_epilogue(uint32_t taddr, bf16 *crow, int 
 #pragma unroll
       for (int j = 0; j < 32; ++j) if ((uint32_t)(col + j) == tgt) tl = __uint_as_float(r[j]);
     }
-    float t[32], cm = -1e30f;
-    const int valid = N - col;      // columns past N hold the zero fill of the weight tile: not part of the softmax
+    if (col + 32 > N) {             // ragged last chunk: columns past N hold the zero fill of the weight tile
 #pragma unroll
-    for (int j = 0; j < 32; ++j) { t[j] = (j < valid) ? __uint_as_float(r[j]) * LOG2E : -1e30f; cm = fmaxf(cm, t[j]); }
+      for (int j = 0; j < 32; ++j) if (col + j >= N) r[j] = __float_as_uint(-1e30f);
+    }
+    float t[32], cm = -1e30f;
+#pragma unroll
+    for (int j = 0; j < 32; ++j) { t[j] = __uint_as_float(r[j]) * LOG2E; cm = fmaxf(cm, t[j]); }
     const float mn = fmaxf(m2, cm);
     float acc = 0.f;
 #pragma unroll

@@ -41,11 +41,13 @@ typedef int (*CommDestroy_t)(comm_t);
 typedef int (*AllReduce_t)(const void *, void *, size_t, int, int, comm_t, cudaStream_t);
 typedef const char *(*GetErrorString_t)(int);
 typedef int (*CommGetAsyncError_t)(comm_t, int *);
+typedef int (*CommAbort_t)(comm_t);
 constexpr int kFloat32 = 7, kSum = 0, kAvg = 4;
 struct Api {
   void *handle = nullptr;
   GetUniqueId_t GetUniqueId = nullptr; CommInitRank_t CommInitRank = nullptr; CommDestroy_t CommDestroy = nullptr;
   AllReduce_t AllReduce = nullptr; GetErrorString_t GetErrorString = nullptr; CommGetAsyncError_t CommGetAsyncError = nullptr;
+  CommAbort_t CommAbort = nullptr;
   bool ok() const { return GetUniqueId && CommInitRank && CommDestroy && AllReduce; }
 };
 static Api &api() {
@@ -60,6 +62,7 @@ static Api &api() {
       a.AllReduce = (AllReduce_t)dlsym(a.handle, "ncclAllReduce");
       a.GetErrorString = (GetErrorString_t)dlsym(a.handle, "ncclGetErrorString");
       a.CommGetAsyncError = (CommGetAsyncError_t)dlsym(a.handle, "ncclCommGetAsyncError");
+      a.CommAbort = (CommAbort_t)dlsym(a.handle, "ncclCommAbort");
     }
   }
   return a;
@@ -114,6 +117,8 @@ struct b200_model {
   // data parallel
   nccl::comm_t comm = nullptr;
   int rank = 0, world = 1;
+  bool comm_failed = false;        // an NCCL call or the communicator reported an error: shut down with ncclCommAbort
+  int inject_comm_error = 0;       // test hook: the next gradient exchange fails with this NCCL result code (host side only)
   cudaStream_t comm_stream = nullptr;
   cudaEvent_t ev_grad_ready = nullptr, ev_comm_done = nullptr;
   // optimizer-in-backward: AdamW of a bucket runs on a side stream as soon as its gradients are final and its
@@ -506,12 +511,17 @@ extern "C" int b200_model_forward(b200_model *m, const int32_t *tok, size_t B, s
 }
 
 static int allreduce_async(b200_model *m, float *buf, size_t n) {
-  if (m->world <= 1 || !m->comm) return B200_OK;
+  if (!m->comm || (m->world <= 1 && !m->inject_comm_error)) return B200_OK;
   b200_ctx *ctx = m->ctx;
   B200_CUDA(ctx, cudaEventRecord(m->ev_grad_ready, ctx->stream));
   B200_CUDA(ctx, cudaStreamWaitEvent(m->comm_stream, m->ev_grad_ready, 0));
-  int r = nccl::api().AllReduce(buf, buf, n, nccl::kFloat32, nccl::kAvg, m->comm, m->comm_stream);
-  if (r != 0) return b200_fail(ctx, B200_ERR_COMM, "ncclAllReduce failed: %s", nccl::api().GetErrorString ? nccl::api().GetErrorString(r) : "?");
+  int r;
+  if (m->inject_comm_error) { r = m->inject_comm_error; m->inject_comm_error = 0; }     // injected on the host: nothing is launched
+  else r = nccl::api().AllReduce(buf, buf, n, nccl::kFloat32, nccl::kAvg, m->comm, m->comm_stream);
+  if (r != 0) {
+    m->comm_failed = true;
+    return b200_fail(ctx, B200_ERR_COMM, "ncclAllReduce failed: %s", nccl::api().GetErrorString ? nccl::api().GetErrorString(r) : "?");
+  }
   return B200_OK;
 }
 // AdamW for parameters [off, off+n) on the side stream, ordered after everything enqueued so far on the main stream
@@ -543,8 +553,10 @@ static int allreduce_join(b200_model *m) {
   B200_CUDA(ctx, cudaStreamWaitEvent(ctx->stream, m->ev_comm_done, 0));
   if (nccl::api().CommGetAsyncError) {
     int aerr = 0;
-    if (nccl::api().CommGetAsyncError(m->comm, &aerr) == 0 && aerr != 0)
+    if (nccl::api().CommGetAsyncError(m->comm, &aerr) == 0 && aerr != 0) {
+      m->comm_failed = true;
       return b200_fail(ctx, B200_ERR_COMM, "NCCL asynchronous error %d", aerr);
+    }
   }
   return B200_OK;
 }
@@ -731,10 +743,27 @@ extern "C" int b200_model_param_checksum(b200_model *m, double *sum, double *sum
   return B200_OK;
 }
 
+// Test hook (not part of the public header): the next gradient exchange reports NCCL result `nccl_result` without
+// calling NCCL -- a host-side failure injection; no kernel or collective is disturbed.
+extern "C" int b200_internal_dp_inject_failure(b200_model *m, int nccl_result) {
+  if (!m) return B200_ERR_INVALID;
+  m->inject_comm_error = nccl_result;
+  return B200_OK;
+}
+extern "C" int b200_internal_dp_comm_failed(const b200_model *m) { return m && m->comm_failed ? 1 : 0; }
+
 extern "C" int b200_dp_shutdown(b200_model *m) {
   if (!m || !m->comm) return B200_OK;
-  cudaStreamSynchronize(m->comm_stream);
-  nccl::api().CommDestroy(m->comm);
+  if (m->comm_failed && nccl::api().CommAbort) {
+    // after an error the communicator may never complete what is queued on it: ncclCommDestroy would block on that work,
+    // ncclCommAbort tears it down; only then is the side stream waited for
+    nccl::api().CommAbort(m->comm);
+    cudaStreamSynchronize(m->comm_stream);
+  } else {
+    cudaStreamSynchronize(m->comm_stream);
+    nccl::api().CommDestroy(m->comm);
+  }
+  m->comm_failed = false;
   m->comm = nullptr; m->world = 1;
   cudaEventDestroy(m->ev_grad_ready); cudaEventDestroy(m->ev_comm_done);
   cudaStreamDestroy(m->comm_stream);
@@ -759,7 +788,26 @@ extern "C" int b200_model_decode_begin(b200_model *m, size_t batch, size_t max_t
   B200_REQUIRE(ctx, batch > 0 && batch <= m->max_batch && max_total_len > 0 && max_total_len <= m->cfg.max_seq_len,
                "decode_begin: batch / length exceed what the model was created for");
   if (m->cache_batch >= batch && m->cache_len >= max_total_len) return B200_OK;
-  B200_REQUIRE(ctx, m->k_cache.empty(), "decode_begin: caches already allocated with a smaller shape");
+  if (!m->k_cache.empty()) {
+    // a larger batch or a longer total length than the caches were made for: let the stream drain, drop the old
+    // decode buffers and allocate again (their contents belong to a finished generation)
+    B200_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    auto drop = [&](void *p) {
+      if (!p) return;
+      for (size_t i = 0; i < m->allocs.size(); ++i) if (m->allocs[i] == p) { m->allocs.erase(m->allocs.begin() + i); break; }
+      cudaFree(p);
+    };
+    for (void *p : m->k_cache) drop(p);
+    for (void *p : m->v_cache) drop(p);
+    drop(m->dec_logits); drop(m->dec_h); drop(m->dec_history); drop(m->dec_next); drop(m->dec_attn_ws);
+    drop(m->dec_attn_tickets); drop(m->dec_pos);
+    m->k_cache.clear(); m->v_cache.clear();
+    m->dec_logits = m->dec_h = nullptr; m->dec_history = m->dec_next = nullptr; m->dec_attn_ws = nullptr;
+    m->dec_attn_tickets = nullptr; m->dec_pos = nullptr;
+    batch = batch > m->cache_batch ? batch : m->cache_batch;
+    max_total_len = max_total_len > m->cache_len ? max_total_len : m->cache_len;
+    m->cache_batch = m->cache_len = 0;
+  }
   const size_t es = dtype_size(m->dt), bytes = batch * max_total_len * m->KV * es;
   m->k_cache.assign(m->L, nullptr); m->v_cache.assign(m->L, nullptr);
   for (size_t l = 0; l < m->L; ++l) {
@@ -859,7 +907,16 @@ static int decode_step_impl(b200_model *m, const int32_t *tok, size_t B, size_t 
   const size_t H = m->H;
   const float eps = m->cfg.rms_norm_eps;
   const b200_dtype dt = m->dt;
-  TRY(b200_embedding_forward(ctx, (const uint32_t *)tok, m->P(m->off_emb()), m->hs[0], B, H, m->V, dt));
+  {
+    // The first kernel of a step is launched WITHOUT programmatic serialization, so it starts only when every kernel of
+    // the previous step has completed: programmatic dependent launch orders a kernel against its immediate predecessor
+    // only, and the attention kernels load cache tiles (written by the previous step) ahead of their own wait.
+    const bool keep = ctx->pdl;
+    ctx->pdl = false;
+    const int rc = b200_embedding_forward(ctx, (const uint32_t *)tok, m->P(m->off_emb()), m->hs[0], B, H, m->V, dt);
+    ctx->pdl = keep;
+    TRY(rc);
+  }
   if (m->L == 0) {
     TRY(b200_rms_norm_forward(ctx, m->hs[0], m->fh, m->P(m->off_final_norm()), nullptr, eps, B, H, dt));
   } else {

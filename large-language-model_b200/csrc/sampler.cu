@@ -5,7 +5,9 @@
 // probability exceeds p, at least two tokens), then a categorical draw from logits/temperature, or the
 // lowest-id argmax at temperature 0.
 //
-// One CTA of 1024 threads per sequence; the penalised logits of the row live in shared memory as fp32.
+// One CTA of 1024 threads per sequence; the penalised logits of the row live in shared memory as fp32 when the
+// vocabulary has at most 32768 entries, else in a per-row fp32 work array in global memory (L2-resident: the
+// reference's own configurations use vocabularies of 100256 and 100352, cpp/include/TransformerConfig.hpp:92,107).
 // Nothing is sorted: the k-th largest value and the top-p crossing value are found by repeated linear
 // histograms (2048 bins) over a shrinking value range, walking the bins from the largest values down.
 // Probability mass is accumulated as 2^-40 fixed point integers, so the result does not depend on the order
@@ -29,6 +31,7 @@ struct SamplerArgs {
   float penalty, top_p, temperature;
   uint64_t seed, step;
   const int *pos_dev;      // when set: hist_len = step = *pos_dev + 1 (read on the device: replayable capture)
+  float *gkeys;            // [batch, V] work array for vocabularies that do not fit in shared memory, else null
   int ws[8];
 };
 
@@ -138,7 +141,8 @@ sample_kernel(const T *__restrict__ logits, int32_t *history, int32_t *__restric
   pdl_launch_dependents();
   pdl_wait();
   if (a.pos_dev) { a.hist_len = *a.pos_dev + 1; a.step = (uint64_t)a.hist_len; }
-  extern __shared__ float keys[];                  // V penalised logits
+  extern __shared__ float smem_keys[];
+  float *keys = a.gkeys ? a.gkeys + (size_t)blockIdx.x * a.V : smem_keys;      // V penalised logits
   __shared__ Scratch sc;
   __shared__ int recent[WINDOW];
   const int b = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -263,17 +267,23 @@ int sample_launch(b200_ctx *ctx, const void *logits, b200_dtype dt, size_t batch
                   size_t hist_len, size_t hist_ld, int append, const b200_sampler_config *cfg, uint64_t step,
                   int32_t *out_tokens, float *out_threshold, int32_t *out_kept, const int *pos_dev) {
   B200_REQUIRE(ctx, logits && cfg && out_tokens && batch > 0, "sample: null pointer");
-  B200_REQUIRE(ctx, vocab >= 2 && vocab <= (size_t)MAX_V, "sample: vocabulary must be in [2, 32768]");
+  B200_REQUIRE(ctx, vocab >= 2 && vocab <= (size_t)0x7fffff00, "sample: vocabulary must have at least 2 entries");
   B200_REQUIRE(ctx, cfg->n_whitespace_ids >= 0 && cfg->n_whitespace_ids <= 8 && (history || (hist_len == 0 && !append)) && (!append || hist_len < hist_ld),
                "sample: bad configuration");
   B200_REQUIRE(ctx, cfg->repetition_penalty > 0.f && cfg->temperature >= 0.f, "sample: penalty must be > 0 and temperature >= 0");
   SamplerArgs a;
   a.V = (int)vocab; a.hist_len = (int)hist_len; a.hist_ld = (int)hist_ld; a.top_k = cfg->top_k;
   a.n_ws = cfg->n_whitespace_ids; a.penalty = cfg->repetition_penalty; a.top_p = cfg->top_p; a.temperature = cfg->temperature;
-  a.seed = cfg->seed; a.step = step; a.pos_dev = pos_dev;
+  a.seed = cfg->seed; a.step = step; a.pos_dev = pos_dev; a.gkeys = nullptr;
   for (int i = 0; i < 8; ++i) a.ws[i] = i < a.n_ws ? cfg->whitespace_ids[i] : -1;
   static bool attr[2] = {false, false};
-  const size_t smem = (size_t)MAX_V * sizeof(float);
+  size_t smem = (size_t)MAX_V * sizeof(float);
+  if (vocab > (size_t)MAX_V) {
+    // the context workspace only grows; a generation loop makes its first call (which may allocate) before it captures a step
+    a.gkeys = (float *)b200_scratch(ctx, batch * vocab * sizeof(float));
+    if (!a.gkeys) return B200_ERR_NOMEM;
+    smem = 0;
+  }
   if (dt == B200_BF16) {
     if (!attr[1]) { B200_CUDA(ctx, cudaFuncSetAttribute(sample_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); attr[1] = true; }
     B200_CUDA(ctx, launch_k(ctx, sample_kernel<bf16>, dim3((unsigned)batch), dim3(THREADS), smem, 0, (const bf16 *)logits, history, out_tokens, out_threshold, out_kept, a, append));

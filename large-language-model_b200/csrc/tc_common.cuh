@@ -42,13 +42,13 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
 // Bounded wait. Returns false (after recording `code` in *status) when the limit is hit
 // or when another thread of the CTA has already given up (`*abort_flag` set).
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, int *status, volatile int *abort_flag,
-                                          int code) {
+                                          int code, long long limit_cycles = WAIT_LIMIT_CYCLES) {
   if (mbar_try_wait(bar, parity)) return true;
   long long t0 = clock64();
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
     if (*abort_flag) return false;
-    if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
+    if (clock64() - t0 > limit_cycles) {
       *abort_flag = 1;
       atomicCAS(status, 0, code);
       return false;

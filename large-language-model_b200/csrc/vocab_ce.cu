@@ -25,19 +25,37 @@ constexpr float LN2 = 0.6931471805599453f, LOG2E = 1.4426950408889634f;
 constexpr float LOSS_CLAMP = 34.538776394910684f;   // -log(1e-15): the reference clamps the target probability (cpp/src/Loss.cpp:113-117)
 
 // lse[r] = log sum_j exp(x[r,j]) from the per-tile (max, sum) pairs (base-2 units); loss[r] = lse - x[r, target].
-__global__ void ce_merge_kernel(const float *__restrict__ pmax, const float *__restrict__ psum,
-                                const float *__restrict__ tgt_logit, const uint32_t *__restrict__ targets,
-                                float *__restrict__ lse, float *__restrict__ tok_loss, size_t M, int tiles, size_t V) {
-  const size_t r = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (r >= M) return;
-  float m = -1e30f;
-  for (int t = 0; t < tiles; ++t) m = fmaxf(m, pmax[(size_t)t * M + r]);
-  float s = 0.f;
-  for (int t = 0; t < tiles; ++t) s += psum[(size_t)t * M + r] * exp2f(pmax[(size_t)t * M + r] - m);
-  const float l = (m + log2f(s)) * LN2;
-  lse[r] = l;
-  const uint32_t tgt = targets[r];
-  tok_loss[r] = tgt < V ? fminf(l - tgt_logit[r], LOSS_CLAMP) : LOSS_CLAMP;
+// A CTA handles 32 rows; its 8 warps take every 8th tile (loads coalesced over the rows) and meet in shared memory.
+__global__ void __launch_bounds__(256)
+ce_merge_kernel(const float *__restrict__ pmax, const float *__restrict__ psum, const float *__restrict__ tgt_logit,
+                const uint32_t *__restrict__ targets, float *__restrict__ lse, float *__restrict__ tok_loss, size_t M,
+                int tiles, size_t V) {
+  __shared__ float sm[8][32], ss[8][32];
+  const int lane = threadIdx.x & 31, g = threadIdx.x >> 5;
+  const size_t r = (size_t)blockIdx.x * 32 + lane;
+  float m = -1e30f, s = 0.f;
+  if (r < M) {
+    for (int t = g; t < tiles; t += 8) {
+      const float pm = pmax[(size_t)t * M + r], ps = psum[(size_t)t * M + r];
+      const float mn = fmaxf(m, pm);
+      s = s * exp2f(m - mn) + ps * exp2f(pm - mn);
+      m = mn;
+    }
+  }
+  sm[g][lane] = m; ss[g][lane] = s;
+  __syncthreads();
+  if (g == 0 && r < M) {
+    float mm = sm[0][lane];
+#pragma unroll
+    for (int i = 1; i < 8; ++i) mm = fmaxf(mm, sm[i][lane]);
+    float tot = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) tot += ss[i][lane] * exp2f(sm[i][lane] - mm);      // fixed order: deterministic
+    const float l = (mm + log2f(tot)) * LN2;
+    lse[r] = l;
+    const uint32_t tgt = targets[r];
+    tok_loss[r] = tgt < V ? fminf(l - tgt_logit[r], LOSS_CLAMP) : LOSS_CLAMP;
+  }
 }
 
 // One CTA per row of stored logits: log-sum-exp and loss (the path without the fused epilogue).
@@ -113,7 +131,7 @@ extern "C" int b200_vocab_ce_forward(b200_ctx *ctx, const void *x, const void *w
     epi.ce_mode = logits_out ? 2 : 1; epi.ce_targets = targets; epi.ce_part_max = pmax; epi.ce_part_sum = psum; epi.ce_tgt_logit = tl;
     int rc = gemm_tc2_launch(ctx, x, w, logits_out, tokens, V, H, 0, 0, 0, B200_BF16, H, V, V, &epi);
     if (rc) return rc;
-    ce_merge_kernel<<<(unsigned)((tokens + 255) / 256), 256, 0, ctx->stream>>>(pmax, psum, tl, targets, lse_out, tok_loss, tokens, (int)tiles, V);
+    ce_merge_kernel<<<(unsigned)((tokens + 31) / 32), 256, 0, ctx->stream>>>(pmax, psum, tl, targets, lse_out, tok_loss, tokens, (int)tiles, V);
     B200_LAUNCHED(ctx);
     return mean_launch(ctx, tok_loss, loss_out, tokens);
   }

@@ -72,3 +72,45 @@ def average_over_ranks(array: np.ndarray) -> np.ndarray:
         dist.all_reduce(t, op=dist.ReduceOp.SUM)
         t /= dist.get_world_size()
     return t.numpy()
+
+
+class Membership:
+    """Agreement on who takes part in the next step, reached on the host BEFORE anything is launched.
+
+    A data-parallel step contains collectives; a rank that enters one without its peers hangs until a timeout.
+    So a rank never finds out about a departure inside a collective: at every step boundary each live rank posts
+    its intent for the next step ("go" or "leave") in a key-value store and reads the intents of the others.  A
+    rank that leaves does so only at such a boundary, with none of its kernels or collectives in flight; a rank
+    that died without a word simply never posts, and the others give up on it after ``timeout_s``.  All ranks
+    therefore hold the same list of live ranks before their next launch, and the survivors can rebuild their
+    communicator (or stop) instead of blocking.  Works with any ``torch.distributed`` store (TCPStore, FileStore).
+    """
+
+    def __init__(self, store, rank: int, world: int, timeout_s: float = 5.0):
+        self.store, self.rank, self.world, self.timeout_s = store, rank, world, timeout_s
+        self.live = list(range(world))
+
+    def _key(self, step: int, rank: int) -> str:
+        return f"membership/{step}/{rank}"
+
+    def post(self, step: int, leaving: bool = False):
+        self.store.set(self._key(step, self.rank), b"leave" if leaving else b"go")
+
+    def agree(self, step: int, leaving: bool = False):
+        """Posts this rank's intent for ``step`` and returns the sorted list of ranks that will run it."""
+        import datetime
+        self.post(step, leaving)
+        staying = []
+        for r in self.live:
+            if r == self.rank:
+                if not leaving:
+                    staying.append(r)
+                continue
+            try:
+                self.store.wait([self._key(step, r)], datetime.timedelta(seconds=self.timeout_s))
+                if bytes(self.store.get(self._key(step, r))) == b"go":
+                    staying.append(r)
+            except Exception:       # noqa: BLE001 - a store timeout: the peer never posted, treat it as gone
+                pass
+        self.live = sorted(staying)
+        return self.live

@@ -69,4 +69,12 @@ if [ "$ALIAS_FIX" = "1" ] && [ -f "$PKGDIR/libb200bridge.so" ]; then
     "$SRC"/*.cpp "$PKGDIR/adaptor/metal_bridge_b200.cpp" "$HERE/ref_driver.cpp" \
     -o "$OUT/libref_on_b200.so" -L"$PKGDIR" -lb200bridge -Wl,-rpath,'$ORIGIN/../../large-language-model_b200' -lpthread
   echo "built $OUT/libref_on_b200.so"
+  # the same with bf16 device mirrors (what the reference's Metal shaders read): the reference engine then runs on the
+  # tensor-core kernels; parity gate 2e-2
+  $CXX_BIN -std=c++20 -O2 -fopenmp -fPIC -shared -fvisibility=hidden -ffp-contract=off -DB200_ADAPTOR_BF16 \
+    -include chrono -include string -include numeric -include cstring -include thread \
+    -I"$HERE/shim" -I"$REF/cpp/include" -I"$HERE/../include" \
+    "$SRC"/*.cpp "$PKGDIR/adaptor/metal_bridge_b200.cpp" "$HERE/ref_driver.cpp" \
+    -o "$OUT/libref_on_b200_bf16.so" -L"$PKGDIR" -lb200bridge -Wl,-rpath,'$ORIGIN/../../large-language-model_b200' -lpthread
+  echo "built $OUT/libref_on_b200_bf16.so"
 fi

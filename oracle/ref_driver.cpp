@@ -249,6 +249,30 @@ REF_API float ref_model_loss_and_grads(const Cfg *c, const int32_t *tokens, cons
   return loss;
 }
 
+// ---- the backend interface's profiling externs and loss read-back (cpp/include/gpu_kernel/MetalBridge.hpp:136-145),
+// as Trainer::train consumes them (cpp/src/Trainer.cpp:347-366): exercised by the drop-in test of a GPU backend; with the
+// CPU stub they stay zero.
+#include "gpu_kernel/MetalBridge.hpp"
+REF_API void ref_backend_stats(double *gpu_ms, uint64_t *gpu_calls, float *last_loss) {
+  *gpu_ms = metal_bridge::accum_gpu_time_ms;
+  *gpu_calls = (uint64_t)metal_bridge::count_gpu_calls;
+  *last_loss = metal_bridge::get_last_loss();
+}
+REF_API void ref_backend_reset_stats() { metal_bridge::reset_profile_stats(); }
+// CrossEntropyLoss inside one begin_scope()/end_scope() pair, the way the trainer's step issues it: the loss scalar is
+// only host-visible after end_scope, and get_last_loss() must return it then.
+REF_API float ref_scoped_cross_entropy(const float *logits, const int32_t *targets, size_t tokens, size_t V) {
+  Quiet q;
+  Tensor lg = from(logits, {1, tokens, V});
+  Tensor tg({1, tokens}, 0.0f);
+  for (size_t i = 0; i < tokens; ++i) tg.data()[i] = (float)targets[i];
+  CrossEntropyLoss ce;
+  metal_bridge::begin_scope();
+  ce.forward(lg, tg);
+  metal_bridge::end_scope();
+  return metal_bridge::get_last_loss();
+}
+
 // ---- training-driver files: the reference's own Checkpoint::save / ::load and LR schedule ------------------
 #include "Checkpoint.hpp"
 #include "Trainer.hpp"

@@ -4,6 +4,10 @@ mode "cpu": world_size gloo ranks on CPU.  Each rank takes its slice of a seeded
   loss and gradients with the CPU checker, and the ranks average them (the CPU model of the engine's
   NCCL exchange).  Rank 0 checks that the result equals the checker run on the whole batch, i.e. that
   batch sharding + gradient averaging is exactly the single-device step.
+mode "leave" / "vanish": three gloo ranks on CPU run steps with a gradient all-reduce; after step 1 the last rank leaves --
+  announcing it at the step boundary ("leave") or exiting without a word ("vanish").  The others must learn of it on the
+  host before their next collective (Membership.agree), rebuild a two-rank group and finish the remaining steps with
+  averages taken over the survivors only; nobody may block in a collective that the departed rank never joins.
 mode "gpu": one rank per GPU.  Each rank runs the device-resident engine on its slice with the NCCL
   gradient exchange enabled, then one AdamW step; rank 0 compares gradients, loss and updated weights
   with a single-device run of the engine on the whole batch.
@@ -44,6 +48,37 @@ def main():
         payload = dp.broadcast_bytes(b"id-from-rank-0" if rank == 0 else None)
         assert payload == b"id-from-rank-0"
         assert dp.max_over_ranks([float(rank)])[0] == float(world - 1)
+        if mode in ("leave", "vanish"):
+            import datetime
+            import torch
+            import torch.distributed as dist
+            store = dist.TCPStore("127.0.0.1", int(os.environ["MASTER_PORT"]) + 1, world, is_master=(rank == 0),
+                                  timeout=datetime.timedelta(seconds=30))
+            mem = dp.Membership(store, rank, world, timeout_s=3.0)
+            group, members = None, list(range(world))       # None = the default (all ranks) group
+            leaver = world - 1
+            for step in range(4):
+                going = rank == leaver and step == 2        # departs at the boundary before step 2
+                if going and mode == "vanish":
+                    os._exit(0)                             # no announcement, no clean-up: the others must time out on it
+                live = mem.agree(step, leaving=going)
+                if going:
+                    break
+                if live != members:                         # somebody left: a new group over the survivors, made by them alone
+                    assert leaver not in live and rank in live, (live, rank)
+                    members = live
+                    # creation is collective over the survivors only; the departed rank cannot take part
+                    group = dist.new_group(ranks=members, use_local_synchronization=True)
+                g = torch.full((4,), float(rank + 1) * (step + 1), dtype=torch.float64)
+                dist.all_reduce(g, op=dist.ReduceOp.SUM, group=group)
+                g /= len(members)
+                expect = np.mean([float(r + 1) * (step + 1) for r in members])
+                assert abs(float(g[0]) - expect) < 1e-12, (step, members, float(g[0]), expect)
+            if rank != leaver:
+                assert members == [r for r in range(world) if r != leaver], members
+            with open(out_path + f".rank{rank}", "w") as f:
+                f.write("OK")
+            os._exit(0)     # the default group still counts the departed rank: no collective tear-down with it
         if mode == "cpu":
             orc = oracle.Oracle()
             loss, grads, _ = orc.model_loss_and_grads(cfg_one, t, y, params)

@@ -34,7 +34,8 @@ def test_library_exports_every_declared_symbol(lib):
 def test_kernel_choice_hooks_of_the_gpu_tests_exist(lib):
     """The GPU parity tests run both forms of a kernel through these undeclared A/B hooks."""
     for name in ("b200_internal_set_gemm_2cta", "b200_internal_set_gemm_skinny", "b200_internal_set_attn_fwd2",
-                 "b200_internal_set_attn_bwd2", "b200_internal_set_attn_decode_tc"):
+                 "b200_internal_set_attn_bwd2", "b200_internal_set_attn_decode_tc", "b200_internal_wait_probe",
+                 "b200_internal_dp_inject_failure", "b200_internal_dp_comm_failed"):
         assert hasattr(lib, name), name
 
 

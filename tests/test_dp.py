@@ -47,3 +47,17 @@ def test_nccl_gradient_exchange_matches_single_device(tmp_path):
     if n < 2:
         pytest.skip("needs at least 2 GPUs")
     _launch("gpu", 2, tmp_path, timeout=600)
+
+
+@pytest.mark.parametrize("mode", ["leave", "vanish"])
+def test_a_rank_that_departs_between_steps_is_noticed_on_the_host(tmp_path, mode):
+    """Three gloo ranks; the last one leaves after two steps (announced, or silently).  The survivors agree on the new
+    membership before their next collective and finish with a two-rank group: no rank blocks, none is killed."""
+    out = tmp_path / f"dp_{mode}.txt"
+    port = _free_port()
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=3", "--master-addr", "127.0.0.1",
+           "--master-port", str(port), os.path.join(HERE, "dp_worker.py"), mode, str(out)]
+    env = dict(os.environ, OMP_NUM_THREADS="1", NCCL_NVLS_ENABLE="0")
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=240, env=env)
+    survivors = [tmp_path / f"dp_{mode}.txt.rank{k}" for k in (0, 1)]
+    assert all(p.exists() and p.read_text() == "OK" for p in survivors), r.stdout[-2000:] + r.stderr[-4000:]

@@ -39,10 +39,13 @@ def ref_filters(logits, generated, penalty, top_k, top_p, whitespace=(), window=
     return pen, lg
 
 
+# 32000: the benchmark model; 100352: the vocabulary of the reference's own training configurations
+# (cpp/src/RunTrainer.cpp:121), which does not fit in shared memory
+@pytest.mark.parametrize("V", [32000, 100352])
 @pytest.mark.parametrize("dtype", ["f32", "bf16"])
 @pytest.mark.parametrize("top_k,top_p,penalty", [(0, 1.0, 1.0), (50, 1.0, 1.0), (0, 0.9, 1.0), (50, 0.9, 1.1), (0, 0.9, 1.1), (1, 0.5, 1.3)])
-def test_sampler_filters_match_the_reference_rules(ctx, dtype, top_k, top_p, penalty):
-    B, V, Lh = 6, 32000, 200
+def test_sampler_filters_match_the_reference_rules(ctx, dtype, top_k, top_p, penalty, V):
+    B, Lh = 6, 200
     lg = synth.normal(4, "logits", (B, V), 2.5)
     lg[1] *= 4.0                      # one peaked row
     lg[2] = np.round(lg[2])           # many exact ties
@@ -102,6 +105,50 @@ def test_fp32_greedy_decode_is_bit_exact_against_the_checker(ctx, orc):
         nxt = logits.reshape(B, ctxt.shape[1], -1)[:, -1].argmax(-1).astype(np.int32)
         np.testing.assert_array_equal(got[:, t], nxt, err_msg=f"generated token {t}")
         ctxt = np.concatenate([ctxt, nxt[:, None]], 1)
+    model.close()
+
+
+def test_generate_again_with_a_longer_total_length_and_a_larger_batch(ctx):
+    """The K/V caches grow when a later call asks for more than the first one allocated."""
+    shape = dict(H=128, I=96, nH=4, nKV=2, hd=32, V=211, L=2)
+    model = bridge.Model(ctx, bridge.Shape(B=4, S=64, **shape), "f32", with_optimizer=False)
+    model.init_synthetic(3, 0.3)
+    greedy = bridge.SamplerConfig.make(temperature=0.0)
+    p_small = synth.token_ids(31, "p", (2, 6), shape["V"])
+    first, _, _ = model.generate(p_small, 4, greedy)
+    p_big = np.concatenate([p_small, synth.token_ids(32, "p2", (2, 6), shape["V"])], 0)
+    longer, _, _ = model.generate(p_big, 20, greedy)              # batch 2 -> 4, total length 10 -> 26
+    np.testing.assert_array_equal(longer[:2, :4], first)           # same prompts decode to the same ids
+    again, _, _ = model.generate(p_small, 4, greedy)
+    np.testing.assert_array_equal(again, first)
+    model.close()
+
+
+def test_generate_with_a_vocabulary_larger_than_shared_memory(ctx, orc):
+    """The reference's own configurations use 100256 / 100352 ids: greedy ids bit-exact against the checker in fp32,
+    and the captured bf16 decode step with sampling is reproducible and stays inside the vocabulary."""
+    B, P, NEW, V = 2, 5, 4, 100352
+    shape = dict(H=64, I=96, nH=2, nKV=1, hd=32, V=V, L=1)
+    params = synth.model_params(23, oracle.Config(B=B, S=P + NEW, **shape), std=0.3)
+    prompt = synth.token_ids(23, "prompt", (B, P), V)
+    model = bridge.Model(ctx, bridge.Shape(B=B, S=P + NEW, **shape), "f32", with_optimizer=False)
+    model.load_params(params)
+    got, _, _ = model.generate(prompt, NEW, bridge.SamplerConfig.make(temperature=0.0))
+    ctxt = prompt.copy()
+    for t in range(NEW):
+        cfg = oracle.Config(B=B, S=ctxt.shape[1], **shape)
+        _, _, logits = orc.model_loss_and_grads(cfg, ctxt, np.zeros_like(ctxt), params, want_grads=False, want_logits=True)
+        nxt = logits.reshape(B, ctxt.shape[1], -1)[:, -1].argmax(-1).astype(np.int32)
+        np.testing.assert_array_equal(got[:, t], nxt, err_msg=f"generated token {t}")
+        ctxt = np.concatenate([ctxt, nxt[:, None]], 1)
+    model.close()
+    model = bridge.Model(ctx, bridge.Shape(B=B, S=P + 8, **shape), "bf16", with_optimizer=False)
+    model.init_synthetic(5, 0.05)
+    cfg = bridge.SamplerConfig.make(temperature=0.8, top_p=0.9, repetition_penalty=1.1, seed=9, whitespace_ids=(220, 256, 198, 385))
+    a, _, _ = model.generate(prompt, 8, cfg)
+    b, _, _ = model.generate(prompt, 8, cfg)
+    np.testing.assert_array_equal(a, b)
+    assert a.min() >= 0 and a.max() < V
     model.close()
 
 
