@@ -393,7 +393,7 @@ def attention_cpu_check(ctx, st, B, S, nH, nKV, hd, b=5, kvh=2):
             "cpu_kind": "port (oracle/block_oracle.c, fp32)", "cores": os.cpu_count()}
 
 
-def ops_metrics(ctx, bridge, torch, reps=10):
+def ops_metrics(ctx, bridge, torch, reps=20):
     """Per-op figures at the model's shapes with M = 8 x 2048 = 16384 tokens, bf16: every projection as forward (NN), data
     gradient (NT) and weight gradient (TN, fp32 result) in TFLOP/s; the bandwidth-bound kernels in GB/s over their
     algorithmic bytes (each input read once, each output written once).  Operands are far larger than L2."""

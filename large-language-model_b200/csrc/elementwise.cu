@@ -714,11 +714,19 @@ extern "C" int b200_cross_entropy(b200_ctx *ctx, const void *logits, const uint3
 // =============================================================== AdamW ====
 // m,v EMA -> decoupled decay -> bias-corrected step with eps outside the sqrt
 // (cpp/src/gpu_kernel/adamw_step.metal:49-68).  fp32 master, optional bf16 shadow.
-__global__ void adamw_kernel(float *__restrict__ p, const float *__restrict__ g, float *__restrict__ m,
+__device__ __forceinline__ float4 load4(const float *g, size_t i) { return reinterpret_cast<const float4 *>(g)[i]; }
+__device__ __forceinline__ float4 load4(const bf16 *g, size_t i) {
+  const uint2 r = reinterpret_cast<const uint2 *>(g)[i];
+  const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&r.x)), b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&r.y));
+  return make_float4(a.x, a.y, b.x, b.y);
+}
+// G: element type of the gradient (fp32, or bf16 when the data-parallel exchange ran in bf16)
+template <class G>
+__global__ void adamw_kernel(float *__restrict__ p, const G *__restrict__ g, float *__restrict__ m,
                              float *__restrict__ v, bf16 *__restrict__ shadow, size_t n, b200_adamw_params a) {
   size_t nv = n / 4;
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < nv; i += (size_t)gridDim.x * blockDim.x) {
-    float4 pp = reinterpret_cast<float4 *>(p)[i], gg = reinterpret_cast<const float4 *>(g)[i];
+    float4 pp = reinterpret_cast<float4 *>(p)[i], gg = load4(g, i);
     float4 mm = reinterpret_cast<float4 *>(m)[i], vv = reinterpret_cast<float4 *>(v)[i];
     float *pf = &pp.x, *gf = &gg.x, *mf = &mm.x, *vf = &vv.x;
 #pragma unroll
@@ -740,7 +748,7 @@ __global__ void adamw_kernel(float *__restrict__ p, const float *__restrict__ g,
     }
   }
   for (size_t i = nv * 4 + (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
-    float gi = g[i];
+    float gi = to_f(g[i]);
     float mi = a.beta1 * m[i] + (1.0f - a.beta1) * gi, vi = a.beta2 * v[i] + (1.0f - a.beta2) * gi * gi;
     float x = p[i];
     if (a.weight_decay > 0.0f) x = x - a.lr * a.weight_decay * x;
@@ -755,7 +763,18 @@ extern "C" int b200_adamw_step(b200_ctx *ctx, float *p, const float *g, float *m
   B200_REQUIRE(ctx, (((uintptr_t)p | (uintptr_t)g | (uintptr_t)m | (uintptr_t)v) % 16 == 0) && ((uintptr_t)shadow % 8 == 0),
                "adamw_step: arrays must be 16-byte aligned");
   if (!n) return B200_OK;
-  adamw_kernel<<<ew_grid(ctx, n / 4 + 1), 256, 0, ctx->stream>>>(p, g, m, v, (bf16 *)shadow, n, *a);
+  adamw_kernel<float><<<ew_grid(ctx, n / 4 + 1), 256, 0, ctx->stream>>>(p, g, m, v, (bf16 *)shadow, n, *a);
+  B200_LAUNCHED(ctx);
+  return B200_OK;
+}
+// The same step with the gradient held in bf16 (8-byte aligned).
+int adamw_step_bf16_grad(b200_ctx *ctx, float *p, const void *g_bf16, float *m, float *v, void *shadow, size_t n,
+                         const b200_adamw_params *a) {
+  B200_REQUIRE(ctx, p && g_bf16 && m && v && a, "adamw_step: null pointer");
+  B200_REQUIRE(ctx, (((uintptr_t)p | (uintptr_t)m | (uintptr_t)v) % 16 == 0) && ((uintptr_t)shadow % 8 == 0) && ((uintptr_t)g_bf16 % 8 == 0),
+               "adamw_step: arrays must be 16-byte aligned (bf16 arrays 8-byte)");
+  if (!n) return B200_OK;
+  adamw_kernel<bf16><<<ew_grid(ctx, n / 4 + 1), 256, 0, ctx->stream>>>(p, (const bf16 *)g_bf16, m, v, (bf16 *)shadow, n, *a);
   B200_LAUNCHED(ctx);
   return B200_OK;
 }

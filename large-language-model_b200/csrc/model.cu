@@ -27,6 +27,8 @@ int add_norm_oop(b200_ctx *, const void *, const void *, void *, const void *, v
                  b200_dtype);
 int convert2d(b200_ctx *, const void *, b200_dtype, void *, b200_dtype, size_t, size_t, size_t, size_t);
 int fill_const(b200_ctx *, void *, b200_dtype, size_t, float);
+int adamw_step_bf16_grad(b200_ctx *ctx, float *p, const void *g_bf16, float *m, float *v, void *shadow, size_t n,
+                         const b200_adamw_params *a);
 bool vocab_ce_is_fused(const void *x, const void *w, size_t tokens, size_t V, size_t H, b200_dtype dt);
 int vocab_ce_dlogits(b200_ctx *ctx, const void *x, const void *w, const uint32_t *targets, const float *lse, void *dlogits,
                      int in_place, size_t tokens, size_t V, size_t H, b200_dtype dt);
@@ -42,12 +44,15 @@ typedef int (*AllReduce_t)(const void *, void *, size_t, int, int, comm_t, cudaS
 typedef const char *(*GetErrorString_t)(int);
 typedef int (*CommGetAsyncError_t)(comm_t, int *);
 typedef int (*CommAbort_t)(comm_t);
-constexpr int kFloat32 = 7, kSum = 0, kAvg = 4;
+typedef int (*ReduceScatter_t)(const void *, void *, size_t, int, int, comm_t, cudaStream_t);
+typedef int (*AllGather_t)(const void *, void *, size_t, int, comm_t, cudaStream_t);
+constexpr int kFloat32 = 7, kBfloat16 = 9, kSum = 0, kAvg = 4;
 struct Api {
   void *handle = nullptr;
   GetUniqueId_t GetUniqueId = nullptr; CommInitRank_t CommInitRank = nullptr; CommDestroy_t CommDestroy = nullptr;
   AllReduce_t AllReduce = nullptr; GetErrorString_t GetErrorString = nullptr; CommGetAsyncError_t CommGetAsyncError = nullptr;
   CommAbort_t CommAbort = nullptr;
+  ReduceScatter_t ReduceScatter = nullptr; AllGather_t AllGather = nullptr;
   bool ok() const { return GetUniqueId && CommInitRank && CommDestroy && AllReduce; }
 };
 static Api &api() {
@@ -63,6 +68,8 @@ static Api &api() {
       a.GetErrorString = (GetErrorString_t)dlsym(a.handle, "ncclGetErrorString");
       a.CommGetAsyncError = (CommGetAsyncError_t)dlsym(a.handle, "ncclCommGetAsyncError");
       a.CommAbort = (CommAbort_t)dlsym(a.handle, "ncclCommAbort");
+      a.ReduceScatter = (ReduceScatter_t)dlsym(a.handle, "ncclReduceScatter");
+      a.AllGather = (AllGather_t)dlsym(a.handle, "ncclAllGather");
     }
   }
   return a;
@@ -117,6 +124,13 @@ struct b200_model {
   // data parallel
   nccl::comm_t comm = nullptr;
   int rank = 0, world = 1;
+  // Sharded optimizer (data parallel, whole training steps): per bucket reduce-scatter of the gradients, AdamW on this
+  // rank's 1/world slice, all-gather of the updated compute-dtype weights -- all on the side stream while backward goes
+  // on.  The fp32 master weights and the moments are then current only inside this rank's slices until gathered.
+  int dp_sharded = 1;              // 0: every rank all-reduces and runs the full AdamW (B200_DP_MODE=allreduce)
+  int dp_grad_bf16 = 0;            // 1: gradients cross NVLink as bf16 (B200_DP_GRAD_DTYPE=bf16)
+  bool state_sharded = false;      // masters / moments outside this rank's slices are stale
+  void *grad_bf16 = nullptr;       // one bucket of bf16 gradients (largest bucket)
   bool comm_failed = false;        // an NCCL call or the communicator reported an error: shut down with ncclCommAbort
   int inject_comm_error = 0;       // test hook: the next gradient exchange fails with this NCCL result code (host side only)
   cudaStream_t comm_stream = nullptr;
@@ -140,6 +154,8 @@ struct b200_model {
   void *P(size_t off) const { return (char *)params + off * dtype_size(dt); }
   float *G(size_t off) const { return grads + off; }
 };
+
+static int gather_sharded_state(b200_model *m);
 
 namespace {
 int dalloc(b200_model *m, void **p, size_t bytes) {
@@ -222,6 +238,7 @@ extern "C" int b200_model_create(b200_ctx *ctx, const b200_model_config *cfg, b2
 
 extern "C" int b200_model_destroy(b200_model *m) {
   if (!m) return B200_OK;
+  m->state_sharded = false;            // nobody reads the state again: no collective on the way out
   b200_dp_shutdown(m);
   cudaStreamSynchronize(m->ctx->stream);
   if (m->opt_stream) { cudaStreamSynchronize(m->opt_stream); cudaStreamDestroy(m->opt_stream); }
@@ -271,6 +288,7 @@ std::vector<Piece> layout_map(const b200_model *m) {
 extern "C" int b200_model_load_params(b200_model *m, const float *host) {
   if (!m) return B200_ERR_INVALID;
   b200_ctx *ctx = m->ctx;
+  TRY(gather_sharded_state(m));        // moments of other ranks' slices must not be lost by overwriting only the weights
   B200_REQUIRE(ctx, host, "model_load_params: null pointer");
   auto map = layout_map(m);
   size_t biggest = 0;
@@ -309,6 +327,7 @@ static int export_flat(b200_model *m, const void *src, b200_dtype sdt, float *ho
 }
 extern "C" int b200_model_read_params(b200_model *m, float *host) {
   if (!m || !host) return B200_ERR_INVALID;
+  TRY(gather_sharded_state(m));
   if (m->master) return export_flat(m, m->master, B200_F32, host);
   return export_flat(m, m->params, m->dt, host);
 }
@@ -324,6 +343,7 @@ extern "C" int b200_model_read_opt_state(b200_model *m, float *host_m, float *ho
   if (!m) return B200_ERR_INVALID;
   b200_ctx *ctx = m->ctx;
   B200_REQUIRE(ctx, m->with_opt && host_m && host_v && step, "read_opt_state: model has no optimizer state or null pointer");
+  TRY(gather_sharded_state(m));
   auto map = layout_map(m);
   size_t biggest = 0;
   for (auto &p : map) biggest = p.rows * p.cols > biggest ? p.rows * p.cols : biggest;
@@ -349,6 +369,7 @@ extern "C" int b200_model_load_opt_state(b200_model *m, const float *host_m, con
   if (!m) return B200_ERR_INVALID;
   b200_ctx *ctx = m->ctx;
   B200_REQUIRE(ctx, m->with_opt && host_m && host_v, "load_opt_state: model has no optimizer state or null pointer");
+  TRY(gather_sharded_state(m));
   auto map = layout_map(m);
   size_t biggest = 0;
   for (auto &p : map) biggest = p.rows * p.cols > biggest ? p.rows * p.cols : biggest;
@@ -374,6 +395,7 @@ extern "C" int b200_model_load_opt_state(b200_model *m, const float *host_m, con
 extern "C" int b200_model_init_synthetic(b200_model *m, uint64_t seed, float std) {
   if (!m) return B200_ERR_INVALID;
   b200_ctx *ctx = m->ctx;
+  TRY(gather_sharded_state(m));
   // trainable tensors ~ N(0, std); norm weights 1 (cpp/src/RMSNorm.cpp:32)
   if (m->master && (void *)m->master != m->params) {
     TRY(b200_fill_normal(ctx, m->master, B200_F32, m->n_train, seed, std));
@@ -524,6 +546,67 @@ static int allreduce_async(b200_model *m, float *buf, size_t n) {
   }
   return B200_OK;
 }
+static bool dp_shardable(const b200_model *m) {
+  // every bucket splits into `world` slices whose offsets keep the 16-byte alignment AdamW and the vector loads want
+  const size_t q = (size_t)m->world * 8;
+  return m->world > 1 && m->comm && m->dp_sharded && m->with_opt && m->master && nccl::api().ReduceScatter && nccl::api().AllGather &&
+         (m->V * m->H) % q == 0 && m->layer_train % q == 0;
+}
+// Sharded-optimizer exchange of bucket [off, off+n): everything below runs on the side stream, after the work enqueued so
+// far on the main stream (the bucket's weight gradients AND the last kernel that reads the bucket's weights).
+static int sharded_bucket(b200_model *m, size_t off, size_t n) {
+  b200_ctx *ctx = m->ctx;
+  const size_t sh = n / (size_t)m->world, mine = off + (size_t)m->rank * sh;
+  const size_t es = dtype_size(m->dt);
+  B200_CUDA(ctx, cudaEventRecord(m->ev_grad_ready, ctx->stream));
+  B200_CUDA(ctx, cudaStreamWaitEvent(m->comm_stream, m->ev_grad_ready, 0));
+  cudaStream_t keep = ctx->stream;
+  ctx->stream = m->comm_stream;
+  int rc = B200_OK, r = 0;
+  void *shadow = ((void *)m->master != m->params) ? (void *)((char *)m->params + mine * es) : nullptr;
+  if (m->inject_comm_error) { r = m->inject_comm_error; m->inject_comm_error = 0; }
+  else if (m->dp_grad_bf16) {
+    rc = b200_convert(ctx, m->grads + off, B200_F32, m->grad_bf16, B200_BF16, n);
+    if (!rc) r = nccl::api().ReduceScatter(m->grad_bf16, (char *)m->grad_bf16 + (size_t)m->rank * sh * 2, sh, nccl::kBfloat16, nccl::kAvg, m->comm, m->comm_stream);
+    if (!rc && !r) rc = adamw_step_bf16_grad(ctx, m->master + mine, (char *)m->grad_bf16 + (size_t)m->rank * sh * 2, m->adam_m + mine, m->adam_v + mine, shadow, sh, m->fused_opt);
+  } else {
+    r = nccl::api().ReduceScatter(m->grads + off, m->grads + mine, sh, nccl::kFloat32, nccl::kAvg, m->comm, m->comm_stream);
+    if (!r) rc = b200_adamw_step(ctx, m->master + mine, m->grads + mine, m->adam_m + mine, m->adam_v + mine, shadow, sh, m->fused_opt);
+  }
+  if (!rc && !r)
+    r = nccl::api().AllGather((char *)m->params + mine * es, (char *)m->params + off * es, sh, m->dt == B200_BF16 ? nccl::kBfloat16 : nccl::kFloat32,
+                              m->comm, m->comm_stream);
+  ctx->stream = keep;
+  if (r != 0) {
+    m->comm_failed = true;
+    return b200_fail(ctx, B200_ERR_COMM, "NCCL reduce-scatter / all-gather failed: %s", nccl::api().GetErrorString ? nccl::api().GetErrorString(r) : "?");
+  }
+  m->state_sharded = true;
+  return rc;
+}
+// Brings the fp32 master weights and the AdamW moments of every rank's slices to all ranks (collective: every rank calls).
+static int gather_sharded_state(b200_model *m) {
+  if (!m->state_sharded || !m->comm || m->world <= 1) return B200_OK;
+  b200_ctx *ctx = m->ctx;
+  TRY(b200_sync(ctx));
+  auto gather = [&](float *base, size_t off, size_t n) -> int {
+    if (!base) return 0;
+    const size_t sh = n / (size_t)m->world;
+    return nccl::api().AllGather(base + off + (size_t)m->rank * sh, base + off, sh, nccl::kFloat32, m->comm, m->comm_stream);
+  };
+  int r = 0;
+  float *arrays[3] = {((void *)m->master != m->params) ? m->master : nullptr, m->adam_m, m->adam_v};   // fp32 models: params were gathered already
+  for (float *a : arrays) {
+    if (!r) r = gather(a, m->off_emb(), m->V * m->H);
+    for (size_t l = 0; l < m->L && !r; ++l) r = gather(a, m->off_layer(l), m->layer_train);
+    if (!r) r = gather(a, m->off_out(), m->H * m->V);
+  }
+  if (r != 0) { m->comm_failed = true; return b200_fail(ctx, B200_ERR_COMM, "ncclAllGather of the optimizer state failed"); }
+  B200_CUDA(ctx, cudaStreamSynchronize(m->comm_stream));
+  m->state_sharded = false;
+  return B200_OK;
+}
+
 // AdamW for parameters [off, off+n) on the side stream, ordered after everything enqueued so far on the main stream
 // (and, data-parallel, after the bucket's all-reduce, which runs on that same side stream).
 static int opt_bucket(b200_model *m, size_t off, size_t n) {
@@ -578,21 +661,23 @@ extern "C" int b200_model_loss_and_grads(b200_model *m, const int32_t *tok, cons
   TRY(b200_vocab_ce_forward(ctx, m->fh, m->P(m->off_out()), (const uint32_t *)tgt, dev_loss, m->ce_lse, keep_logits ? m->logits : nullptr, M, V, H, dt));
   TRY(vocab_ce_dlogits(ctx, m->fh, m->P(m->off_out()), (const uint32_t *)tgt, m->ce_lse, m->logits, keep_logits, M, V, H, dt));
   // output projection (cpp/src/Transformer.cpp:515-521, 607-627) and final norm (:632)
+  const bool sharded = m->fused_opt && dp_shardable(m);
   TRY(b200_gemm_ld(ctx, m->fh, m->logits, m->G(m->off_out()), H, V, M, 1, 0, 0, dt, B200_F32, H, V, V));
-  TRY(allreduce_async(m, m->G(m->off_out()), H * V));
+  if (!sharded) TRY(allreduce_async(m, m->G(m->off_out()), H * V));
   TRY(b200_gemm_ld(ctx, m->logits, m->P(m->off_out()), m->tmpH, M, H, V, 0, 1, 0, dt, dt, V, V, H));
-  TRY(opt_bucket(m, m->off_out(), H * V));          // after the data-gradient GEMM, the last reader of this weight
+  // after the data-gradient GEMM, the last reader of this weight
+  if (sharded) TRY(sharded_bucket(m, m->off_out(), H * V)); else TRY(opt_bucket(m, m->off_out(), H * V));
   void *g = m->g_ping, *g_next = m->g_pong;
   TRY(b200_rms_norm_backward(ctx, m->tmpH, m->hs[m->L], m->P(m->off_final_norm()), g, nullptr, eps, M, H, dt));
   for (size_t l = m->L; l-- > 0;) {
     TRY(layer_backward_core(m, l, g, g_next, B, S));
-    TRY(allreduce_async(m, m->G(m->off_layer(l)), m->layer_train));
-    TRY(opt_bucket(m, m->off_layer(l), m->layer_train));
+    if (sharded) TRY(sharded_bucket(m, m->off_layer(l), m->layer_train));
+    else { TRY(allreduce_async(m, m->G(m->off_layer(l)), m->layer_train)); TRY(opt_bucket(m, m->off_layer(l), m->layer_train)); }
     void *t = g; g = g_next; g_next = t;
   }
   TRY(b200_embedding_backward(ctx, (const uint32_t *)tok, g, m->G(m->off_emb()), M, H, V, dt));
-  TRY(allreduce_async(m, m->G(m->off_emb()), V * H));
-  TRY(opt_bucket(m, m->off_emb(), V * H));
+  if (sharded) TRY(sharded_bucket(m, m->off_emb(), V * H));
+  else { TRY(allreduce_async(m, m->G(m->off_emb()), V * H)); TRY(opt_bucket(m, m->off_emb(), V * H)); }
   TRY(opt_join(m));
   return allreduce_join(m);
 }
@@ -600,6 +685,7 @@ extern "C" int b200_model_loss_and_grads(b200_model *m, const int32_t *tok, cons
 extern "C" int b200_model_adamw_step(b200_model *m, float lr, float beta1, float beta2, float eps, float wd) {
   if (!m) return B200_ERR_INVALID;
   B200_REQUIRE(m->ctx, m->with_opt && m->master, "model was created without optimizer state");
+  TRY(gather_sharded_state(m));
   m->step_count++;
   b200_adamw_params p;
   p.lr = lr; p.beta1 = beta1; p.beta2 = beta2; p.eps = eps; p.weight_decay = wd;
@@ -615,9 +701,11 @@ extern "C" int b200_model_train_step(b200_model *m, const int32_t *tok, const in
   // Optimizer in backward (opt-in, B200_FUSED_OPT=1): measured no faster on a power-capped B200 -- the GEMMs it runs
   // under lose what the hidden AdamW gains -- so the plain order is the default.  Every bucket offset keeps the
   // 16-byte alignment the AdamW kernel wants.
+  // Data parallel: the optimizer is sharded over the ranks and runs bucket by bucket behind the gradient exchange.
   const char *env = getenv("B200_FUSED_OPT");
-  const bool fuse = (env && env[0] == '1') && m->with_opt && m->master && m->opt_stream && (m->V * m->H) % 4 == 0 && m->layer_train % 4 == 0;
+  const bool fuse = ((env && env[0] == '1') || dp_shardable(m)) && m->with_opt && m->master && m->opt_stream && (m->V * m->H) % 4 == 0 && m->layer_train % 4 == 0;
   if (!fuse) {
+    TRY(gather_sharded_state(m));
     TRY(b200_model_loss_and_grads(m, tok, tgt, B, S, dev_loss));
     return b200_model_adamw_step(m, lr, beta1, beta2, eps, wd);
   }
@@ -688,6 +776,12 @@ extern "C" int b200_dp_init(b200_model *m, const void *id128, int rank, int worl
   int r = nccl::api().CommInitRank(&m->comm, world, id, rank);
   if (r != 0) return b200_fail(ctx, B200_ERR_COMM, "ncclCommInitRank failed: %s", nccl::api().GetErrorString ? nccl::api().GetErrorString(r) : "?");
   m->rank = rank; m->world = world;
+  if (const char *e = getenv("B200_DP_MODE")) m->dp_sharded = !(e[0] == 'a');             // "allreduce" | "sharded"
+  if (const char *e = getenv("B200_DP_GRAD_DTYPE")) m->dp_grad_bf16 = (e[0] == 'b');      // "bf16" | "fp32"
+  if (m->dp_grad_bf16 && !m->grad_bf16) {
+    const size_t biggest = m->V * m->H > m->layer_train ? m->V * m->H : m->layer_train;
+    TRY(dalloc(m, &m->grad_bf16, biggest * 2));
+  }
   B200_CUDA(ctx, cudaStreamCreateWithFlags(&m->comm_stream, cudaStreamNonBlocking));
   B200_CUDA(ctx, cudaEventCreateWithFlags(&m->ev_grad_ready, cudaEventDisableTiming));
   B200_CUDA(ctx, cudaEventCreateWithFlags(&m->ev_comm_done, cudaEventDisableTiming));
@@ -720,6 +814,7 @@ extern "C" int b200_model_param_checksum(b200_model *m, double *sum, double *sum
   if (!m) return B200_ERR_INVALID;
   b200_ctx *ctx = m->ctx;
   B200_REQUIRE(ctx, sum && sum_sq, "param_checksum: null pointer");
+  TRY(gather_sharded_state(m));
   constexpr int BLOCKS = 1024;
   double *d = (double *)b200_scratch(ctx, (2 * BLOCKS + 2) * sizeof(double));
   if (!d) return B200_ERR_NOMEM;
@@ -754,6 +849,7 @@ extern "C" int b200_internal_dp_comm_failed(const b200_model *m) { return m && m
 
 extern "C" int b200_dp_shutdown(b200_model *m) {
   if (!m || !m->comm) return B200_OK;
+  if (!m->comm_failed) gather_sharded_state(m);      // leave every replica with complete masters and moments
   if (m->comm_failed && nccl::api().CommAbort) {
     // after an error the communicator may never complete what is queued on it: ncclCommDestroy would block on that work,
     // ncclCommAbort tears it down; only then is the side stream waited for

@@ -103,7 +103,18 @@ def main():
             model.adamw_step(1e-2)
             new_params = model.read_params()
             l_avg = dp.average_over_ranks(np.array([loss]))[0]
-            model.close(); ctx.close()
+            model.close()
+            # whole training steps: the optimizer is sharded over the ranks (reduce-scatter, AdamW on one slice per rank,
+            # all-gather of the weights); reading the weights back gathers the fp32 masters from all ranks
+            stepper = bridge.Model(ctx, cfg_one, "f32")
+            stepper.load_params(params)
+            uid2 = dp.broadcast_bytes(bridge.dp_unique_id() if rank == 0 else None)
+            stepper.dp_init(uid2, rank, world)
+            step_losses = [stepper.train_step_host(t, y, lr=1e-2) for _ in range(3)]
+            stepped = stepper.read_params()
+            m_sh, v_sh, n_sh = stepper.read_opt_state()
+            stepper.close(); ctx.close()
+            step_l_avg = [dp.average_over_ranks(np.array([l]))[0] for l in step_losses]
             if rank == 0:
                 ctx1 = bridge.Context(local)
                 single = bridge.Model(ctx1, cfg_all, "f32")
@@ -112,7 +123,16 @@ def main():
                 grads_all = single.read_grads()
                 single.adamw_step(1e-2)
                 params_all = single.read_params()
-                single.close(); ctx1.close()
+                single.close()
+                one = bridge.Model(ctx1, cfg_all, "f32")
+                one.load_params(params)
+                one_losses = [one.train_step_host(ta, ya, lr=1e-2) for _ in range(3)]
+                one_params = one.read_params()
+                m_one, v_one, n_one = one.read_opt_state()
+                one.close(); ctx1.close()
+                assert np.allclose(step_l_avg, one_losses, rtol=1e-5, atol=1e-6), (step_l_avg, one_losses)
+                assert rel(stepped, one_params) < 1e-5, rel(stepped, one_params)
+                assert n_sh == n_one == 3 and rel(m_sh, m_one) < 1e-4 and rel(v_sh, v_one) < 1e-4
                 assert abs(l_avg - loss_all) < 1e-5, (l_avg, loss_all)
                 assert rel(grads, grads_all) < 1e-4, rel(grads, grads_all)
                 assert rel(new_params, params_all) < 1e-5, rel(new_params, params_all)
