@@ -281,6 +281,16 @@ int add_norm_norm_oop(b200_ctx *ctx, const void *x, const void *r, void *h_out, 
   if (r1) return r1;
   return b200_rms_norm_forward(ctx, y1, y2, w2, nullptr, eps, rows, D, dt);
 }
+template <class T>
+int rms_bwd2_warp(b200_ctx *, const void *, const void *, const void *, const void *, void *, float, size_t, size_t);
+// Engine form: backward of y2 = rmsnorm(rmsnorm(h) * w) (second norm with unit weight) plus the residual gradient in
+// one pass, without the first norm's output.  Returns 1 when done, 0 when the row shape needs the two-pass route.
+int norm_norm_backward_fused(b200_ctx *ctx, const void *g, const void *h, const void *w, const void *res_grad, void *dx,
+                             size_t rows, size_t D, float eps, b200_dtype dt) {
+  if (rows == 0) return 1;
+  return dt == B200_BF16 ? rms_bwd2_warp<bf16>(ctx, g, h, w, res_grad, dx, eps, rows, D)
+                         : rms_bwd2_warp<float>(ctx, g, h, w, res_grad, dx, eps, rows, D);
+}
 extern "C" int b200_rms_norm_backward(b200_ctx *ctx, const void *g, const void *x, const void *w, void *dx,
                                       float *dw, float eps, size_t rows, size_t D, b200_dtype dt) {
   B200_REQUIRE(ctx, g && x && w && dx && D > 0, "rms_norm_backward: null pointer or empty row");

@@ -27,6 +27,8 @@ int add_norm_oop(b200_ctx *, const void *, const void *, void *, const void *, v
                  b200_dtype);
 int convert2d(b200_ctx *, const void *, b200_dtype, void *, b200_dtype, size_t, size_t, size_t, size_t);
 int fill_const(b200_ctx *, void *, b200_dtype, size_t, float);
+int norm_norm_backward_fused(b200_ctx *ctx, const void *g, const void *h, const void *w, const void *res_grad, void *dx,
+                             size_t rows, size_t D, float eps, b200_dtype dt);
 int adamw_step_bf16_grad(b200_ctx *ctx, float *p, const void *g_bf16, float *m, float *v, void *shadow, size_t n,
                          const b200_adamw_params *a);
 bool vocab_ce_is_fused(const void *x, const void *w, size_t tokens, size_t V, size_t H, b200_dtype dt);
@@ -98,7 +100,7 @@ struct b200_model {
   float *cos_t = nullptr, *sin_t = nullptr;
   // activations kept for backward, per layer (compute dtype)
   std::vector<void *> hs;    // L+1 residual-stream states [M,H]
-  struct Act { void *a1, *a2, *qkv, *o, *h_mid, *ffn_in, *gate_up, *act; float *lse; };
+  struct Act { void *a1, *a2, *qkv, *o, *h_mid, *ffn_in, *gate_up, *act; float *lse; bool a1_valid; };
   std::vector<Act> acts;
   // workspace
   void *tmpH = nullptr, *g_act = nullptr, *g_gate_up = nullptr, *g_ffn_in = nullptr, *g_h_mid = nullptr, *g_o = nullptr,
@@ -490,9 +492,19 @@ static int layer_backward_core(b200_model *m, size_t l, const void *g, void *g_i
     TRY(rope_strided(ctx, gq, m->cos_t, m->sin_t, B, m->nH + m->nKV, S, m->hd, (long long)S * ld, (long long)m->hd, ld, dt, true));
   TRY(b200_gemm_ld(ctx, a.a2, m->g_qkv, m->G(m->off_qkv(l)), H, m->QKV, M, 1, 0, 0, dt, B200_F32, H, m->QKV, m->QKV));
   TRY(b200_gemm_ld(ctx, m->g_qkv, m->P(m->off_qkv(l)), m->g_a2, M, H, m->QKV, 0, 1, 0, dt, dt, m->QKV, m->QKV, H));
-  TRY(b200_rms_norm_backward(ctx, m->g_a2, a.a1, m->ones, m->g_a1, nullptr, eps, M, H, dt));
-  // F. attn norm + residual (cpp/src/Transformer.cpp:460-471)
-  TRY(b200_fused_backward_add_norm(ctx, m->g_a1, m->hs[l], m->P(m->off_attn_norm(l)), m->g_h_mid, g_in, M, H, eps, dt));
+  // the attention's inner unit-weight norm and F. attn norm + residual (cpp/src/Transformer.cpp:460-471) in one pass
+  // that recomputes the first norm's output from the layer input; two passes for row shapes the warp kernel does not take
+  static const bool allow_fused = !(getenv("B200_NORM_BWD_FUSED") && getenv("B200_NORM_BWD_FUSED")[0] == '0');   // A/B switch
+  const int fused = allow_fused ? norm_norm_backward_fused(ctx, m->g_a2, m->hs[l], m->P(m->off_attn_norm(l)), m->g_h_mid, g_in, M, H, eps, dt) : 0;
+  if (fused < 0) return fused;
+  if (fused == 0) {
+    if (!a.a1_valid) {     // the forward pass skipped the first norm's output: make it now
+      TRY(b200_rms_norm_forward(ctx, m->hs[l], a.a1, m->P(m->off_attn_norm(l)), nullptr, eps, M, H, dt));
+      a.a1_valid = true;
+    }
+    TRY(b200_rms_norm_backward(ctx, m->g_a2, a.a1, m->ones, m->g_a1, nullptr, eps, M, H, dt));
+    TRY(b200_fused_backward_add_norm(ctx, m->g_a1, m->hs[l], m->P(m->off_attn_norm(l)), m->g_h_mid, g_in, M, H, eps, dt));
+  }
   return B200_OK;
 }
 
@@ -510,13 +522,18 @@ static int forward_all(b200_model *m, const int32_t *tok, size_t B, size_t S) {
   TRY(b200_embedding_forward(ctx, (const uint32_t *)tok, m->P(m->off_emb()), m->hs[0], M, H, m->V, dt));
   if (m->L == 0) return b200_rms_norm_forward(ctx, m->hs[0], m->fh, m->P(m->off_final_norm()), nullptr, eps, M, H, dt);
   // the layer's outer norm and the attention's inner unit-weight norm are produced in one pass
-  TRY(add_norm_norm_oop(ctx, m->hs[0], nullptr, nullptr, m->P(m->off_attn_norm(0)), m->acts[0].a1, m->ones, m->acts[0].a2, nullptr, M, H, eps, dt));
+  // The first norm's output a1 is only an intermediate here: the backward pass recomputes it from the layer input, so it
+  // is not written (a1 doubles as the scratch of the two-pass route for row shapes the one-pass kernel does not take).
+  TRY(add_norm_norm_oop(ctx, m->hs[0], nullptr, nullptr, m->P(m->off_attn_norm(0)), nullptr, m->ones, m->acts[0].a2, m->acts[0].a1, M, H, eps, dt));
+  m->acts[0].a1_valid = false;
   for (size_t l = 0; l < m->L; ++l) {
     TRY(layer_forward_core(m, l, m->hs[l], B, S, true));
     // h_out = h_mid + ffn_out, fused with the norm(s) that consume it next
-    if (l + 1 < m->L)
-      TRY(add_norm_norm_oop(ctx, m->acts[l].h_mid, m->tmpH, m->hs[l + 1], m->P(m->off_attn_norm(l + 1)), m->acts[l + 1].a1, m->ones,
-                            m->acts[l + 1].a2, nullptr, M, H, eps, dt));
+    if (l + 1 < m->L) {
+      TRY(add_norm_norm_oop(ctx, m->acts[l].h_mid, m->tmpH, m->hs[l + 1], m->P(m->off_attn_norm(l + 1)), nullptr, m->ones,
+                            m->acts[l + 1].a2, m->acts[l + 1].a1, M, H, eps, dt));
+      m->acts[l + 1].a1_valid = false;
+    }
     else
       TRY(add_norm_oop(ctx, m->acts[l].h_mid, m->tmpH, m->hs[l + 1], m->P(m->off_final_norm()), m->fh, M, H, eps, dt));
   }
@@ -746,6 +763,7 @@ extern "C" int b200_model_layer_forward(b200_model *m, size_t l, const void *h_i
   const size_t M = B * S, H = m->H;
   TRY(b200_copy(ctx, m->hs[l], h_in, M * H * dtype_size(m->dt)));
   TRY(b200_rms_norm_forward(ctx, m->hs[l], m->acts[l].a1, m->P(m->off_attn_norm(l)), nullptr, m->cfg.rms_norm_eps, M, H, m->dt));
+  m->acts[l].a1_valid = true;
   TRY(layer_forward_core(m, l, m->hs[l], B, S));
   TRY(b200_copy(ctx, h_out, m->acts[l].h_mid, M * H * dtype_size(m->dt)));
   return b200_residual_add(ctx, h_out, m->tmpH, M * H, m->dt);

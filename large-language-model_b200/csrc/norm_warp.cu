@@ -229,6 +229,88 @@ rms_bwd_warp_kernel(const T *__restrict__ g, const T *__restrict__ x, const T *_
   }
 }
 
+// Backward of the pair "a1 = rmsnorm(h) * w; a2 = rmsnorm(a1)" (the layer's norm followed by the attention's own
+// unit-weight norm, cpp/src/Transformer.cpp:147 + cpp/src/Attention.cpp:192-194) plus the residual gradient, in ONE
+// pass: dx = d(a2)/d(h)^T g + res_grad.  a1 is not read: it is recomputed from h exactly as the forward kernel stored
+// it (same arithmetic, rounded to T), so the forward need not keep it.  Reads g, h, res_grad; writes dx.
+// WPR warps share a row (a 2048-wide bf16 row held by one warp, widened to floats, does not fit in the register file);
+// their partial sums meet in shared memory behind a named barrier of the row's WPR*32 threads.
+template <class T, int VPL, int WPR>
+__global__ void __launch_bounds__(WARPS_PER_CTA * 32)
+rms_bwd2_warp_kernel(const T *__restrict__ g, const T *__restrict__ h, const T *__restrict__ w,
+                     const T *__restrict__ res_grad, T *__restrict__ dx, float eps, size_t rows, int D) {
+  constexpr int N = Vec16<T>::N, ROWS_PER_CTA = WARPS_PER_CTA / WPR;
+  __shared__ float part[4][ROWS_PER_CTA][WPR];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, slot = warp / WPR, sub = warp % WPR;
+  const float inv_d = 1.0f / (float)D;
+  auto row_sum = [&](float v, int which) -> float {
+    v = warp_sum(v);
+    if (WPR == 1) return v;
+    if (lane == 0) part[which][slot][sub] = v;
+    asm volatile("bar.sync %0, %1;" ::"r"(1 + slot), "n"(WPR * 32) : "memory");
+    float t = 0.f;
+#pragma unroll
+    for (int k = 0; k < WPR; ++k) t += part[which][slot][k];
+    return t;
+  };
+  const size_t n_slots = (size_t)gridDim.x * ROWS_PER_CTA;
+  // every warp of a row group runs the same number of iterations (the barrier counts on it)
+  for (size_t row = (size_t)blockIdx.x * ROWS_PER_CTA + slot; row < rows; row += n_slots) {
+    const size_t base = row * (size_t)D;
+    auto at = [&](int i) { return (size_t)((i * WPR + sub) * 32 + lane) * N; };
+    Vec16<T> ha[VPL], ga[VPL], ra[VPL];
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) { ha[i].load(h + base + at(i)); ga[i].load(g + base + at(i)); }
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) ra[i].load(res_grad + base + at(i));
+    float hv[VPL][N], gv[VPL][N], a1[VPL][N];
+    float ss1 = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+      ha[i].unpack(hv[i]);
+#pragma unroll
+      for (int j = 0; j < N; ++j) ss1 += hv[i][j] * hv[i][j];
+    }
+    const float rstd1 = rsqrtf(row_sum(ss1, 0) * inv_d + eps);
+    // a1 as the forward stored it, and the statistics of the second norm
+    float ss2 = 0.f, dot2 = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+      Vec16<T> wv; float wf[N];
+      wv.load(w + at(i)); wv.unpack(wf);
+      ga[i].unpack(gv[i]);
+#pragma unroll
+      for (int j = 0; j < N; ++j) {
+        a1[i][j] = to_f(from_f<T>(hv[i][j] * rstd1 * wf[j]));
+        ss2 += a1[i][j] * a1[i][j]; dot2 += gv[i][j] * a1[i][j];
+      }
+    }
+    const float rstd2 = rsqrtf(row_sum(ss2, 1) * inv_d + eps);
+    const float s2 = row_sum(dot2, 2) * rstd2 * inv_d;          // mean(g * a1_hat)
+    // g1 = d/d(a1) through the unit-weight norm, times w; the first norm's statistic mean(g1 * w * h_hat)
+    float dot1 = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+      Vec16<T> wv; float wf[N];
+      wv.load(w + at(i)); wv.unpack(wf);
+#pragma unroll
+      for (int j = 0; j < N; ++j) {
+        gv[i][j] = rstd2 * (gv[i][j] - a1[i][j] * rstd2 * s2) * wf[j];
+        dot1 += gv[i][j] * hv[i][j];
+      }
+    }
+    const float s1 = row_sum(dot1, 3) * rstd1 * inv_d;
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+      float o[N];
+      ra[i].unpack(o);
+#pragma unroll
+      for (int j = 0; j < N; ++j) o[j] += rstd1 * (gv[i][j] - hv[i][j] * rstd1 * s1);
+      Vec16<T> ov; ov.pack(o); ov.store(dx + base + at(i));
+    }
+  }
+}
+
 int warp_grid(b200_ctx *ctx, size_t rows) {
   size_t blocks = (rows + WARPS_PER_CTA - 1) / WARPS_PER_CTA, cap = (size_t)ctx->sm_count * 4;
   return (int)(blocks < cap ? (blocks ? blocks : 1) : cap);
@@ -292,6 +374,31 @@ int rms_bwd_warp(b200_ctx *ctx, const void *g, const void *x, const void *w, con
   if (cudaGetLastError() != cudaSuccess) return b200_fail(ctx, B200_ERR_CUDA, "rms_norm backward launch failed");
   return 1;
 }
+// Returns 1 when launched, 0 when the shape does not fit (the caller then runs the two separate backward passes).
+template <class T>
+int rms_bwd2_warp(b200_ctx *ctx, const void *g, const void *h, const void *w, const void *rg, void *dx, float eps,
+                  size_t rows, size_t D) {
+  constexpr int N = Vec16<T>::N;
+  if (D % (32 * N) || !aligned16({g, h, w, rg, dx})) return 0;
+  const int vecs = (int)(D / (32 * N));               // 16-byte vectors per lane if one warp took the row
+#define B2(V, W_) do { const size_t per = WARPS_PER_CTA / W_; size_t blocks = (rows + per - 1) / per; const size_t cap = (size_t)ctx->sm_count * 4; \
+    if (blocks > cap) blocks = cap; if (!blocks) blocks = 1; \
+    rms_bwd2_warp_kernel<T, V, W_><<<(unsigned)blocks, WARPS_PER_CTA * 32, 0, ctx->stream>>>((const T *)g, (const T *)h, (const T *)w, (const T *)rg, (T *)dx, eps, rows, (int)D); } while (0)
+  switch (vecs) {
+    case 1: B2(1, 1); break;
+    case 2: B2(2, 1); break;
+    case 4: B2(4, 1); break;
+    case 8: B2(4, 2); break;
+    case 16: B2(4, 4); break;
+    default: return 0;
+  }
+#undef B2
+  ctx->launches++;
+  if (cudaGetLastError() != cudaSuccess) return b200_fail(ctx, B200_ERR_CUDA, "double rms_norm backward launch failed");
+  return 1;
+}
+template int rms_bwd2_warp<float>(b200_ctx *, const void *, const void *, const void *, const void *, void *, float, size_t, size_t);
+template int rms_bwd2_warp<bf16>(b200_ctx *, const void *, const void *, const void *, const void *, void *, float, size_t, size_t);
 template int rms_fwd_warp<float>(b200_ctx *, const void *, void *, const void *, const void *, void *, float *, float, size_t, size_t, bool, const void *, void *);
 template int rms_fwd_warp<bf16>(b200_ctx *, const void *, void *, const void *, const void *, void *, float *, float, size_t, size_t, bool, const void *, void *);
 template int rms_bwd_warp<float>(b200_ctx *, const void *, const void *, const void *, const void *, void *, float *, float, size_t, size_t, bool);

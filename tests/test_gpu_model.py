@@ -40,7 +40,11 @@ def digest(a, n=256):
     return np.concatenate([[np.sqrt(np.sum(a.astype(np.float64) ** 2)), a.astype(np.float64).sum()], a[idx].astype(np.float64)])
 
 
-@pytest.mark.parametrize("cfgd", [TOY, C1], ids=["toy", "single_layer_benchmark_config"])
+# d_model 2048 in fp32: the row shape at which the norm kernels split a row over four warps
+WIDE = dict(B=1, S=32, H=2048, I=256, nH=16, nKV=4, hd=128, V=128, L=1)
+
+
+@pytest.mark.parametrize("cfgd", [TOY, C1, WIDE], ids=["toy", "single_layer_benchmark_config", "d_model_2048"])
 def test_fp32_model_loss_logits_and_every_gradient(ctx, orc, cfgd):
     cfg = oracle.Config(**cfgd)
     params, tok, tgt = inputs(cfg)
@@ -105,8 +109,11 @@ def test_fp32_single_layer_forward_backward(ctx, orc, cfgd):
 @pytest.mark.parametrize("cfgd", [dict(B=2, S=128, H=256, I=688, nH=8, nKV=2, hd=32, V=4096, L=2),
                                   dict(B=2, S=256, H=512, I=1024, nH=4, nKV=2, hd=128, V=2048, L=2),
                                   # enough 256x256 tile pairs for the two-CTA GEMM with the SwiGLU epilogues (forward and backward)
-                                  dict(B=2, S=1024, H=256, I=1280, nH=2, nKV=1, hd=128, V=1024, L=1)],
-                         ids=["hd32", "hd128", "two_cta_fused_swiglu"])
+                                  dict(B=2, S=1024, H=256, I=1280, nH=2, nKV=1, hd=128, V=1024, L=1),
+                                  # the benchmark's d_model (norm rows of 1024 / 2048: one and two warps per row)
+                                  dict(B=1, S=128, H=1024, I=512, nH=8, nKV=2, hd=128, V=512, L=2),
+                                  dict(B=1, S=128, H=2048, I=512, nH=16, nKV=4, hd=128, V=512, L=2)],
+                         ids=["hd32", "hd128", "two_cta_fused_swiglu", "d_model_1024", "d_model_2048"])
 def test_bf16_model_against_fp32_checker(ctx, orc, cfgd):
     cfg = oracle.Config(**cfgd)
     params, tok, tgt = inputs(cfg, seed=9)
