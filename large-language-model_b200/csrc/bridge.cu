@@ -168,6 +168,54 @@ extern "C" int b200_profile_gemm_read(b200_ctx *ctx, double *total_ms, double *t
   return B200_OK;
 }
 
+// ---- launch trace (development hook, not part of the public header) ------------------------------------------------
+// With the trace on, an event is recorded on the stream after every kernel launch of this library.  The dump attributes the
+// time between consecutive events to the source line of the later launch (the kernel's own time plus the gap in front of
+// it: everything runs on one stream) and writes one line per launch site, largest first.
+void b200_trace_mark(b200_ctx *ctx, const char *file, int line) {
+  cudaEvent_t e;
+  if (cudaEventCreate(&e) != cudaSuccess) return;
+  cudaEventRecord(e, ctx->stream);
+  ctx->marks.push_back({e, file, line});
+}
+extern "C" int b200_internal_trace(b200_ctx *ctx, int enable) {
+  if (!ctx) return B200_ERR_INVALID;
+  if (enable && !ctx->trace_on) b200_trace_mark(ctx, "start", 0);
+  ctx->trace_on = enable != 0;
+  return B200_OK;
+}
+extern "C" int b200_internal_trace_dump(b200_ctx *ctx, const char *path) {
+  if (!ctx || !path) return B200_ERR_INVALID;
+  B200_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  struct Site { std::string key; double ms = 0; size_t n = 0; };
+  std::vector<Site> sites;
+  double total = 0;
+  for (size_t i = 1; i < ctx->marks.size(); ++i) {
+    float ms = 0.f;
+    if (cudaEventElapsedTime(&ms, ctx->marks[i - 1].ev, ctx->marks[i].ev) != cudaSuccess) { cudaGetLastError(); continue; }
+    const char *f = strrchr(ctx->marks[i].file, '/');
+    std::string key = std::string(f ? f + 1 : ctx->marks[i].file) + ":" + std::to_string(ctx->marks[i].line);
+    size_t k = 0;
+    while (k < sites.size() && sites[k].key != key) ++k;
+    if (k == sites.size()) { sites.push_back(Site()); sites[k].key = key; }
+    sites[k].ms += ms; sites[k].n++; total += ms;
+  }
+  for (auto &m : ctx->marks) cudaEventDestroy(m.ev);
+  ctx->marks.clear();
+  FILE *fp = fopen(path, "w");
+  if (!fp) return b200_fail(ctx, B200_ERR_INVALID, "trace_dump: cannot open %s", path);
+  fprintf(fp, "total_ms %.3f\n", total);
+  for (size_t a = 0; a < sites.size(); ++a) {      // selection sort, largest first
+    size_t best = a;
+    for (size_t b = a + 1; b < sites.size(); ++b) if (sites[b].ms > sites[best].ms) best = b;
+    std::swap(sites[a], sites[best]);
+    fprintf(fp, "%-28s launches %6zu  total_ms %9.3f  avg_us %9.2f  share %5.1f%%\n", sites[a].key.c_str(), sites[a].n, sites[a].ms,
+            1000.0 * sites[a].ms / (double)sites[a].n, 100.0 * sites[a].ms / total);
+  }
+  fclose(fp);
+  return B200_OK;
+}
+
 extern "C" int b200_batch_timer_begin(b200_ctx *ctx) {
   if (!ctx) return B200_ERR_INVALID;
   if (!ctx->batch_t0) { B200_CUDA(ctx, cudaEventCreate(&ctx->batch_t0)); B200_CUDA(ctx, cudaEventCreate(&ctx->batch_t1)); }

@@ -42,6 +42,10 @@ struct b200_ctx {
   std::vector<cudaEvent_t> event_pool;
   cudaEvent_t batch_t0 = nullptr, batch_t1 = nullptr;   // b200_batch_timer_begin / _end
   bool batch_timing = false;
+  // launch trace (b200_internal_trace): one event after every kernel launch, attributed to its source line
+  bool trace_on = false;
+  struct Mark { cudaEvent_t ev; const char *file; int line; };
+  std::vector<Mark> marks;
 };
 
 int b200_fail(b200_ctx *ctx, int code, const char *fmt, ...);
@@ -56,9 +60,11 @@ void *b200_scratch(b200_ctx *ctx, size_t bytes);
                        cudaGetErrorString(e_), __FILE__, __LINE__);                 \
   } while (0)
 
+void b200_trace_mark(b200_ctx *ctx, const char *file, int line);
 #define B200_LAUNCHED(ctx)                                                          \
   do {                                                                              \
     (ctx)->launches++;                                                              \
+    if ((ctx)->trace_on) b200_trace_mark((ctx), __FILE__, __LINE__);                \
     cudaError_t e_ = cudaGetLastError();                                            \
     if (e_ != cudaSuccess)                                                          \
       return b200_fail((ctx), B200_ERR_CUDA, "kernel launch failed: %s (%s:%d)",    \
@@ -144,8 +150,8 @@ struct GemmEpilogue {
   int S = 0, hd = 0, cols = 0;
   const int *pos_dev = nullptr;   // few-row kernel only: every row is at token position *pos_dev (decode; read on the device so that a captured step can be replayed)
   // W = [gate | up] (I columns each).  Few-row kernel: C[M, I] = silu(A*gate) * (A*up) and nothing else is written.
-  // Two-CTA kernel (act_out set): C[M, 2I] = A*W as usual AND act_out[M, I] = silu(gate) * up computed from the
-  // bf16-rounded values that were just stored (what the separate SwiGLU kernel would read back).
+  // Two-CTA kernel (act_out set): C[M, 2I] = A*W as usual AND act_out[M, I] = silu(gate) * up computed from the fp32
+  // accumulators (slightly more accurate than the separate SwiGLU kernel, which reads the bf16-rounded products back).
   int swiglu_I = 0;
   void *act_out = nullptr;
   size_t ld_act = 0;

@@ -19,7 +19,8 @@ constexpr int BM = 128, BN = 256, BK = 64, STAGES = 6;
 constexpr int A_STAGE_BYTES = BM * BK * 2;        // 16 KiB: this CTA's 128 rows
 constexpr int B_STAGE_BYTES = (BN / 2) * BK * 2;  // 16 KiB: this CTA's half of the 256 columns
 constexpr int CHUNK_BYTES = 64 * BK * 2;
-constexpr int SMEM_BYTES = STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + 1024 + 256;
+constexpr int STORE_STAGE_BYTES = 32 * 128;       // per epilogue warp: 32 rows x 128 B, the transposition buffer of the result stores
+constexpr int SMEM_BYTES = STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + 1024 + 256 + 4 * STORE_STAGE_BYTES;
 constexpr int THREADS = 192;
 constexpr int GROUP_M = 8;                        // 256-row tile pairs per rasterisation group
 constexpr uint32_t LEADER_MASK = 0xFEFFFFFFu;     // clears the CTA-rank bit of a shared::cluster address (rank 0)
@@ -72,53 +73,95 @@ __device__ __forceinline__ void tmem_dealloc_2sm(uint32_t taddr, uint32_t ncols)
 __device__ __forceinline__ void red_add_v4(float *p, float a, float b, float c, float d) {
   asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
 }
-// One 32-column chunk of one accumulator row -> global memory (optional rotary embedding, accumulate).
-// `red`: this tile is one K-split of several -> add into C with vector reductions instead of storing.
+// Rotary embedding of one 32-column chunk of an accumulator row (cpp/src/Positional.cpp:120-147): the 16 (cos, sin)
+// pairs of the chunk are fetched by rope_fetch -- early, so that their latency hides behind the wait for the accumulator
+// or the previous chunk's arithmetic -- and applied by rope_apply to the fp32 values before they are rounded.
+struct RopeVals { float4 c[4], s[4]; };
+__device__ __forceinline__ bool rope_wanted(const GemmEpilogue &epi, int row, int col, int M, int N) {
+  return epi.cos_t != nullptr && col < epi.cols && col + 32 <= N && row < M;
+}
+__device__ __forceinline__ void rope_fetch(RopeVals &v, const GemmEpilogue &epi, int row, int col) {
+  const int half = epi.hd >> 1;
+  const size_t tab = (size_t)(row % epi.S) * half + ((col % epi.hd) >> 1);
+  const float4 *c4 = reinterpret_cast<const float4 *>(epi.cos_t + tab), *s4 = reinterpret_cast<const float4 *>(epi.sin_t + tab);
+#pragma unroll
+  for (int g = 0; g < 4; ++g) { v.c[g] = __ldg(c4 + g); v.s[g] = __ldg(s4 + g); }
+}
+__device__ __forceinline__ void rope_apply(uint32_t (&r)[32], const RopeVals &v) {
+#pragma unroll
+  for (int g = 0; g < 4; ++g) {
+    const float cv[4] = {v.c[g].x, v.c[g].y, v.c[g].z, v.c[g].w}, sv[4] = {v.s[g].x, v.s[g].y, v.s[g].z, v.s[g].w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float x0 = __uint_as_float(r[g * 8 + 2 * j]), x1 = __uint_as_float(r[g * 8 + 2 * j + 1]);
+      r[g * 8 + 2 * j] = __float_as_uint(x0 * cv[j] - x1 * sv[j]);
+      r[g * 8 + 2 * j + 1] = __float_as_uint(x0 * sv[j] + x1 * cv[j]);
+    }
+  }
+}
+// Result stores.  An epilogue thread owns one accumulator ROW; written directly, one warp store instruction would touch
+// 32 rows with 16 bytes each (32 half-used sectors) -- measured, those stores, not the MMAs, bounded the kernel (a 756 GFLOP
+// GEMM took 0.49 ms without them, 0.55 ms with its bf16 result, 0.64 ms with a third output).  So each warp transposes
+// its 32-row chunk through a private, swizzled shared-memory buffer and writes whole row segments: one instruction covers
+// 8 rows x 64 B (bf16) or 4 rows x 128 B (fp32).  All 32 lanes must call; rows at or beyond rows_valid are not written.
+// base points at (first row of the warp, first column of the chunk).
+__device__ __forceinline__ void stage_store_bf16(uint8_t *stg, int lane, const uint4 (&v)[4], bf16 *base, size_t ld, int rows_valid) {
+#pragma unroll
+  for (int k = 0; k < 4; ++k) *reinterpret_cast<uint4 *>(stg + lane * 64 + ((k ^ ((lane >> 1) & 3)) << 4)) = v[k];
+  __syncwarp();
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int r = 8 * i + (lane >> 2), w = lane & 3;
+    const uint4 x = *reinterpret_cast<const uint4 *>(stg + r * 64 + ((w ^ ((r >> 1) & 3)) << 4));
+    if (r < rows_valid) *reinterpret_cast<uint4 *>(base + (size_t)r * ld + w * 8) = x;
+  }
+  __syncwarp();
+}
+__device__ __forceinline__ void pack_chunk_bf16(const uint32_t (&r)[32], uint4 (&v)[4]) {
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    uint32_t *po = &v[k].x;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[k * 8 + 2 * j]), __uint_as_float(r[k * 8 + 2 * j + 1]));
+      po[j] = *reinterpret_cast<uint32_t *>(&h);
+    }
+  }
+}
+// One 32-column chunk of the warp's 32 accumulator rows -> global memory.  Warp-collective: every lane calls it with its
+// own row's values (lane = row - row0); `red`: this tile is one K-split of several -> add into C with vector reductions.
 template <class TO, bool ACC>
-__device__ __forceinline__ void store_chunk(uint32_t (&r)[32], TO *crow, int row, int col, int N, const GemmEpilogue &epi,
-                                            bool red) {
+__device__ __forceinline__ void store_chunk(uint32_t (&r)[32], TO *C, size_t ldc, int row0, int lane, int col, int M, int N,
+                                            uint8_t *stg, bool red) {
+  const int rows_valid = M - row0;
   if (col + 32 <= N) {
     if constexpr (sizeof(TO) == 2) {
-      if (epi.cos_t != nullptr && col < epi.cols) {
-        const int half = epi.hd >> 1;
-        const size_t tab = (size_t)(row % epi.S) * half + ((col % epi.hd) >> 1);
-        const float4 *c4 = reinterpret_cast<const float4 *>(epi.cos_t + tab), *s4 = reinterpret_cast<const float4 *>(epi.sin_t + tab);
-#pragma unroll
-        for (int g = 0; g < 4; ++g) {
-          const float4 cc = __ldg(c4 + g), ss = __ldg(s4 + g);
-          const float cv[4] = {cc.x, cc.y, cc.z, cc.w}, sv[4] = {ss.x, ss.y, ss.z, ss.w};
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const float x0 = __uint_as_float(r[g * 8 + 2 * j]), x1 = __uint_as_float(r[g * 8 + 2 * j + 1]);
-            r[g * 8 + 2 * j] = __float_as_uint(x0 * cv[j] - x1 * sv[j]);
-            r[g * 8 + 2 * j + 1] = __float_as_uint(x0 * sv[j] + x1 * cv[j]);
-          }
-        }
-      }
-#pragma unroll
-      for (int v = 0; v < 4; ++v) {
-        uint4 o;
-        uint32_t *po = &o.x;
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[v * 8 + 2 * j]), __uint_as_float(r[v * 8 + 2 * j + 1]));
-          po[j] = *reinterpret_cast<uint32_t *>(&h);
-        }
-        *reinterpret_cast<uint4 *>(crow + col + v * 8) = o;
-      }
+      uint4 v[4];
+      pack_chunk_bf16(r, v);
+      stage_store_bf16(stg, lane, v, reinterpret_cast<bf16 *>(C) + (size_t)row0 * ldc + col, ldc, rows_valid);
     } else {
 #pragma unroll
-      for (int v = 0; v < 8; ++v) {
-        float4 o = make_float4(__uint_as_float(r[v * 4]), __uint_as_float(r[v * 4 + 1]), __uint_as_float(r[v * 4 + 2]), __uint_as_float(r[v * 4 + 3]));
-        if (red) { red_add_v4(reinterpret_cast<float *>(crow + col + v * 4), o.x, o.y, o.z, o.w); continue; }
-        if (ACC) {
-          float4 p = *reinterpret_cast<const float4 *>(crow + col + v * 4);
-          o.x += p.x; o.y += p.y; o.z += p.z; o.w += p.w;
+      for (int k = 0; k < 8; ++k)
+        *reinterpret_cast<uint4 *>(stg + lane * 128 + ((k ^ (lane & 7)) << 4)) = make_uint4(r[4 * k], r[4 * k + 1], r[4 * k + 2], r[4 * k + 3]);
+      __syncwarp();
+      float *base = reinterpret_cast<float *>(C) + (size_t)row0 * ldc + col;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int rr = 4 * i + (lane >> 3), w = lane & 7;
+        const uint4 x = *reinterpret_cast<const uint4 *>(stg + rr * 128 + ((w ^ (rr & 7)) << 4));
+        if (rr < rows_valid) {
+          float *p = base + (size_t)rr * ldc + w * 4;
+          float4 o = make_float4(__uint_as_float(x.x), __uint_as_float(x.y), __uint_as_float(x.z), __uint_as_float(x.w));
+          if (red) { red_add_v4(p, o.x, o.y, o.z, o.w); continue; }
+          if (ACC) { const float4 q = *reinterpret_cast<const float4 *>(p); o.x += q.x; o.y += q.y; o.z += q.z; o.w += q.w; }
+          *reinterpret_cast<float4 *>(p) = o;
         }
-        *reinterpret_cast<float4 *>(crow + col + v * 4) = o;
       }
+      __syncwarp();
     }
-  } else {
+  } else if (lane < rows_valid) {
+    // ragged last columns: each thread writes its own row element by element
+    TO *crow = C + (size_t)(row0 + lane) * ldc;
 #pragma unroll
     for (int j = 0; j < 32; ++j) {
       if (col + j < N) {
@@ -133,12 +176,15 @@ __device__ __forceinline__ void store_chunk(uint32_t (&r)[32], TO *crow, int row
   }
 }
 
+__device__ __forceinline__ float tanh_approx(float x) { float y; asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
 __device__ __forceinline__ float ex2(float x) { float y; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
 constexpr float LOG2E = 1.4426950408889634f;
 
 // Cross-entropy epilogue of one accumulator row (one thread) over the 256 columns of a tile; see GemmEpilogue::ce_mode.
 // Softmax statistics are kept in base-2 units (x * log2e): one FMA and one ex2 per element.
-__device__ __forceinline__ void ce_row_epilogue(uint32_t taddr, bf16 *crow, int row, int tn, int M, int N, const GemmEpilogue &epi) {
+__device__ __forceinline__ void ce_row_epilogue(uint32_t taddr, bf16 *C, size_t ldc, int row0, int lane, int tn, int M, int N,
+                                                const GemmEpilogue &epi, uint8_t *stg) {
+  const int row = row0 + lane;
   const bool row_ok = row < M;
   const uint32_t tgt = row_ok ? __ldg(epi.ce_targets + row) : 0xffffffffu;
   const int col0 = tn * BN;
@@ -151,14 +197,16 @@ __device__ __forceinline__ void ce_row_epilogue(uint32_t taddr, bf16 *crow, int 
       tc::tmem_ld_32x32(taddr + c * 32, r);
       tc::tmem_ld_wait();
       const int col = col0 + c * 32;
-      if (row_ok && col < N) {
+      if (col < N) {
+        if (row_ok) {
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          float p = ex2(fmaf(__uint_as_float(r[j]), LOG2E, -lse2));
-          if ((uint32_t)(col + j) == tgt) p -= 1.0f;
-          r[j] = __float_as_uint(p * epi.ce_scale);
+          for (int j = 0; j < 32; ++j) {
+            float p = ex2(fmaf(__uint_as_float(r[j]), LOG2E, -lse2));
+            if ((uint32_t)(col + j) == tgt) p -= 1.0f;
+            r[j] = __float_as_uint(p * epi.ce_scale);
+          }
         }
-        store_chunk<bf16, false>(r, crow, row, col, N, epi, false);
+        store_chunk<bf16, false>(r, C, ldc, row0, lane, col, M, N, stg, false);
       }
     }
     return;
@@ -171,12 +219,14 @@ __device__ __forceinline__ void ce_row_epilogue(uint32_t taddr, bf16 *crow, int 
     tc::tmem_ld_32x32(taddr + c * 32, r);
     tc::tmem_ld_wait();
     const int col = col0 + c * 32;
-    if (!(row_ok && col < N)) continue;
+    if (col >= N) continue;                                   // warp-uniform
     if (epi.ce_mode == 2) {
       // the stored logits are bf16: take the statistics from the rounded values, which is what a later pass reads back
+      store_chunk<bf16, false>(r, C, ldc, row0, lane, col, M, N, stg, false);
 #pragma unroll
       for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__bfloat162float(__float2bfloat16_rn(__uint_as_float(r[j]))));
     }
+    if (!row_ok) continue;
     if (tgt - (uint32_t)col < 32u) {
 #pragma unroll
       for (int j = 0; j < 32; ++j) if ((uint32_t)(col + j) == tgt) tl = __uint_as_float(r[j]);
@@ -194,7 +244,6 @@ __device__ __forceinline__ void ce_row_epilogue(uint32_t taddr, bf16 *crow, int 
     for (int j = 0; j < 32; ++j) acc += ex2(t[j] - mn);
     s = s * ex2(m2 - mn) + acc;
     m2 = mn;
-    if (epi.ce_mode == 2) store_chunk<bf16, false>(r, crow, row, col, N, epi, false);
   }
   if (row_ok) {
     epi.ce_part_max[(size_t)tn * M + row] = m2;
@@ -310,18 +359,24 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     }
   } else {
     const int q = warp & 3;                        // tensor-memory lane quarter this warp may read
+    uint8_t *stg = smem + STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + 256 + (warp - 2) * STORE_STAGE_BYTES;
     int acc = 0; uint32_t acc_phase = 0;
     bool ok = true;
     for (int it = cluster_id; it < items && ok; it += n_clusters) {
       int tm, tn; tile_coords(it % total, tm, tn);
+      const int row0 = tm * 2 * BM + (int)rank * BM + q * 32, row = row0 + lane;
+      RopeVals rope_now, rope_next;
+      bool rope0 = false;
+      if constexpr (sizeof(TO) == 2 && !ACC) {
+        rope0 = !swiglu && !epi.ce_mode && rope_wanted(epi, row, tn * BN, M, N);
+        if (rope0) rope_fetch(rope_now, epi, row, tn * BN);        // in flight while this warp waits for the MMAs
+      }
       if (!tc::mbar_wait(&sh->acc_full[acc], acc_phase, status, abort_flag, 114)) { ok = false; break; }
       tc::tc_fence_after();
-      const int row = tm * 2 * BM + (int)rank * BM + q * 32 + lane;
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN;
-      TO *crow = C + (size_t)row * ldc;
       if constexpr (sizeof(TO) == 2 && !ACC) {
         if (epi.ce_mode) {
-          ce_row_epilogue(taddr, (bf16 *)crow, row, tn, M, N, epi);
+          ce_row_epilogue(taddr, (bf16 *)C, ldc, row0, lane, tn, M, N, epi, stg);
           tc::tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive_cluster(tc::smem_u32(&sh->acc_empty[acc]) & LEADER_MASK);
@@ -329,7 +384,6 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           continue;
         }
         if (swiglu) {
-          bf16 *arow = (bf16 *)epi.act_out + (size_t)row * epi.ld_act;
 #pragma unroll 1
           for (int c = 0; c < BN / 64; ++c) {
             uint32_t g[32], u[32];
@@ -337,26 +391,22 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             tc::tmem_ld_32x32(taddr + BN / 2 + c * 32, u);
             tc::tmem_ld_wait();
             const int col = tn * (BN / 2) + c * 32;
-            if (row < M && col < epi.swiglu_I) {
+            if (col < epi.swiglu_I) {               // warp-uniform; swiglu_I is a multiple of 32
+              uint4 vg[4], vu[4], va[4];
+              pack_chunk_bf16(g, vg);
+              pack_chunk_bf16(u, vu);
+              // silu(x) = x * sigmoid(x) = h + h * tanh(h) with h = x / 2: one special-function op and two FMA-pipe ops
+              // per element, taken from the fp32 accumulators
 #pragma unroll
-              for (int v = 0; v < 4; ++v) {
-                uint4 og, ou, oa;
-                uint32_t *pg = &og.x, *pu = &ou.x, *pa = &oa.x;
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                  const __nv_bfloat162 hg = __floats2bfloat162_rn(__uint_as_float(g[v * 8 + 2 * j]), __uint_as_float(g[v * 8 + 2 * j + 1]));
-                  const __nv_bfloat162 hu = __floats2bfloat162_rn(__uint_as_float(u[v * 8 + 2 * j]), __uint_as_float(u[v * 8 + 2 * j + 1]));
-                  const float2 gf = __bfloat1622float2(hg), uf = __bfloat1622float2(hu);
-                  const float s0 = 1.0f / (1.0f + __expf(-gf.x)), s1 = 1.0f / (1.0f + __expf(-gf.y));
-                  const __nv_bfloat162 ha = __floats2bfloat162_rn(gf.x * s0 * uf.x, gf.y * s1 * uf.y);
-                  pg[j] = *reinterpret_cast<const uint32_t *>(&hg);
-                  pu[j] = *reinterpret_cast<const uint32_t *>(&hu);
-                  pa[j] = *reinterpret_cast<const uint32_t *>(&ha);
-                }
-                *reinterpret_cast<uint4 *>(crow + col + v * 8) = og;
-                *reinterpret_cast<uint4 *>(crow + epi.swiglu_I + col + v * 8) = ou;
-                *reinterpret_cast<uint4 *>(arow + col + v * 8) = oa;
+              for (int j = 0; j < 32; ++j) {
+                const float h = 0.5f * __uint_as_float(g[j]);
+                g[j] = __float_as_uint(fmaf(h, tanh_approx(h), h) * __uint_as_float(u[j]));
               }
+              pack_chunk_bf16(g, va);
+              bf16 *cbase = (bf16 *)C + (size_t)row0 * ldc + col;
+              stage_store_bf16(stg, lane, vg, cbase, ldc, M - row0);
+              stage_store_bf16(stg, lane, vu, cbase + epi.swiglu_I, ldc, M - row0);
+              stage_store_bf16(stg, lane, va, (bf16 *)epi.act_out + (size_t)row0 * epi.ld_act + col, epi.ld_act, M - row0);
             }
           }
           tc::tc_fence_before();
@@ -370,9 +420,19 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t r[32];
         tc::tmem_ld_32x32(taddr + c * 32, r);
-        tc::tmem_ld_wait();
         const int col = tn * BN + c * 32;
-        if (row < M && col < N) store_chunk<TO, ACC>(r, crow, row, col, N, epi, splits > 1);
+        bool rope_ahead = false;
+        if constexpr (sizeof(TO) == 2 && !ACC) {
+          rope_ahead = c + 1 < BN / 32 && rope_wanted(epi, row, col + 32, M, N);
+          if (rope_ahead) rope_fetch(rope_next, epi, row, col + 32);
+        }
+        tc::tmem_ld_wait();
+        if constexpr (sizeof(TO) == 2 && !ACC) {
+          if (rope0) rope_apply(r, rope_now);
+          rope0 = rope_ahead;
+          if (rope_ahead) rope_now = rope_next;
+        }
+        if (col < N) store_chunk<TO, ACC>(r, C, ldc, row0, lane, col, M, N, stg, splits > 1);
       }
       tc::tc_fence_before();
       __syncwarp();
@@ -433,6 +493,15 @@ int launch_variant(b200_ctx *ctx, const CUtensorMap &ma, const CUtensorMap &mb, 
   if (splits > 1 && !ACC) B200_CUDA(ctx, cudaMemsetAsync(C, 0, (size_t)M * N * sizeof(float), ctx->stream));
   B200_CUDA(ctx, cudaLaunchKernelEx(&cfg, kern, ma, mb, (TO *)C, M, N, K, ldc, ctx->dev_status, epi, splits));
   ctx->launches++;
+  if (ctx->trace_on) {      // one trace site per GEMM shape and form
+    static std::vector<std::string *> keys;
+    char buf[96];
+    snprintf(buf, sizeof(buf), "gemm2 %dx%dx%d %s%s%s ce%d sk%d", M, N, K, A_MN ? "T" : "N", B_MN ? "N" : "T", sizeof(TO) == 4 ? " f32" : "", epi.ce_mode, splits);
+    std::string *k = nullptr;
+    for (auto *p : keys) if (*p == buf) k = p;
+    if (!k) { k = new std::string(buf); keys.push_back(k); }
+    b200_trace_mark(ctx, k->c_str(), 0);
+  }
   if (ctx->time_gemm) { cudaEventRecord(tm.stop, ctx->stream); ctx->timed.push_back(tm); }
   return B200_OK;
 }

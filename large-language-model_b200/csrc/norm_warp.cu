@@ -334,6 +334,7 @@ int rms_fwd_warp(b200_ctx *ctx, const void *x, void *h, const void *r, const voi
     else { if (add) FR(2, true); else FR(2, false); }
 #undef FR
     ctx->launches++;
+    if (ctx->trace_on) b200_trace_mark(ctx, __FILE__, __LINE__);
     if (cudaGetLastError() != cudaSuccess) return b200_fail(ctx, B200_ERR_CUDA, "rms_norm forward launch failed");
     return 1;
   }
@@ -349,6 +350,7 @@ int rms_fwd_warp(b200_ctx *ctx, const void *x, void *h, const void *r, const voi
   }
 #undef FW
   ctx->launches++;
+  if (ctx->trace_on) b200_trace_mark(ctx, __FILE__, __LINE__);
   if (cudaGetLastError() != cudaSuccess) return b200_fail(ctx, B200_ERR_CUDA, "rms_norm forward launch failed");
   return 1;
 }
@@ -371,6 +373,7 @@ int rms_bwd_warp(b200_ctx *ctx, const void *g, const void *x, const void *w, con
 #undef BWV
 #undef BW
   ctx->launches++;
+  if (ctx->trace_on) b200_trace_mark(ctx, __FILE__, __LINE__);
   if (cudaGetLastError() != cudaSuccess) return b200_fail(ctx, B200_ERR_CUDA, "rms_norm backward launch failed");
   return 1;
 }
@@ -388,12 +391,14 @@ int rms_bwd2_warp(b200_ctx *ctx, const void *g, const void *h, const void *w, co
     case 1: B2(1, 1); break;
     case 2: B2(2, 1); break;
     case 4: B2(4, 1); break;
-    case 8: B2(4, 2); break;
-    case 16: B2(4, 4); break;
+    // wide rows: several warps per row, few enough vectors per lane that two CTAs fit the register file of an SM
+    case 8: if (sizeof(T) == 2) B2(2, 4); else B2(4, 2); break;
+    case 16: if (sizeof(T) == 2) B2(2, 8); else B2(4, 4); break;
     default: return 0;
   }
 #undef B2
   ctx->launches++;
+  if (ctx->trace_on) b200_trace_mark(ctx, __FILE__, __LINE__);
   if (cudaGetLastError() != cudaSuccess) return b200_fail(ctx, B200_ERR_CUDA, "double rms_norm backward launch failed");
   return 1;
 }

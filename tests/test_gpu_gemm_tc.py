@@ -142,7 +142,9 @@ def test_ffn_gemm_with_the_activation_in_the_epilogue(ctx, M, I, K, want):
     ref_act = synth.bf16_round(g / (1.0 + np.exp(-g)) * u)
     if want:
         np.testing.assert_array_equal(res[1].download(), plain)
-        assert rel(act, ref_act) < 4e-3                     # same bf16 inputs; device exp differs in the last ulp
+        assert rel(act, ref_act) < 6e-3                     # the epilogue activates the fp32 accumulators, the reference the rounded products
+        exact = x.astype(np.float64) @ w.astype(np.float64)
+        assert rel(act, exact[:, :I] / (1.0 + np.exp(-exact[:, :I])) * exact[:, I:]) < 5e-3
     else:
         exact = x.astype(np.float64) @ w.astype(np.float64)
         ge, ue = exact[:, :I], exact[:, I:]

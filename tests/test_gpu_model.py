@@ -144,7 +144,10 @@ def test_bf16_model_against_fp32_checker(ctx, orc, cfgd):
         grads1 = model.read_grads()
     finally:
         ctx.lib.b200_internal_set_gemm_2cta(ctx.h, 1)
-    assert abs(loss1 - loss) < 1e-4 * abs(loss) and rel(grads1, grads) < 2e-3
+    # the two-CTA epilogue activates the fp32 accumulators, the separate kernel the bf16-rounded products: the two
+    # routes differ by one bf16 rounding of gate and up, both stay inside the gate against the checker
+    assert abs(loss1 - loss) < 2e-4 * abs(loss) and rel(grads1, grads) < 6e-3, (loss1, loss, rel(grads1, grads))
+    assert rel(grads1[-cfg.H * cfg.V:], grads_ref[-cfg.H * cfg.V:]) < BF16_TOL and rel(grads1[:e], grads_ref[:e]) < BF16_TOL
     model.close()
 
 
