@@ -15,7 +15,8 @@ import os
 import numpy as np
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libb200bridge.so")
+# B200_BRIDGE_LIB names another build of the same library (A/B measurements of two kernel versions in one run)
+LIB_PATH = os.environ.get("B200_BRIDGE_LIB") or os.path.join(_HERE, "libb200bridge.so")
 F32, BF16 = 0, 1
 _synth = importlib.import_module(__package__ + ".synth") if __package__ else None
 

@@ -261,7 +261,8 @@ attn_bwd_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_const
 template <int HD>
 __global__ void __launch_bounds__(256)
 attn_dsum_kernel(const bf16 *__restrict__ O, const bf16 *__restrict__ dO, float *__restrict__ D, int B, int nH, int S,
-                 long long o_b, long long o_h, long long o_s, const float *__restrict__ lse, float *__restrict__ lse2) {
+                 long long o_b, long long o_h, long long o_s, const float *__restrict__ lse, float *__restrict__ lse2,
+                 float *__restrict__ zero_acc) {
   constexpr int VEC = HD / 8;                       // elements per lane: 16 (32 bytes) or 8 (16 bytes)
   typedef typename std::conditional<VEC == 16, uint4, uint2>::type Raw;   // loaded in 16- or 8-byte pieces
   constexpr int PIECES = VEC * 2 / (int)sizeof(Raw);
@@ -288,11 +289,20 @@ attn_dsum_kernel(const bf16 *__restrict__ O, const bf16 *__restrict__ dO, float 
     acc += __shfl_xor_sync(0xffffffffu, acc, 4);
     acc += __shfl_xor_sync(0xffffffffu, acc, 2);
     acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-    if (sub == 0 && r < rows) {
+    if (r < rows) {
       const int h = (int)(r % nH), s = (int)((r / nH) % S), b = (int)(r / ((long long)nH * S));
       const long long at = ((long long)b * nH + h) * S + s;
-      D[at] = acc;
-      if (lse2) lse2[at] = lse[at] * LOG2E;             // the row's log-sum-exp in base-2 units for the second backward form
+      if (sub == 0) {
+        D[at] = acc;
+        if (lse2) lse2[at] = lse[at] * LOG2E;           // the row's log-sum-exp in base-2 units for the second backward form
+      }
+      if (zero_acc) {
+        // the row of the fp32 dQ accumulator starts at zero: cleared here, 64 bytes per lane, instead of by a memset of
+        // its own in front of this kernel
+        float4 *z = reinterpret_cast<float4 *>(zero_acc + at * HD + sub * VEC);
+#pragma unroll
+        for (int p = 0; p < VEC / 4; ++p) z[p] = make_float4(0.f, 0.f, 0.f, 0.f);
+      }
     }
   };
   for (long long r0 = group * 2; r0 < rows; r0 += n_groups * 2) {      // the shuffles need every lane: rows past the end are clamped
@@ -347,11 +357,10 @@ int bwd_launch_t(b200_ctx *ctx, const void *Q, const void *K, const void *V, con
   if (!scr) return B200_ERR_NOMEM;
   float *Dsum = scr, *lse2 = scr + d_elems, *dQacc = scr + 2 * d_elems;
   const bool second_form = HD == 128 && ctx->attn_bwd2 && attn_bwd2_supported(S, HD);
-  B200_CUDA(ctx, cudaMemsetAsync(dQacc, 0, rows * HD * sizeof(float), ctx->stream));
   {
     size_t blocks = (rows + 63) / 64, cap = (size_t)ctx->sm_count * 16;      // 32 lane groups x 2 rows per block pass
     attn_dsum_kernel<HD><<<(int)(blocks < cap ? blocks : cap), 256, 0, ctx->stream>>>((const bf16 *)O, (const bf16 *)dO, Dsum, (int)B, (int)nH, (int)S,
-                                                                                      st.o_b, st.o_h, st.o_s, lse, second_form ? lse2 : nullptr);
+                                                                                      st.o_b, st.o_h, st.o_s, lse, second_form ? lse2 : nullptr, dQacc);
     B200_LAUNCHED(ctx);
   }
   if (second_form) {

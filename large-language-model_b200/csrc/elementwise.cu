@@ -430,39 +430,25 @@ __global__ void swiglu_fwd_kernel(const T *__restrict__ gate, const T *__restric
     Vec16<T> ov; ov.pack(o); ov.store(out + r * ld_out + c);
   }
 }
-// Four independent 16-byte vectors per thread and stream are in flight before any is used (12 loads per thread), and the
-// row / column split is 32-bit arithmetic (the index space of one call is far below 2^32 vectors).
 template <class T>
-__global__ void __launch_bounds__(256)
-swiglu_bwd_kernel(const T *__restrict__ dy, const T *__restrict__ gate, const T *__restrict__ up,
-                  T *__restrict__ dgate, T *__restrict__ dup, size_t rows, size_t cols, size_t ld_dy,
-                  size_t ld_in, size_t ld_out) {
-  constexpr int N = Vec16<T>::N, U = 4;
-  const uint32_t vec_per_row = (uint32_t)(cols / N), total = (uint32_t)(rows * vec_per_row);
-  const uint32_t stride = gridDim.x * blockDim.x;
-  for (uint32_t idx0 = blockIdx.x * blockDim.x + threadIdx.x; idx0 < total; idx0 += U * stride) {
-    Vec16<T> a[U], b[U], d[U];
-    size_t off_in[U], off_dy[U], off_out[U];
+__global__ void swiglu_bwd_kernel(const T *__restrict__ dy, const T *__restrict__ gate, const T *__restrict__ up,
+                                  T *__restrict__ dgate, T *__restrict__ dup, size_t rows, size_t cols, size_t ld_dy,
+                                  size_t ld_in, size_t ld_out) {
+  constexpr int N = Vec16<T>::N;
+  size_t vec_per_row = cols / N, total = rows * vec_per_row;
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+    size_t r = idx / vec_per_row, c = (idx % vec_per_row) * N;
+    Vec16<T> a, b, d; float g[N], u[N], y[N], og[N], ou[N];
+    a.load(gate + r * ld_in + c); a.unpack(g);
+    b.load(up + r * ld_in + c); b.unpack(u);
+    d.load(dy + r * ld_dy + c); d.unpack(y);
 #pragma unroll
-    for (int k = 0; k < U; ++k) {
-      const uint32_t idx = idx0 + k * stride;
-      const uint32_t r = idx / vec_per_row, c = (idx - r * vec_per_row) * N;
-      off_in[k] = (size_t)r * ld_in + c; off_dy[k] = (size_t)r * ld_dy + c; off_out[k] = (size_t)r * ld_out + c;
-      if (idx < total) { a[k].load(gate + off_in[k]); b[k].load(up + off_in[k]); d[k].load(dy + off_dy[k]); }
+    for (int j = 0; j < N; ++j) {
+      float sig = 1.0f / (1.0f + __expf(-g[j]));
+      ou[j] = y[j] * g[j] * sig;
+      og[j] = y[j] * u[j] * sig * (1.0f + g[j] * (1.0f - sig));
     }
-#pragma unroll
-    for (int k = 0; k < U; ++k) {
-      if (idx0 + k * stride >= total) break;
-      float g[N], u[N], y[N], og[N], ou[N];
-      a[k].unpack(g); b[k].unpack(u); d[k].unpack(y);
-#pragma unroll
-      for (int j = 0; j < N; ++j) {
-        float sig = 1.0f / (1.0f + __expf(-g[j]));
-        ou[j] = y[j] * g[j] * sig;
-        og[j] = y[j] * u[j] * sig * (1.0f + g[j] * (1.0f - sig));
-      }
-      Vec16<T> v1, v2; v1.pack(og); v1.store(dgate + off_out[k]); v2.pack(ou); v2.store(dup + off_out[k]);
-    }
+    Vec16<T> v1, v2; v1.pack(og); v1.store(dgate + r * ld_out + c); v2.pack(ou); v2.store(dup + r * ld_out + c);
   }
 }
 template <class T>
@@ -508,8 +494,8 @@ int swiglu_bwd_strided(b200_ctx *ctx, const void *dy, const void *gate, const vo
   size_t N = 16 / dtype_size(dt);
   bool vec = cols % N == 0 && ld_in % N == 0 && ld_out % N == 0 && ld_dy % N == 0 &&
              (((uintptr_t)gate | (uintptr_t)up | (uintptr_t)dy | (uintptr_t)dgate | (uintptr_t)dup) % 16 == 0);
-  if (vec && rows * cols / N < 0xffffffffull - 4 * 256 * 65536ull) {
-    int grid = ew_grid(ctx, rows * cols / N / 4 + 1);
+  if (vec) {
+    int grid = ew_grid(ctx, rows * cols / N);
     if (dt == B200_BF16) swiglu_bwd_kernel<bf16><<<grid, 256, 0, ctx->stream>>>((const bf16 *)dy, (const bf16 *)gate, (const bf16 *)up, (bf16 *)dgate, (bf16 *)dup, rows, cols, ld_dy, ld_in, ld_out);
     else swiglu_bwd_kernel<float><<<grid, 256, 0, ctx->stream>>>((const float *)dy, (const float *)gate, (const float *)up, (float *)dgate, (float *)dup, rows, cols, ld_dy, ld_in, ld_out);
   } else {

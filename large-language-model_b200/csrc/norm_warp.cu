@@ -236,7 +236,7 @@ rms_bwd_warp_kernel(const T *__restrict__ g, const T *__restrict__ x, const T *_
 // WPR warps share a row (a 2048-wide bf16 row held by one warp, widened to floats, does not fit in the register file);
 // their partial sums meet in shared memory behind a named barrier of the row's WPR*32 threads.
 template <class T, int VPL, int WPR>
-__global__ void __launch_bounds__(WARPS_PER_CTA * 32)
+__global__ void __launch_bounds__(WARPS_PER_CTA * 32, VPL <= 2 ? 2 : 1)
 rms_bwd2_warp_kernel(const T *__restrict__ g, const T *__restrict__ h, const T *__restrict__ w,
                      const T *__restrict__ res_grad, T *__restrict__ dx, float eps, size_t rows, int D) {
   constexpr int N = Vec16<T>::N, ROWS_PER_CTA = WARPS_PER_CTA / WPR;
@@ -255,21 +255,28 @@ rms_bwd2_warp_kernel(const T *__restrict__ g, const T *__restrict__ h, const T *
   };
   const size_t n_slots = (size_t)gridDim.x * ROWS_PER_CTA;
   // every warp of a row group runs the same number of iterations (the barrier counts on it)
-  for (size_t row = (size_t)blockIdx.x * ROWS_PER_CTA + slot; row < rows; row += n_slots) {
+  auto at = [&](int i) { return (size_t)((i * WPR + sub) * 32 + lane) * N; };
+  size_t row = (size_t)blockIdx.x * ROWS_PER_CTA + slot;
+  Vec16<T> ha[VPL], ga[VPL], ra[VPL];
+  if (row < rows) {
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) { ha[i].load(h + row * (size_t)D + at(i)); ga[i].load(g + row * (size_t)D + at(i)); ra[i].load(res_grad + row * (size_t)D + at(i)); }
+  }
+  for (; row < rows; row += n_slots) {
     const size_t base = row * (size_t)D;
-    auto at = [&](int i) { return (size_t)((i * WPR + sub) * 32 + lane) * N; };
-    Vec16<T> ha[VPL], ga[VPL], ra[VPL];
-#pragma unroll
-    for (int i = 0; i < VPL; ++i) { ha[i].load(h + base + at(i)); ga[i].load(g + base + at(i)); }
-#pragma unroll
-    for (int i = 0; i < VPL; ++i) ra[i].load(res_grad + base + at(i));
-    float hv[VPL][N], gv[VPL][N], a1[VPL][N];
+    float hv[VPL][N], gv[VPL][N], a1[VPL][N], rv[VPL][N];
     float ss1 = 0.f;
 #pragma unroll
     for (int i = 0; i < VPL; ++i) {
-      ha[i].unpack(hv[i]);
+      ha[i].unpack(hv[i]); ga[i].unpack(gv[i]); ra[i].unpack(rv[i]);
 #pragma unroll
       for (int j = 0; j < N; ++j) ss1 += hv[i][j] * hv[i][j];
+    }
+    // the next row of this group is requested now: its latency hides behind the four reductions of the current row
+    if (row + n_slots < rows) {
+      const size_t nb = (row + n_slots) * (size_t)D;
+#pragma unroll
+      for (int i = 0; i < VPL; ++i) { ha[i].load(h + nb + at(i)); ga[i].load(g + nb + at(i)); ra[i].load(res_grad + nb + at(i)); }
     }
     const float rstd1 = rsqrtf(row_sum(ss1, 0) * inv_d + eps);
     // a1 as the forward stored it, and the statistics of the second norm
@@ -278,7 +285,6 @@ rms_bwd2_warp_kernel(const T *__restrict__ g, const T *__restrict__ h, const T *
     for (int i = 0; i < VPL; ++i) {
       Vec16<T> wv; float wf[N];
       wv.load(w + at(i)); wv.unpack(wf);
-      ga[i].unpack(gv[i]);
 #pragma unroll
       for (int j = 0; j < N; ++j) {
         a1[i][j] = to_f(from_f<T>(hv[i][j] * rstd1 * wf[j]));
@@ -303,9 +309,8 @@ rms_bwd2_warp_kernel(const T *__restrict__ g, const T *__restrict__ h, const T *
 #pragma unroll
     for (int i = 0; i < VPL; ++i) {
       float o[N];
-      ra[i].unpack(o);
 #pragma unroll
-      for (int j = 0; j < N; ++j) o[j] += rstd1 * (gv[i][j] - hv[i][j] * rstd1 * s1);
+      for (int j = 0; j < N; ++j) o[j] = rv[i][j] + rstd1 * (gv[i][j] - hv[i][j] * rstd1 * s1);
       Vec16<T> ov; ov.pack(o); ov.store(dx + base + at(i));
     }
   }
