@@ -9,6 +9,7 @@ random-init N(0, 0.02) weights.
     python bench.py --workload decode [--layers L]           # only the decode workload (batch 32, prompt 512, +256 tokens)
 
     python bench.py --workload ops                           # only the per-op figures (attention, projections, bandwidth kernels)
+    python bench.py --workload trace --steps 3               # in-step device time per launch site (table on stdout, not a JSON line)
 
 Prints ONE JSON line on rank 0.  For N > 1 launch with torch.distributed.run (one rank per GPU).
 `value` is whole-job tokens/s with inputs resident in HBM; `e2e` is the same step driven from
@@ -485,6 +486,36 @@ def run_ops(args):
                       "attention": att, "ops": ops}))
 
 
+def run_trace(args):
+    """In-step device time per launch site: an event after every kernel launch of the library during `--steps` training
+    steps (after `--warmup` untraced ones); the time between consecutive events goes to the later launch's source line, or
+    to the GEMM's shape.  Prints the table (development aid; the events themselves cost about 1 % of the step)."""
+    import tempfile
+    bridge = importlib.import_module(PKG + ".bridge")
+    synth = importlib.import_module(PKG + ".synth")
+    B, S = args.batch, args.seq
+    cfg = bridge.Shape(B=B, S=S, H=MODEL["H"], I=MODEL["I"], nH=MODEL["nH"], nKV=MODEL["nKV"], hd=MODEL["hd"], V=MODEL["V"], L=args.layers)
+    ctx = bridge.Context(int(os.environ.get("LOCAL_RANK", "0")))
+    ctx.lib.b200_internal_trace.argtypes = [bridge._vp, bridge._i]
+    ctx.lib.b200_internal_trace_dump.argtypes = [bridge._vp, bridge.C.c_char_p]
+    model = bridge.Model(ctx, cfg, "bf16", max_batch=B)
+    model.init_synthetic(1234, 0.02)
+    tok = synth.token_ids(1000, "tokens", (B, S + 1), MODEL["V"])
+    d_tok, d_tgt = ctx.array(np.ascontiguousarray(tok[:, :-1]), "i32"), ctx.array(np.ascontiguousarray(tok[:, 1:]), "i32")
+    for _ in range(max(1, args.warmup)):
+        model.train_step(d_tok, d_tgt, B, S, **HYPER)
+    ctx.sync()
+    ctx.lib.b200_internal_trace(ctx.h, 1)
+    for _ in range(args.steps):
+        model.train_step(d_tok, d_tgt, B, S, **HYPER)
+    ctx.lib.b200_internal_trace(ctx.h, 0)
+    with tempfile.NamedTemporaryFile("r", suffix=".txt") as f:
+        ctx._check(ctx.lib.b200_internal_trace_dump(ctx.h, f.name.encode()))
+        print(f"# {args.steps} traced steps, {args.layers} layers, batch {B} x seq {S}")
+        print(open(f.name).read())
+    model.close(); ctx.close()
+
+
 def dp_check(ctx, bridge, synth, dist, rank, world, local):
     """Data-parallel correctness on the running ranks, at the model's widths with 2 layers and seq 512: every rank takes
     one sequence, gradients are averaged by the engine's NCCL exchange; rank 0 also runs the engine without NCCL on the
@@ -562,7 +593,6 @@ def run_b200(args):
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
-    ctx.profile_gemm(True)
     launches0 = ctx.launch_count()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
@@ -573,6 +603,17 @@ def run_b200(args):
     barrier()
     ms = e0.elapsed_time(e1)
     launches = ctx.launch_count() - launches0
+    # The same K steps once more, now with a CUDA event pair around every tensor-core GEMM launch (the roofline's kernel
+    # time).  The events sit between kernels and keep a kernel's set-up from overlapping its predecessor's tail, so the
+    # headline region above runs without them; the clock sampler covers both regions.
+    ctx.profile_gemm(True)
+    p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    p0.record(stream)
+    for _ in range(args.steps):
+        step_dev()
+    p1.record(stream)
+    barrier()
+    ms_profiled = p0.elapsed_time(p1)
     gemm_ms, gemm_flops, gemm_n = ctx.profile_gemm_read()
     ctx.profile_gemm(False)
     loss_dev = float(model._loss.download()[0])
@@ -621,7 +662,9 @@ def run_b200(args):
             "roofline": {"kernel": "gemm_tc2_kernel / gemm_tc_kernel (tcgen05 bf16 GEMM: all projection and vocab GEMMs, fwd + dgrad + wgrad)",
                          "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
                          "frac": (achieved / peak) if achieved else None, "peak_source": peak_src,
-                         "launches_timed": gemm_n, "share_of_step_time": gemm_ms / ms if ms > 0 else None,
+                         "launches_timed": gemm_n, "share_of_step_time": gemm_ms / ms_profiled if ms_profiled > 0 else None,
+                         "timed_in": f"a second pass of the same {args.steps} steps with an event pair around every GEMM launch "
+                                     f"({ms_profiled / args.steps:.2f} ms per step with the events, {ms / args.steps:.2f} without)",
                          "traffic": GEMM_DRAM_BYTES_PER_LAUNCH, "traffic_source": GEMM_TRAFFIC_SOURCE,
                          "algorithmic_bytes_per_launch": GEMM_ALGO_BYTES_PER_LAUNCH},
             "e2e": {"value": tokens_total / e2e_s, "unit": UNIT, "h2d_bytes_per_step": int(2 * B * S * 4),
@@ -657,7 +700,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-decode", action="store_true", help="skip the decode workload appended to the 1-GPU line")
     ap.add_argument("--no-ops", action="store_true", help="skip the attention / per-op figures appended to the 1-GPU line")
-    ap.add_argument("--workload", default="train", choices=["train", "decode", "ops"])
+    ap.add_argument("--workload", default="train", choices=["train", "decode", "ops", "trace"])
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
@@ -665,6 +708,8 @@ def main():
         run_decode(args)
     elif args.workload == "ops":
         run_ops(args)
+    elif args.workload == "trace":
+        run_trace(args)
     else:
         run_b200(args)
 

@@ -255,6 +255,13 @@ int b200_model_loss_and_grads(b200_model *m, const int32_t *dev_tokens, const in
 /* AdamWOptimizer::step over every registered parameter (cpp/src/Optimizer.cpp:139-149);
  * norm weights are not trained (cpp/src/Trainer.cpp:195-205). */
 int b200_model_adamw_step(b200_model *m, float lr, float beta1, float beta2, float eps, float weight_decay);
+/* Global-norm gradient clipping for the optimizer step (the reference's MLX trainer: grad_clip_norm,
+ * python/apple-silicon/src/pre-training/train.py:858-867; its C++ trainer has none): when the L2 norm of all trainable
+ * gradients exceeds max_norm they are scaled by max_norm / (norm + 1e-6) inside the AdamW kernel.  0 (default) = off.
+ * Data-parallel steps with clipping all-reduce the gradients first (the sharded optimizer would update buckets before
+ * the norm is known).  _last_grad_norm returns the norm and factor of the last clipped step (host; synchronises). */
+int b200_model_set_grad_clip(b200_model *m, float max_norm);
+int b200_model_last_grad_norm(b200_model *m, float *norm, float *factor);
 /* One whole training step from HOST buffers: copies tokens/targets in, runs
  * forward, loss, backward, (gradient all-reduce when data-parallel), AdamW,
  * copies the loss out and synchronises. (Trainer::train step body, cpp/src/Trainer.cpp:263-378) */

@@ -126,6 +126,8 @@ _SIGS = {
     "b200_model_forward": (_i, [_vp, _vp, _sz, _sz, _vp]),
     "b200_model_loss_and_grads": (_i, [_vp, _vp, _vp, _sz, _sz, _vp]),
     "b200_model_adamw_step": (_i, [_vp, _f, _f, _f, _f, _f]),
+    "b200_model_set_grad_clip": (_i, [_vp, _f]),
+    "b200_model_last_grad_norm": (_i, [_vp, C.POINTER(_f), C.POINTER(_f)]),
     "b200_model_train_step_host": (_i, [_vp, _vp, _vp, _sz, _sz, _f, _f, _f, _f, _f, C.POINTER(_f)]),
     "b200_model_train_step": (_i, [_vp, _vp, _vp, _sz, _sz, _f, _f, _f, _f, _f, _vp]),
     "b200_model_layer_forward": (_i, [_vp, _sz, _vp, _vp, _sz, _sz]),
@@ -548,6 +550,16 @@ class Model:
 
     def adamw_step(self, lr, beta1=0.9, beta2=0.95, eps=1e-8, wd=0.1):
         self.ctx._check(self.ctx.lib.b200_model_adamw_step(self.h, lr, beta1, beta2, eps, wd))
+
+    def set_grad_clip(self, max_norm: float):
+        """Global-norm gradient clipping of the optimizer step (0 turns it off)."""
+        self.ctx._check(self.ctx.lib.b200_model_set_grad_clip(self.h, max_norm))
+
+    def last_grad_norm(self):
+        """(gradient norm, factor applied) of the last clipped optimizer step."""
+        n, f = _f(0.0), _f(1.0)
+        self.ctx._check(self.ctx.lib.b200_model_last_grad_norm(self.h, C.byref(n), C.byref(f)))
+        return float(n.value), float(f.value)
 
     def train_step(self, tokens_dev, targets_dev, B, S, lr=3e-4, beta1=0.9, beta2=0.95, eps=1e-8, wd=0.1):
         self.ctx._check(self.ctx.lib.b200_model_train_step(self.h, tokens_dev.ptr, targets_dev.ptr, B, S, lr, beta1,

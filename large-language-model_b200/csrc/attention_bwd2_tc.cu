@@ -99,6 +99,7 @@ attn_bwd2_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     if (threadIdx.x == 0) atomicCAS(status, 0, 297);
     return;
   }
+  pdl_launch_dependents();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_sub = (S + SQ - 1) / SQ;
   const int j = blockIdx.y, kvh = blockIdx.x % nKV, b = blockIdx.x / nKV;
@@ -121,6 +122,7 @@ attn_bwd2_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   tc::tc_fence_before();
   __syncthreads();
   tc::tc_fence_after();
+  pdl_wait();                          // set-up above may overlap the previous kernel's tail; operands are touched from here on
   const uint32_t tmem_base = sh->tmem_base;
   const uint32_t t_dv = tmem_base + 256, t_dk = tmem_base + 384;
   auto step_head = [&](int st) { return kvh * G + st / per_head; };
@@ -393,9 +395,8 @@ int attn_bwd2_tc_run(b200_ctx *ctx, const void *Q, const void *K, const void *V,
   static bool attr = false;
   if (!attr) { B200_CUDA(ctx, cudaFuncSetAttribute(attn_bwd2_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)); attr = true; }
   dim3 grid((unsigned)(nKV * B), (unsigned)((S + TK - 1) / TK), 1);
-  attn_bwd2_tc_kernel<<<grid, BWD2_THREADS, smem, ctx->stream>>>(mq, mk, mv, mdo, dQacc, lse2, Dsum, (bf16 *)dK, (bf16 *)dV, (int)nH, (int)nKV, (int)S,
-                                                          gst.k_b, gst.k_h, gst.k_s, gst.v_b, gst.v_h, gst.v_s, 1.0f / sqrtf((float)HD),
-                                                          ctx->dev_status, rope_cos, rope_sin);
+  B200_CUDA(ctx, launch_k(ctx, attn_bwd2_tc_kernel, grid, dim3(BWD2_THREADS), (size_t)smem, 0, mq, mk, mv, mdo, dQacc, lse2, Dsum, (bf16 *)dK, (bf16 *)dV, (int)nH,
+                          (int)nKV, (int)S, gst.k_b, gst.k_h, gst.k_s, gst.v_b, gst.v_h, gst.v_s, 1.0f / sqrtf((float)HD), ctx->dev_status, rope_cos, rope_sin));
   B200_LAUNCHED(ctx);
   return B200_OK;
 }

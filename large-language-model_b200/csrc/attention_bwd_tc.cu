@@ -263,6 +263,8 @@ __global__ void __launch_bounds__(256)
 attn_dsum_kernel(const bf16 *__restrict__ O, const bf16 *__restrict__ dO, float *__restrict__ D, int B, int nH, int S,
                  long long o_b, long long o_h, long long o_s, const float *__restrict__ lse, float *__restrict__ lse2,
                  float *__restrict__ zero_acc) {
+  pdl_launch_dependents();
+  pdl_wait();
   constexpr int VEC = HD / 8;                       // elements per lane: 16 (32 bytes) or 8 (16 bytes)
   typedef typename std::conditional<VEC == 16, uint4, uint2>::type Raw;   // loaded in 16- or 8-byte pieces
   constexpr int PIECES = VEC * 2 / (int)sizeof(Raw);
@@ -318,6 +320,8 @@ attn_dsum_kernel(const bf16 *__restrict__ O, const bf16 *__restrict__ dO, float 
 __global__ void attn_dq_store_kernel(const float *__restrict__ acc, bf16 *__restrict__ dQ, int B, int nH, int S,
                                      int hd, long long q_b, long long q_h, long long q_s,
                                      const float *__restrict__ rope_cos, const float *__restrict__ rope_sin, float mul) {
+  pdl_launch_dependents();
+  pdl_wait();
   const size_t total = (size_t)B * nH * S * (hd / 8);
   for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
     const int u = (int)(idx % (hd / 8)); size_t r = idx / (hd / 8);
@@ -359,8 +363,8 @@ int bwd_launch_t(b200_ctx *ctx, const void *Q, const void *K, const void *V, con
   const bool second_form = HD == 128 && ctx->attn_bwd2 && attn_bwd2_supported(S, HD);
   {
     size_t blocks = (rows + 63) / 64, cap = (size_t)ctx->sm_count * 16;      // 32 lane groups x 2 rows per block pass
-    attn_dsum_kernel<HD><<<(int)(blocks < cap ? blocks : cap), 256, 0, ctx->stream>>>((const bf16 *)O, (const bf16 *)dO, Dsum, (int)B, (int)nH, (int)S,
-                                                                                      st.o_b, st.o_h, st.o_s, lse, second_form ? lse2 : nullptr, dQacc);
+    B200_CUDA(ctx, launch_k(ctx, attn_dsum_kernel<HD>, dim3((unsigned)(blocks < cap ? blocks : cap)), dim3(256), 0, 0, (const bf16 *)O, (const bf16 *)dO, Dsum,
+                            (int)B, (int)nH, (int)S, st.o_b, st.o_h, st.o_s, lse, second_form ? lse2 : (float *)nullptr, dQacc));
     B200_LAUNCHED(ctx);
   }
   if (second_form) {
@@ -383,8 +387,8 @@ int bwd_launch_t(b200_ctx *ctx, const void *Q, const void *K, const void *V, con
   }
   {
     size_t items = rows * (HD / 8), blocks = (items + 255) / 256, cap = (size_t)ctx->sm_count * 16;
-    attn_dq_store_kernel<<<(int)(blocks < cap ? blocks : cap), 256, 0, ctx->stream>>>(dQacc, (bf16 *)dQ, (int)B, (int)nH, (int)S, HD, gst.q_b, gst.q_h, gst.q_s, rope_cos, rope_sin,
-                                                                                      second_form ? 1.0f / sqrtf((float)HD) : 1.0f);
+    B200_CUDA(ctx, launch_k(ctx, attn_dq_store_kernel, dim3((unsigned)(blocks < cap ? blocks : cap)), dim3(256), 0, 0, (const float *)dQacc, (bf16 *)dQ, (int)B, (int)nH,
+                            (int)S, (int)HD, gst.q_b, gst.q_h, gst.q_s, rope_cos, rope_sin, second_form ? 1.0f / sqrtf((float)HD) : 1.0f));
     B200_LAUNCHED(ctx);
   }
   return B200_OK;

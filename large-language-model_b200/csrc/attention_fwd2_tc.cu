@@ -47,6 +47,7 @@ __global__ void __launch_bounds__(FWD2_THREADS, 1)
 attn_fwd2_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                     const __grid_constant__ CUtensorMap map_v, bf16 *__restrict__ O, float *__restrict__ lse,
                     int nH, int nKV, int S, long long o_b, long long o_h, long long o_s, float scale, int *status) {
+  pdl_launch_dependents();
   constexpr int TILE_BYTES = 128 * HD * 2;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t *smem = smem_raw;
@@ -80,6 +81,7 @@ attn_fwd2_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   tc::tc_fence_before();
   __syncthreads();
   tc::tc_fence_after();
+  pdl_wait();                          // set-up above may overlap the previous kernel's tail; operands are touched from here on
   const uint32_t tmem_base = sh->tmem_base;
 
   if (warp >= 8) {
@@ -271,8 +273,8 @@ int fwd2_launch_t(b200_ctx *ctx, const void *Q, const void *K, const void *V, vo
   if (!attr) { B200_CUDA(ctx, cudaFuncSetAttribute(attn_fwd2_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)); attr = true; }
   const size_t n_qt = (S + TQ - 1) / TQ;
   dim3 grid((unsigned)(nH * B), (unsigned)((n_qt + 1) / 2), 1);
-  attn_fwd2_tc_kernel<HD><<<grid, FWD2_THREADS, smem, ctx->stream>>>(mq, mk, mv, (bf16 *)O, lse, (int)nH, (int)nKV, (int)S, st.o_b, st.o_h,
-                                                               st.o_s, 1.0f / sqrtf((float)HD), ctx->dev_status);
+  B200_CUDA(ctx, launch_k(ctx, attn_fwd2_tc_kernel<HD>, grid, dim3(FWD2_THREADS), (size_t)smem, 0, mq, mk, mv, (bf16 *)O, lse, (int)nH, (int)nKV, (int)S, st.o_b,
+                          st.o_h, st.o_s, 1.0f / sqrtf((float)HD), ctx->dev_status));
   B200_LAUNCHED(ctx);
   return B200_OK;
 }

@@ -78,6 +78,11 @@ extern "C" int b200_init(int device, b200_ctx **out) {
   if (const char *e = getenv("B200_ATTN_FWD2")) ctx->attn_fwd2 = e[0] != '0';     // A/B switch for measurements
   if (const char *e = getenv("B200_ATTN_BWD2")) ctx->attn_bwd2 = e[0] != '0';
   if (const char *e = getenv("B200_DECODE_ATTN_TC")) ctx->attn_decode_tc = e[0] != '0';
+  // B200_PDL=1: programmatic dependent launch for every kernel that supports it (each waits before its first dependent
+  // access), so that a kernel's launch and set-up overlap the tail of the one before.  The decode step always uses it
+  // (it is a chain of microsecond kernels); for training steps it measured no gain on a power-capped B200
+  // (152.5 vs 152.7 ms per step, same GPU), so plain stream order is the default there.
+  ctx->pdl = getenv("B200_PDL") && getenv("B200_PDL")[0] == '1';
   cudaMemsetAsync(ctx->dev_status, 0, sizeof(int), ctx->stream);
   cudaStreamSynchronize(ctx->stream);
   *out = ctx;

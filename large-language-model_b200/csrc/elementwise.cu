@@ -435,6 +435,8 @@ __global__ void swiglu_bwd_kernel(const T *__restrict__ dy, const T *__restrict_
                                   T *__restrict__ dgate, T *__restrict__ dup, size_t rows, size_t cols, size_t ld_dy,
                                   size_t ld_in, size_t ld_out) {
   constexpr int N = Vec16<T>::N;
+  pdl_launch_dependents();
+  pdl_wait();
   size_t vec_per_row = cols / N, total = rows * vec_per_row;
   for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
     size_t r = idx / vec_per_row, c = (idx % vec_per_row) * N;
@@ -496,8 +498,8 @@ int swiglu_bwd_strided(b200_ctx *ctx, const void *dy, const void *gate, const vo
              (((uintptr_t)gate | (uintptr_t)up | (uintptr_t)dy | (uintptr_t)dgate | (uintptr_t)dup) % 16 == 0);
   if (vec) {
     int grid = ew_grid(ctx, rows * cols / N);
-    if (dt == B200_BF16) swiglu_bwd_kernel<bf16><<<grid, 256, 0, ctx->stream>>>((const bf16 *)dy, (const bf16 *)gate, (const bf16 *)up, (bf16 *)dgate, (bf16 *)dup, rows, cols, ld_dy, ld_in, ld_out);
-    else swiglu_bwd_kernel<float><<<grid, 256, 0, ctx->stream>>>((const float *)dy, (const float *)gate, (const float *)up, (float *)dgate, (float *)dup, rows, cols, ld_dy, ld_in, ld_out);
+    if (dt == B200_BF16) launch_k(ctx, swiglu_bwd_kernel<bf16>, dim3(grid), dim3(256), 0, 0, (const bf16 *)dy, (const bf16 *)gate, (const bf16 *)up, (bf16 *)dgate, (bf16 *)dup, rows, cols, ld_dy, ld_in, ld_out);
+    else launch_k(ctx, swiglu_bwd_kernel<float>, dim3(grid), dim3(256), 0, 0, (const float *)dy, (const float *)gate, (const float *)up, (float *)dgate, (float *)dup, rows, cols, ld_dy, ld_in, ld_out);
   } else {
     B200_REQUIRE(ctx, ld_in == cols && ld_out == cols && ld_dy == cols, "swiglu: unaligned strided form unsupported");
     int grid = ew_grid(ctx, rows * cols);
@@ -731,9 +733,14 @@ __device__ __forceinline__ float4 load4(const bf16 *g, size_t i) {
   return make_float4(a.x, a.y, b.x, b.y);
 }
 // G: element type of the gradient (fp32, or bf16 when the data-parallel exchange ran in bf16)
+// gscale (optional, device): every gradient is multiplied by *gscale first (global-norm clipping).
 template <class G>
 __global__ void adamw_kernel(float *__restrict__ p, const G *__restrict__ g, float *__restrict__ m,
-                             float *__restrict__ v, bf16 *__restrict__ shadow, size_t n, b200_adamw_params a) {
+                             float *__restrict__ v, bf16 *__restrict__ shadow, size_t n, b200_adamw_params a,
+                             const float *__restrict__ gscale) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const float gs = gscale ? *gscale : 1.0f;
   size_t nv = n / 4;
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < nv; i += (size_t)gridDim.x * blockDim.x) {
     float4 pp = reinterpret_cast<float4 *>(p)[i], gg = load4(g, i);
@@ -741,6 +748,7 @@ __global__ void adamw_kernel(float *__restrict__ p, const G *__restrict__ g, flo
     float *pf = &pp.x, *gf = &gg.x, *mf = &mm.x, *vf = &vv.x;
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
+      gf[j] *= gs;
       mf[j] = a.beta1 * mf[j] + (1.0f - a.beta1) * gf[j];
       vf[j] = a.beta2 * vf[j] + (1.0f - a.beta2) * gf[j] * gf[j];
       float x = pf[j];
@@ -758,7 +766,7 @@ __global__ void adamw_kernel(float *__restrict__ p, const G *__restrict__ g, flo
     }
   }
   for (size_t i = nv * 4 + (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
-    float gi = to_f(g[i]);
+    float gi = to_f(g[i]) * gs;
     float mi = a.beta1 * m[i] + (1.0f - a.beta1) * gi, vi = a.beta2 * v[i] + (1.0f - a.beta2) * gi * gi;
     float x = p[i];
     if (a.weight_decay > 0.0f) x = x - a.lr * a.weight_decay * x;
@@ -773,7 +781,54 @@ extern "C" int b200_adamw_step(b200_ctx *ctx, float *p, const float *g, float *m
   B200_REQUIRE(ctx, (((uintptr_t)p | (uintptr_t)g | (uintptr_t)m | (uintptr_t)v) % 16 == 0) && ((uintptr_t)shadow % 8 == 0),
                "adamw_step: arrays must be 16-byte aligned");
   if (!n) return B200_OK;
-  adamw_kernel<float><<<ew_grid(ctx, n / 4 + 1), 256, 0, ctx->stream>>>(p, g, m, v, (bf16 *)shadow, n, *a);
+  launch_k(ctx, adamw_kernel<float>, dim3(ew_grid(ctx, n / 4 + 1)), dim3(256), 0, 0, p, g, m, v, (bf16 *)shadow, n, *a, (const float *)nullptr);
+  B200_LAUNCHED(ctx);
+  return B200_OK;
+}
+// AdamW with every gradient multiplied by the device scalar *gscale (the clip factor of clip_scale_launch).
+int adamw_step_scaled(b200_ctx *ctx, float *p, const float *g, float *m, float *v, void *shadow, size_t n,
+                      const b200_adamw_params *a, const float *gscale) {
+  B200_REQUIRE(ctx, p && g && m && v && a && gscale, "adamw_step: null pointer");
+  B200_REQUIRE(ctx, (((uintptr_t)p | (uintptr_t)g | (uintptr_t)m | (uintptr_t)v) % 16 == 0) && ((uintptr_t)shadow % 8 == 0),
+               "adamw_step: arrays must be 16-byte aligned");
+  if (!n) return B200_OK;
+  launch_k(ctx, adamw_kernel<float>, dim3(ew_grid(ctx, n / 4 + 1)), dim3(256), 0, 0, p, g, m, v, (bf16 *)shadow, n, *a, gscale);
+  B200_LAUNCHED(ctx);
+  return B200_OK;
+}
+// Global gradient norm and clip factor (python/apple-silicon/src/pre-training/train.py:858-867 of the reference's MLX
+// trainer): out[0] = ||g||_2 over n floats, out[1] = norm > max_norm ? max_norm / (norm + 1e-6) : 1.  Fixed summation
+// order (1024 partial sums in fp64, then one thread), so replicas holding the same gradients get the same factor.
+namespace {
+__global__ void __launch_bounds__(256) sumsq_partial_kernel(const float *__restrict__ g, size_t n, double *__restrict__ part) {
+  __shared__ double sh[256];
+  double a = 0.0;
+  const size_t nv = n / 4;
+  for (size_t i = (size_t)blockIdx.x * 256 + threadIdx.x; i < nv; i += (size_t)gridDim.x * 256) {
+    const float4 x = reinterpret_cast<const float4 *>(g)[i];
+    a += (double)x.x * x.x + (double)x.y * x.y + (double)x.z * x.z + (double)x.w * x.w;
+  }
+  if (blockIdx.x == 0) for (size_t i = nv * 4 + threadIdx.x; i < n; i += 256) a += (double)g[i] * g[i];
+  sh[threadIdx.x] = a;
+  __syncthreads();
+  for (int o = 128; o > 0; o >>= 1) { if ((int)threadIdx.x < o) sh[threadIdx.x] += sh[threadIdx.x + o]; __syncthreads(); }
+  if (threadIdx.x == 0) part[blockIdx.x] = sh[0];
+}
+__global__ void clip_scale_kernel(const double *__restrict__ part, int blocks, float max_norm, float *__restrict__ out) {
+  if (threadIdx.x == 0 && blockIdx.x == 0) {
+    double a = 0.0;
+    for (int i = 0; i < blocks; ++i) a += part[i];
+    const float norm = (float)sqrt(a);
+    out[0] = norm;
+    out[1] = norm > max_norm ? max_norm / (norm + 1e-6f) : 1.0f;
+  }
+}
+}  // namespace
+int clip_scale_launch(b200_ctx *ctx, const float *g, size_t n, float max_norm, double *part1024, float *out2) {
+  B200_REQUIRE(ctx, g && part1024 && out2 && (uintptr_t)g % 16 == 0, "clip_scale: bad arguments");
+  sumsq_partial_kernel<<<1024, 256, 0, ctx->stream>>>(g, n, part1024);
+  B200_LAUNCHED(ctx);
+  clip_scale_kernel<<<1, 32, 0, ctx->stream>>>(part1024, 1024, max_norm, out2);
   B200_LAUNCHED(ctx);
   return B200_OK;
 }
@@ -784,7 +839,7 @@ int adamw_step_bf16_grad(b200_ctx *ctx, float *p, const void *g_bf16, float *m, 
   B200_REQUIRE(ctx, (((uintptr_t)p | (uintptr_t)m | (uintptr_t)v) % 16 == 0) && ((uintptr_t)shadow % 8 == 0) && ((uintptr_t)g_bf16 % 8 == 0),
                "adamw_step: arrays must be 16-byte aligned (bf16 arrays 8-byte)");
   if (!n) return B200_OK;
-  adamw_kernel<bf16><<<ew_grid(ctx, n / 4 + 1), 256, 0, ctx->stream>>>(p, (const bf16 *)g_bf16, m, v, (bf16 *)shadow, n, *a);
+  launch_k(ctx, adamw_kernel<bf16>, dim3(ew_grid(ctx, n / 4 + 1)), dim3(256), 0, 0, p, (const bf16 *)g_bf16, m, v, (bf16 *)shadow, n, *a, (const float *)nullptr);
   B200_LAUNCHED(ctx);
   return B200_OK;
 }

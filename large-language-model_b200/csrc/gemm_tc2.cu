@@ -256,6 +256,7 @@ template <bool A_MN, bool B_MN, class TO, bool ACC>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                 TO *__restrict__ C, int M, int N, int K, size_t ldc, int *status, GemmEpilogue epi, int splits) {
+  pdl_launch_dependents();             // the next kernel of the stream may be scheduled onto SMs as this grid leaves them
   extern __shared__ uint8_t smem_raw[];
   uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t *sA = smem, *sB = smem + STAGES * A_STAGE_BYTES;
@@ -288,6 +289,9 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   cluster_sync();                      // the peer's barriers are initialised before anything arrives on them
   tc::tc_fence_after();
   const uint32_t tmem_base = sh->tmem_base;
+  // Everything above (barriers, tensor-memory allocation, descriptor prefetch) touched nothing another kernel owns and may
+  // have overlapped the tail of the kernel before; from here on operands are read and results written.
+  pdl_wait();
 
   auto tile_coords = [&](int t, int &tm, int &tn) {
     int per_group = GROUP_M * tiles_n;
@@ -457,10 +461,12 @@ int launch_variant(b200_ctx *ctx, const CUtensorMap &ma, const CUtensorMap &mb, 
   static bool attr_set = false;
   static int max_clusters = 0;
   cudaLaunchConfig_t cfg = {};
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
-  cfg.blockDim = dim3(THREADS); cfg.dynamicSmemBytes = SMEM_BYTES; cfg.stream = ctx->stream; cfg.attrs = attr; cfg.numAttrs = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.blockDim = dim3(THREADS); cfg.dynamicSmemBytes = SMEM_BYTES; cfg.stream = ctx->stream; cfg.attrs = attr; cfg.numAttrs = ctx->pdl ? 2 : 1;
   if (!attr_set) {
     B200_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
     cfg.gridDim = dim3(ctx->sm_count & ~1);

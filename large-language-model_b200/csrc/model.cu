@@ -31,6 +31,9 @@ int norm_norm_backward_fused(b200_ctx *ctx, const void *g, const void *h, const 
                              size_t rows, size_t D, float eps, b200_dtype dt);
 int adamw_step_bf16_grad(b200_ctx *ctx, float *p, const void *g_bf16, float *m, float *v, void *shadow, size_t n,
                          const b200_adamw_params *a);
+int adamw_step_scaled(b200_ctx *ctx, float *p, const float *g, float *m, float *v, void *shadow, size_t n,
+                      const b200_adamw_params *a, const float *gscale);
+int clip_scale_launch(b200_ctx *ctx, const float *g, size_t n, float max_norm, double *part1024, float *out2);
 bool vocab_ce_is_fused(const void *x, const void *w, size_t tokens, size_t V, size_t H, b200_dtype dt);
 int vocab_ce_dlogits(b200_ctx *ctx, const void *x, const void *w, const uint32_t *targets, const float *lse, void *dlogits,
                      int in_place, size_t tokens, size_t V, size_t H, b200_dtype dt);
@@ -108,6 +111,9 @@ struct b200_model {
        *fh = nullptr;
   int32_t *d_tokens = nullptr, *d_targets = nullptr;
   float *d_loss = nullptr;
+  float grad_clip = 0.f;          // > 0: gradients are scaled so that their global L2 norm does not exceed it
+  double *clip_part = nullptr;    // 1024 partial sums of squares
+  float *clip_out = nullptr;      // [0] gradient norm of the last clipped step, [1] the factor applied
   float *ce_lse = nullptr;        // [M] log-sum-exp of every token's logits, kept from the loss for its gradient
   // 1: the loss GEMM stores no logits and the gradient of the logits comes from a second run of the projection;
   // 0: the loss GEMM also stores bf16 logits and one in-place pass turns them into their gradient
@@ -218,6 +224,7 @@ extern "C" int b200_model_create(b200_ctx *ctx, const b200_model_config *cfg, b2
   A(&m->fh, M * H * es);
   A((void **)&m->d_tokens, M * 4); A((void **)&m->d_targets, M * 4); A((void **)&m->d_loss, 4);
   A((void **)&m->ce_lse, M * 4);
+  A((void **)&m->clip_part, 1024 * sizeof(double)); A((void **)&m->clip_out, 2 * sizeof(float));
   if (const char *e = getenv("B200_VOCAB_CE")) m->vocab_ce_recompute = (e[0] == 'r' || e[0] == '1');   // "recompute" | "store"
   if (rc == B200_OK && (cudaMallocHost(&m->pin_tokens, M * 4) != cudaSuccess || cudaMallocHost(&m->pin_targets, M * 4) != cudaSuccess ||
                         cudaMallocHost(&m->pin_loss, 4) != cudaSuccess))
@@ -566,7 +573,8 @@ static int allreduce_async(b200_model *m, float *buf, size_t n) {
 static bool dp_shardable(const b200_model *m) {
   // every bucket splits into `world` slices whose offsets keep the 16-byte alignment AdamW and the vector loads want
   const size_t q = (size_t)m->world * 8;
-  return m->world > 1 && m->comm && m->dp_sharded && m->with_opt && m->master && nccl::api().ReduceScatter && nccl::api().AllGather &&
+  // (global-norm clipping needs every bucket's gradients before the first update: it runs the all-reduce route)
+  return m->world > 1 && m->comm && m->dp_sharded && m->grad_clip <= 0.f && m->with_opt && m->master && nccl::api().ReduceScatter && nccl::api().AllGather &&
          (m->V * m->H) % q == 0 && m->layer_train % q == 0;
 }
 // Sharded-optimizer exchange of bucket [off, off+n): everything below runs on the side stream, after the work enqueued so
@@ -709,7 +717,29 @@ extern "C" int b200_model_adamw_step(b200_model *m, float lr, float beta1, float
   p.bias_correction1 = 1.0f - powf(beta1, (float)m->step_count);   // cpp/src/Optimizer.cpp:141-142
   p.bias_correction2 = 1.0f - powf(beta2, (float)m->step_count);
   void *shadow = ((void *)m->master != m->params) ? m->params : nullptr;
+  if (m->grad_clip > 0.f) {
+    TRY(clip_scale_launch(m->ctx, m->grads, m->n_train, m->grad_clip, m->clip_part, m->clip_out));
+    return adamw_step_scaled(m->ctx, m->master, m->grads, m->adam_m, m->adam_v, shadow, m->n_train, &p, m->clip_out + 1);
+  }
   return b200_adamw_step(m->ctx, m->master, m->grads, m->adam_m, m->adam_v, shadow, m->n_train, &p);
+}
+// Optional global-norm gradient clipping of the optimizer step (the MLX trainer's grad_clip_norm,
+// python/apple-silicon/src/pre-training/train.py:858-867; the C++ trainer has none): 0 turns it off.
+extern "C" int b200_model_set_grad_clip(b200_model *m, float max_norm) {
+  if (!m) return B200_ERR_INVALID;
+  B200_REQUIRE(m->ctx, max_norm >= 0.f, "set_grad_clip: the norm bound must not be negative");
+  m->grad_clip = max_norm;
+  return B200_OK;
+}
+// Norm of the gradients and the factor applied in the last clipped optimizer step (host outputs; synchronises).
+extern "C" int b200_model_last_grad_norm(b200_model *m, float *norm, float *factor) {
+  if (!m) return B200_ERR_INVALID;
+  B200_REQUIRE(m->ctx, norm && factor, "last_grad_norm: null pointer");
+  float h[2] = {0.f, 1.f};
+  TRY(b200_memcpy_d2h(m->ctx, h, m->clip_out, sizeof(h)));
+  TRY(b200_sync(m->ctx));
+  *norm = h[0]; *factor = h[1];
+  return B200_OK;
 }
 
 extern "C" int b200_model_train_step(b200_model *m, const int32_t *tok, const int32_t *tgt, size_t B, size_t S,
@@ -720,7 +750,7 @@ extern "C" int b200_model_train_step(b200_model *m, const int32_t *tok, const in
   // 16-byte alignment the AdamW kernel wants.
   // Data parallel: the optimizer is sharded over the ranks and runs bucket by bucket behind the gradient exchange.
   const char *env = getenv("B200_FUSED_OPT");
-  const bool fuse = ((env && env[0] == '1') || dp_shardable(m)) && m->with_opt && m->master && m->opt_stream && (m->V * m->H) % 4 == 0 && m->layer_train % 4 == 0;
+  const bool fuse = (((env && env[0] == '1') && m->grad_clip <= 0.f) || dp_shardable(m)) && m->with_opt && m->master && m->opt_stream && (m->V * m->H) % 4 == 0 && m->layer_train % 4 == 0;
   if (!fuse) {
     TRY(gather_sharded_state(m));
     TRY(b200_model_loss_and_grads(m, tok, tgt, B, S, dev_loss));

@@ -165,6 +165,8 @@ rms_bwd_warp_kernel(const T *__restrict__ g, const T *__restrict__ x, const T *_
                     const T *__restrict__ res_grad, T *__restrict__ dx, float *__restrict__ dw, float eps,
                     size_t rows, int D) {
   constexpr int N = Vec16<T>::N;
+  pdl_launch_dependents();
+  pdl_wait();
   const int lane = threadIdx.x & 31;
   const size_t warp_global = (size_t)blockIdx.x * WARPS_PER_CTA + (threadIdx.x >> 5);
   const size_t n_warps = (size_t)gridDim.x * WARPS_PER_CTA;
@@ -241,6 +243,8 @@ rms_bwd2_warp_kernel(const T *__restrict__ g, const T *__restrict__ h, const T *
                      const T *__restrict__ res_grad, T *__restrict__ dx, float eps, size_t rows, int D) {
   constexpr int N = Vec16<T>::N, ROWS_PER_CTA = WARPS_PER_CTA / WPR;
   __shared__ float part[4][ROWS_PER_CTA][WPR];
+  pdl_launch_dependents();
+  pdl_wait();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, slot = warp / WPR, sub = warp % WPR;
   const float inv_d = 1.0f / (float)D;
   auto row_sum = [&](float v, int which) -> float {
@@ -366,7 +370,7 @@ int rms_bwd_warp(b200_ctx *ctx, const void *g, const void *x, const void *w, con
   if (D % (32 * N) || !aligned16({g, x, w, rg, dx})) return 0;
   const int vpl = (int)(D / (32 * N));
   const int grid = warp_grid(ctx, rows);
-#define BW(V, A, W_) rms_bwd_warp_kernel<T, V, A, W_><<<grid, WARPS_PER_CTA * 32, 0, ctx->stream>>>((const T *)g, (const T *)x, (const T *)w, (const T *)rg, (T *)dx, dw, eps, rows, (int)D)
+#define BW(V, A, W_) launch_k(ctx, rms_bwd_warp_kernel<T, V, A, W_>, dim3(grid), dim3(WARPS_PER_CTA * 32), 0, 0, (const T *)g, (const T *)x, (const T *)w, (const T *)rg, (T *)dx, dw, eps, rows, (int)D)
 #define BWV(V) do { if (add) { if (dw) BW(V, true, true); else BW(V, true, false); } else { if (dw) BW(V, false, true); else BW(V, false, false); } } while (0)
   switch (vpl) {
     case 1: BWV(1); break;
@@ -391,7 +395,7 @@ int rms_bwd2_warp(b200_ctx *ctx, const void *g, const void *h, const void *w, co
   const int vecs = (int)(D / (32 * N));               // 16-byte vectors per lane if one warp took the row
 #define B2(V, W_) do { const size_t per = WARPS_PER_CTA / W_; size_t blocks = (rows + per - 1) / per; const size_t cap = (size_t)ctx->sm_count * 4; \
     if (blocks > cap) blocks = cap; if (!blocks) blocks = 1; \
-    rms_bwd2_warp_kernel<T, V, W_><<<(unsigned)blocks, WARPS_PER_CTA * 32, 0, ctx->stream>>>((const T *)g, (const T *)h, (const T *)w, (const T *)rg, (T *)dx, eps, rows, (int)D); } while (0)
+    launch_k(ctx, rms_bwd2_warp_kernel<T, V, W_>, dim3((unsigned)blocks), dim3(WARPS_PER_CTA * 32), 0, 0, (const T *)g, (const T *)h, (const T *)w, (const T *)rg, (T *)dx, eps, rows, (int)D); } while (0)
   switch (vecs) {
     case 1: B2(1, 1); break;
     case 2: B2(2, 1); break;

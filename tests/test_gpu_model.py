@@ -174,6 +174,29 @@ def test_adamw_training_steps_match_the_checker_and_reduce_the_loss(ctx, orc):
     model.close()
 
 
+def test_global_norm_gradient_clipping_of_the_optimizer_step(ctx, orc):
+    """python/apple-silicon/src/pre-training/train.py:858-867: norm over all gradients; scale max/(norm + 1e-6) when it
+    exceeds the bound.  The step with clipping equals the checker's AdamW on the scaled gradients; a bound above the
+    norm changes nothing."""
+    cfg = oracle.Config(B=2, S=16, H=64, I=96, nH=4, nKV=2, hd=16, V=96, L=2)
+    params, tok, tgt = inputs(cfg, seed=4)
+    mask = trainable_mask(cfg)
+    _, g_ref, _ = orc.model_loss_and_grads(cfg, tok, tgt, params)
+    norm_ref = float(np.sqrt(np.sum(g_ref[mask].astype(np.float64) ** 2)))
+    for bound in (0.25 * norm_ref, 4.0 * norm_ref):
+        model = bridge.Model(ctx, cfg, "f32")
+        model.load_params(params)
+        model.set_grad_clip(bound)
+        model.train_step_host(tok, tgt, lr=1e-2, beta1=0.9, beta2=0.95, eps=1e-8, wd=0.1)
+        norm, factor = model.last_grad_norm()
+        exp_factor = bound / (norm_ref + 1e-6) if norm_ref > bound else 1.0
+        assert abs(norm - norm_ref) < 1e-4 * norm_ref and abs(factor - exp_factor) < 1e-5
+        pn, _, _ = orc.adamw_step(params, g_ref * np.float32(exp_factor), np.zeros_like(params), np.zeros_like(params), 1e-2, 0.9, 0.95, 1e-8, 0.1, 1)
+        expect = np.where(mask, pn, params)
+        assert rel(model.read_params(), expect) < 1e-5
+        model.close()
+
+
 def test_shape_errors_are_reported_not_ignored(ctx):
     cfg = oracle.Config(**TOY)
     model = bridge.Model(ctx, cfg, "f32")
