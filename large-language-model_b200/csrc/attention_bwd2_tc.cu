@@ -326,8 +326,12 @@ attn_bwd2_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
     // dK / dV of this key tile: rows = keys, this thread's half of the head_dim
     if (ok && __all_sync(0xffffffffu, tc::mbar_wait(&sh->done, 0, status, abort_flag, 344))) {
       tc::tc_fence_after();
-      bf16 *dkrow = dK + (long long)b * dk_b + (long long)kvh * dk_h + (long long)key * dk_s;
-      bf16 *dvrow = dV + (long long)b * dv_b + (long long)kvh * dv_h + (long long)key * dv_s;
+      // every MMA of the CTA has completed: the Q ring is free and serves as the transposition buffers of the stores
+      // (whole 64-byte row segments per store instruction, see tc::stage_store_bf16)
+      const int key0 = j * TK + quarter * 32;
+      bf16 *dkbase = dK + (long long)b * dk_b + (long long)kvh * dk_h + (long long)key0 * dk_s;
+      bf16 *dvbase = dV + (long long)b * dv_b + (long long)kvh * dv_h + (long long)key0 * dv_s;
+      uint8_t *stg = sQ + warp * 2048;
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
         const int col = (half * 2 + c) * 32;
@@ -335,10 +339,10 @@ attn_bwd2_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         tc::tmem_ld_32x32(t_dk + lane_base + col, a);
         tc::tmem_ld_32x32(t_dv + lane_base + col, g);
         tc::tmem_ld_wait();
-        if (key < S) {
+        {
 #pragma unroll
           for (int e = 0; e < 32; ++e) a[e] = __float_as_uint(__uint_as_float(a[e]) * scale);       // dS was left unscaled
-          if (rope_cos != nullptr) {
+          if (rope_cos != nullptr && key < S) {
             // gradient of the rotary embedding (inverse rotation, cpp/src/Positional.cpp:207-231) on dK, position = key
             const float *cp = rope_cos + (size_t)key * (HD / 2) + (col >> 1), *sp = rope_sin + (size_t)key * (HD / 2) + (col >> 1);
 #pragma unroll
@@ -348,20 +352,20 @@ attn_bwd2_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
               a[2 * p2 + 1] = __float_as_uint(-x0 * ss + x1 * cc);
             }
           }
+          uint4 wk[4], wv[4];
 #pragma unroll
           for (int u = 0; u < 4; ++u) {
-            uint4 w;
-            w.x = pack_bf16(__uint_as_float(a[u * 8 + 0]), __uint_as_float(a[u * 8 + 1]));
-            w.y = pack_bf16(__uint_as_float(a[u * 8 + 2]), __uint_as_float(a[u * 8 + 3]));
-            w.z = pack_bf16(__uint_as_float(a[u * 8 + 4]), __uint_as_float(a[u * 8 + 5]));
-            w.w = pack_bf16(__uint_as_float(a[u * 8 + 6]), __uint_as_float(a[u * 8 + 7]));
-            *reinterpret_cast<uint4 *>(dkrow + col + u * 8) = w;
-            w.x = pack_bf16(__uint_as_float(g[u * 8 + 0]), __uint_as_float(g[u * 8 + 1]));
-            w.y = pack_bf16(__uint_as_float(g[u * 8 + 2]), __uint_as_float(g[u * 8 + 3]));
-            w.z = pack_bf16(__uint_as_float(g[u * 8 + 4]), __uint_as_float(g[u * 8 + 5]));
-            w.w = pack_bf16(__uint_as_float(g[u * 8 + 6]), __uint_as_float(g[u * 8 + 7]));
-            *reinterpret_cast<uint4 *>(dvrow + col + u * 8) = w;
+            wk[u].x = pack_bf16(__uint_as_float(a[u * 8 + 0]), __uint_as_float(a[u * 8 + 1]));
+            wk[u].y = pack_bf16(__uint_as_float(a[u * 8 + 2]), __uint_as_float(a[u * 8 + 3]));
+            wk[u].z = pack_bf16(__uint_as_float(a[u * 8 + 4]), __uint_as_float(a[u * 8 + 5]));
+            wk[u].w = pack_bf16(__uint_as_float(a[u * 8 + 6]), __uint_as_float(a[u * 8 + 7]));
+            wv[u].x = pack_bf16(__uint_as_float(g[u * 8 + 0]), __uint_as_float(g[u * 8 + 1]));
+            wv[u].y = pack_bf16(__uint_as_float(g[u * 8 + 2]), __uint_as_float(g[u * 8 + 3]));
+            wv[u].z = pack_bf16(__uint_as_float(g[u * 8 + 4]), __uint_as_float(g[u * 8 + 5]));
+            wv[u].w = pack_bf16(__uint_as_float(g[u * 8 + 6]), __uint_as_float(g[u * 8 + 7]));
           }
+          tc::stage_store_bf16(stg, lane, wk, dkbase + col, (size_t)dk_s, S - key0);
+          tc::stage_store_bf16(stg, lane, wv, dvbase + col, (size_t)dv_s, S - key0);
         }
       }
     }

@@ -53,6 +53,7 @@ attn_fwd2_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
   uint8_t *smem = smem_raw;
   uint8_t *sQ = smem, *sK = sQ + 2 * TILE_BYTES, *sV = sK + 2 * TILE_BYTES;
   Fwd2Shared *sh = (Fwd2Shared *)(sV + 2 * TILE_BYTES);
+  uint8_t *stage = (uint8_t *)(sh + 1);          // 8 softmax warps x 2 KiB: transposition buffers of the output stores
   if (tc::smem_u32(smem) & 1023u) {           // swizzled tiles need 1024-byte alignment: refuse rather than corrupt
     if (threadIdx.x == 0) atomicCAS(status, 0, 298);
     return;
@@ -228,23 +229,24 @@ attn_fwd2_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       tc::tc_fence_after();
       if (ok) {
         const float inv = 1.0f / l;
-        bf16 *orow = O + (long long)b * o_b + (long long)h * o_h + (long long)q_idx * o_s;
+        // rows of the warp: q0w .. q0w+31; whole 64-byte row segments per store instruction (see tc::stage_store_bf16)
+        const int q0w = qt * TQ + quarter * 32;
+        bf16 *obase = O + (long long)b * o_b + (long long)h * o_h + (long long)q0w * o_s;
+        uint8_t *stg = stage + warp * 2048;
 #pragma unroll
         for (int c = 0; c < HD / 32; ++c) {
           uint32_t v[32];
           tc::tmem_ld_32x32(tO + c * 32, v);
           tc::tmem_ld_wait();
-          if (q_idx < S) {
+          uint4 w[4];
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
-              uint4 w;
-              w.x = pack_bf16(__uint_as_float(v[u * 8 + 0]) * inv, __uint_as_float(v[u * 8 + 1]) * inv);
-              w.y = pack_bf16(__uint_as_float(v[u * 8 + 2]) * inv, __uint_as_float(v[u * 8 + 3]) * inv);
-              w.z = pack_bf16(__uint_as_float(v[u * 8 + 4]) * inv, __uint_as_float(v[u * 8 + 5]) * inv);
-              w.w = pack_bf16(__uint_as_float(v[u * 8 + 6]) * inv, __uint_as_float(v[u * 8 + 7]) * inv);
-              *reinterpret_cast<uint4 *>(orow + c * 32 + u * 8) = w;
-            }
+          for (int u = 0; u < 4; ++u) {
+            w[u].x = pack_bf16(__uint_as_float(v[u * 8 + 0]) * inv, __uint_as_float(v[u * 8 + 1]) * inv);
+            w[u].y = pack_bf16(__uint_as_float(v[u * 8 + 2]) * inv, __uint_as_float(v[u * 8 + 3]) * inv);
+            w[u].z = pack_bf16(__uint_as_float(v[u * 8 + 4]) * inv, __uint_as_float(v[u * 8 + 5]) * inv);
+            w[u].w = pack_bf16(__uint_as_float(v[u * 8 + 6]) * inv, __uint_as_float(v[u * 8 + 7]) * inv);
           }
+          tc::stage_store_bf16(stg, lane, w, obase + c * 32, (size_t)o_s, S - q0w);
         }
         if (lse && q_idx < S) lse[((long long)b * nH + h) * S + q_idx] = (m_used + log2f(l)) * (1.0f / LOG2E);   // natural-log units
       }
@@ -267,7 +269,7 @@ int fwd2_launch_t(b200_ctx *ctx, const void *Q, const void *K, const void *V, vo
   if (make_map_4d(&mq, Q, HD, S, nH, B, st.q_s, st.q_h, st.q_b) || make_map_4d(&mk, K, HD, S, nKV, B, st.k_s, st.k_h, st.k_b) ||
       make_map_4d(&mv, V, HD, S, nKV, B, st.v_s, st.v_h, st.v_b))
     return b200_fail(ctx, B200_ERR_CUDA, "cuTensorMapEncodeTiled failed for attention operands");
-  constexpr int smem = 6 * 128 * HD * 2 + (int)sizeof(Fwd2Shared);
+  constexpr int smem = 6 * 128 * HD * 2 + (int)sizeof(Fwd2Shared) + 8 * 2048;
   static_assert(smem <= 232448, "forward attention tiles exceed the 227 KiB of shared memory per CTA");
   static bool attr = false;
   if (!attr) { B200_CUDA(ctx, cudaFuncSetAttribute(attn_fwd2_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)); attr = true; }

@@ -105,18 +105,7 @@ __device__ __forceinline__ void rope_apply(uint32_t (&r)[32], const RopeVals &v)
 // its 32-row chunk through a private, swizzled shared-memory buffer and writes whole row segments: one instruction covers
 // 8 rows x 64 B (bf16) or 4 rows x 128 B (fp32).  All 32 lanes must call; rows at or beyond rows_valid are not written.
 // base points at (first row of the warp, first column of the chunk).
-__device__ __forceinline__ void stage_store_bf16(uint8_t *stg, int lane, const uint4 (&v)[4], bf16 *base, size_t ld, int rows_valid) {
-#pragma unroll
-  for (int k = 0; k < 4; ++k) *reinterpret_cast<uint4 *>(stg + lane * 64 + ((k ^ ((lane >> 1) & 3)) << 4)) = v[k];
-  __syncwarp();
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const int r = 8 * i + (lane >> 2), w = lane & 3;
-    const uint4 x = *reinterpret_cast<const uint4 *>(stg + r * 64 + ((w ^ ((r >> 1) & 3)) << 4));
-    if (r < rows_valid) *reinterpret_cast<uint4 *>(base + (size_t)r * ld + w * 8) = x;
-  }
-  __syncwarp();
-}
+using tc::stage_store_bf16;
 __device__ __forceinline__ void pack_chunk_bf16(const uint32_t (&r)[32], uint4 (&v)[4]) {
 #pragma unroll
   for (int k = 0; k < 4; ++k) {

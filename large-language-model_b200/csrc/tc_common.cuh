@@ -137,6 +137,27 @@ __device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t *r)
 }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
+// ---- result stores ------------------------------------------------------------
+// A thread that read one accumulator ROW from tensor memory holds 32 columns of it; written directly, one warp store
+// instruction touches 32 rows with 16 bytes each (32 half-used sectors), and such stores -- not the MMAs -- were
+// measured to bound the GEMM epilogue.  Here the warp transposes its 32-row x 32-column bf16 chunk (v[k] = columns
+// 8k..8k+7 of the lane's row) through a private 2 KiB shared-memory buffer, XOR-swizzled so that neither phase has bank
+// conflicts, and writes whole row segments: one instruction covers 8 rows x 64 B.  All 32 lanes must call; rows at or
+// beyond rows_valid are not written.  base points at (first row of the warp, first column of the chunk); ld in elements.
+__device__ __forceinline__ void stage_store_bf16(uint8_t *stg, int lane, const uint4 (&v)[4], __nv_bfloat16 *base, size_t ld,
+                                                 int rows_valid) {
+#pragma unroll
+  for (int k = 0; k < 4; ++k) *reinterpret_cast<uint4 *>(stg + lane * 64 + ((k ^ ((lane >> 1) & 3)) << 4)) = v[k];
+  __syncwarp();
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int r = 8 * i + (lane >> 2), w = lane & 3;
+    const uint4 x = *reinterpret_cast<const uint4 *>(stg + r * 64 + ((w ^ ((r >> 1) & 3)) << 4));
+    if (r < rows_valid) *reinterpret_cast<uint4 *>(base + (size_t)r * ld + w * 8) = x;
+  }
+  __syncwarp();
+}
+
 // ---- descriptors -------------------------------------------------------------
 // Shared-memory matrix descriptor for a 128-byte-swizzled tile (tile base 1024-byte aligned):
 //   bits [0,14)  start address >> 4        bits [16,30) leading byte offset >> 4
