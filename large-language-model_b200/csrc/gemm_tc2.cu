@@ -19,8 +19,8 @@ constexpr int BM = 128, BN = 256, BK = 64, STAGES = 6;
 constexpr int A_STAGE_BYTES = BM * BK * 2;        // 16 KiB: this CTA's 128 rows
 constexpr int B_STAGE_BYTES = (BN / 2) * BK * 2;  // 16 KiB: this CTA's half of the 256 columns
 constexpr int CHUNK_BYTES = 64 * BK * 2;
-constexpr int STORE_STAGE_BYTES = 32 * 128;       // per epilogue warp: 32 rows x 128 B, the transposition buffer of the result stores
-constexpr int SMEM_BYTES = STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + 1024 + 256 + 4 * STORE_STAGE_BYTES;
+constexpr int STORE_STAGE_BYTES = 2 * 32 * 128;   // per epilogue warp: two boxes of 32 rows x 128 B for the result stores
+constexpr int SMEM_BYTES = STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + 1024 + 1024 + 4 * STORE_STAGE_BYTES;
 constexpr int THREADS = 192;
 constexpr int GROUP_M = 8;                        // 256-row tile pairs per rasterisation group
 constexpr uint32_t LEADER_MASK = 0xFEFFFFFFu;     // clears the CTA-rank bit of a shared::cluster address (rank 0)
@@ -117,11 +117,53 @@ __device__ __forceinline__ void pack_chunk_bf16(const uint32_t (&r)[32], uint4 (
     }
   }
 }
+// Bulk-store route of a warp: its boxes alternate between two 4 KiB buffers; a buffer is rewritten only after the bulk
+// store issued from it two boxes ago has finished reading it.  Box layout = the tensor map's swizzle (64-byte for bf16
+// rows of 64 B, 128-byte for fp32 rows of 128 B), which is also what makes the st.shared of 32 rows conflict-free.
+struct BulkOut {
+  uint8_t *buf;      // 1024-byte aligned, 2 x 4096 bytes; null: the route is off
+  int n;             // boxes issued so far
+};
+__device__ __forceinline__ uint8_t *bulk_box_begin(BulkOut &o, int lane) {
+  if (lane == 0) tc::bulk_wait_read<1>();
+  __syncwarp();
+  return o.buf + (o.n & 1) * 4096;
+}
+__device__ __forceinline__ void bulk_box_issue(BulkOut &o, int lane, const uint8_t *box, const CUtensorMap *map, int col, int row, bool add) {
+  tc::fence_proxy_async();           // this thread's st.shared become visible to the bulk-copy engine
+  __syncwarp();
+  if (lane == 0) {
+    if (add) tc::tma_reduce_add_2d(map, box, col, row); else tc::tma_store_2d(map, box, col, row);
+    tc::bulk_commit();
+  }
+  ++o.n;
+}
+__device__ __forceinline__ void bulk_store_bf16(BulkOut &o, int lane, const uint4 (&v)[4], const CUtensorMap *map, int col, int row) {
+  uint8_t *box = bulk_box_begin(o, lane);
+#pragma unroll
+  for (int k = 0; k < 4; ++k) *reinterpret_cast<uint4 *>(box + lane * 64 + ((k ^ ((lane >> 1) & 3)) << 4)) = v[k];
+  bulk_box_issue(o, lane, box, map, col, row, false);
+}
 // One 32-column chunk of the warp's 32 accumulator rows -> global memory.  Warp-collective: every lane calls it with its
 // own row's values (lane = row - row0); `red`: this tile is one K-split of several -> add into C with vector reductions.
 template <class TO, bool ACC>
 __device__ __forceinline__ void store_chunk(uint32_t (&r)[32], TO *C, size_t ldc, int row0, int lane, int col, int M, int N,
-                                            uint8_t *stg, bool red) {
+                                            uint8_t *stg, bool red, BulkOut &bo, const CUtensorMap *map_c) {
+  if (bo.buf) {                     // bulk tensor store: clipped at the edges of C by the copy engine
+    if (row0 >= M) return;
+    if constexpr (sizeof(TO) == 2) {
+      uint4 v[4];
+      pack_chunk_bf16(r, v);
+      bulk_store_bf16(bo, lane, v, map_c, col, row0);
+    } else {
+      uint8_t *box = bulk_box_begin(bo, lane);
+#pragma unroll
+      for (int k = 0; k < 8; ++k)
+        *reinterpret_cast<uint4 *>(box + lane * 128 + ((k ^ (lane & 7)) << 4)) = make_uint4(r[4 * k], r[4 * k + 1], r[4 * k + 2], r[4 * k + 3]);
+      bulk_box_issue(bo, lane, box, map_c, col, row0, red || ACC);
+    }
+    return;
+  }
   const int rows_valid = M - row0;
   if (col + 32 <= N) {
     if constexpr (sizeof(TO) == 2) {
@@ -172,7 +214,7 @@ constexpr float LOG2E = 1.4426950408889634f;
 // Cross-entropy epilogue of one accumulator row (one thread) over the 256 columns of a tile; see GemmEpilogue::ce_mode.
 // Softmax statistics are kept in base-2 units (x * log2e): one FMA and one ex2 per element.
 __device__ __forceinline__ void ce_row_epilogue(uint32_t taddr, bf16 *C, size_t ldc, int row0, int lane, int tn, int M, int N,
-                                                const GemmEpilogue &epi, uint8_t *stg) {
+                                                const GemmEpilogue &epi, uint8_t *stg, BulkOut &bo, const CUtensorMap *map_c) {
   const int row = row0 + lane;
   const bool row_ok = row < M;
   const uint32_t tgt = row_ok ? __ldg(epi.ce_targets + row) : 0xffffffffu;
@@ -195,7 +237,7 @@ __device__ __forceinline__ void ce_row_epilogue(uint32_t taddr, bf16 *C, size_t 
             r[j] = __float_as_uint(p * epi.ce_scale);
           }
         }
-        store_chunk<bf16, false>(r, C, ldc, row0, lane, col, M, N, stg, false);
+        store_chunk<bf16, false>(r, C, ldc, row0, lane, col, M, N, stg, false, bo, map_c);
       }
     }
     return;
@@ -211,7 +253,7 @@ __device__ __forceinline__ void ce_row_epilogue(uint32_t taddr, bf16 *C, size_t 
     if (col >= N) continue;                                   // warp-uniform
     if (epi.ce_mode == 2) {
       // the stored logits are bf16: take the statistics from the rounded values, which is what a later pass reads back
-      store_chunk<bf16, false>(r, C, ldc, row0, lane, col, M, N, stg, false);
+      store_chunk<bf16, false>(r, C, ldc, row0, lane, col, M, N, stg, false, bo, map_c);
 #pragma unroll
       for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__bfloat162float(__float2bfloat16_rn(__uint_as_float(r[j]))));
     }
@@ -244,7 +286,8 @@ __device__ __forceinline__ void ce_row_epilogue(uint32_t taddr, bf16 *C, size_t 
 template <bool A_MN, bool B_MN, class TO, bool ACC>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                TO *__restrict__ C, int M, int N, int K, size_t ldc, int *status, GemmEpilogue epi, int splits) {
+                const __grid_constant__ CUtensorMap map_c, const __grid_constant__ CUtensorMap map_act,
+                TO *__restrict__ C, int M, int N, int K, size_t ldc, int *status, GemmEpilogue epi, int splits, int bulk_store) {
   pdl_launch_dependents();             // the next kernel of the stream may be scheduled onto SMs as this grid leaves them
   extern __shared__ uint8_t smem_raw[];
   uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -352,7 +395,8 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     }
   } else {
     const int q = warp & 3;                        // tensor-memory lane quarter this warp may read
-    uint8_t *stg = smem + STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + 256 + (warp - 2) * STORE_STAGE_BYTES;
+    uint8_t *stg = smem + STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + 1024 + (warp - 2) * STORE_STAGE_BYTES;
+    BulkOut bo{bulk_store ? stg : nullptr, 0};
     int acc = 0; uint32_t acc_phase = 0;
     bool ok = true;
     for (int it = cluster_id; it < items && ok; it += n_clusters) {
@@ -369,7 +413,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN;
       if constexpr (sizeof(TO) == 2 && !ACC) {
         if (epi.ce_mode) {
-          ce_row_epilogue(taddr, (bf16 *)C, ldc, row0, lane, tn, M, N, epi, stg);
+          ce_row_epilogue(taddr, (bf16 *)C, ldc, row0, lane, tn, M, N, epi, stg, bo, &map_c);
           tc::tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive_cluster(tc::smem_u32(&sh->acc_empty[acc]) & LEADER_MASK);
@@ -396,10 +440,18 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                 g[j] = __float_as_uint(fmaf(h, tanh_approx(h), h) * __uint_as_float(u[j]));
               }
               pack_chunk_bf16(g, va);
-              bf16 *cbase = (bf16 *)C + (size_t)row0 * ldc + col;
-              stage_store_bf16(stg, lane, vg, cbase, ldc, M - row0);
-              stage_store_bf16(stg, lane, vu, cbase + epi.swiglu_I, ldc, M - row0);
-              stage_store_bf16(stg, lane, va, (bf16 *)epi.act_out + (size_t)row0 * epi.ld_act + col, epi.ld_act, M - row0);
+              if (bo.buf) {
+                if (row0 < M) {
+                bulk_store_bf16(bo, lane, vg, &map_c, col, row0);
+                bulk_store_bf16(bo, lane, vu, &map_c, col + epi.swiglu_I, row0);
+                bulk_store_bf16(bo, lane, va, &map_act, col, row0);
+                }
+              } else {
+                bf16 *cbase = (bf16 *)C + (size_t)row0 * ldc + col;
+                stage_store_bf16(stg, lane, vg, cbase, ldc, M - row0);
+                stage_store_bf16(stg, lane, vu, cbase + epi.swiglu_I, ldc, M - row0);
+                stage_store_bf16(stg, lane, va, (bf16 *)epi.act_out + (size_t)row0 * epi.ld_act + col, epi.ld_act, M - row0);
+              }
             }
           }
           tc::tc_fence_before();
@@ -425,13 +477,14 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           rope0 = rope_ahead;
           if (rope_ahead) rope_now = rope_next;
         }
-        if (col < N) store_chunk<TO, ACC>(r, C, ldc, row0, lane, col, M, N, stg, splits > 1);
+        if (col < N) store_chunk<TO, ACC>(r, C, ldc, row0, lane, col, M, N, stg, splits > 1, bo, &map_c);
       }
       tc::tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(tc::smem_u32(&sh->acc_empty[acc]) & LEADER_MASK);   // the leader issues the MMAs
       if (++acc == 2) { acc = 0; acc_phase ^= 1; }
     }
+    if (bo.buf && lane == 0) tc::bulk_wait_all();      // the bulk stores have landed before the CTA exits
   }
   tc::tc_fence_before();
   __syncthreads();
@@ -447,6 +500,15 @@ template <bool A_MN, bool B_MN, class TO, bool ACC>
 int launch_variant(b200_ctx *ctx, const CUtensorMap &ma, const CUtensorMap &mb, void *C, int M, int N, int K,
                    size_t ldc, const GemmEpilogue &epi) {
   auto kern = gemm_tc2_kernel<A_MN, B_MN, TO, ACC>;
+  // Results leave through bulk tensor stores when C (and the activation output) can carry a tensor map.
+  static const bool bulk_wanted = [] { const char *e = getenv("B200_GEMM_BULK_STORE"); return !(e && e[0] == '0'); }();
+  CUtensorMap mc = ma, mact = ma;    // placeholders when the route is off (never dereferenced)
+  int bulk = 0;
+  if (bulk_wanted && C && (uintptr_t)C % 16 == 0 && (ldc * sizeof(TO)) % 16 == 0) {
+    bulk = tc_make_map_store_2d(&mc, C, (int)sizeof(TO), (uint64_t)N, (uint64_t)M, ldc * sizeof(TO)) == 0;
+    if (bulk && epi.swiglu_I > 0)
+      bulk = tc_make_map_store_2d(&mact, epi.act_out, 2, (uint64_t)epi.swiglu_I, (uint64_t)M, (uint64_t)epi.ld_act * 2) == 0;
+  }
   static bool attr_set = false;
   static int max_clusters = 0;
   cudaLaunchConfig_t cfg = {};
@@ -486,7 +548,7 @@ int launch_variant(b200_ctx *ctx, const CUtensorMap &ma, const CUtensorMap &mb, 
   }
   // the clear that split-K needs is part of the GEMM's cost: it sits inside the timed interval
   if (splits > 1 && !ACC) B200_CUDA(ctx, cudaMemsetAsync(C, 0, (size_t)M * N * sizeof(float), ctx->stream));
-  B200_CUDA(ctx, cudaLaunchKernelEx(&cfg, kern, ma, mb, (TO *)C, M, N, K, ldc, ctx->dev_status, epi, splits));
+  B200_CUDA(ctx, cudaLaunchKernelEx(&cfg, kern, ma, mb, mc, mact, (TO *)C, M, N, K, ldc, ctx->dev_status, epi, splits, bulk));
   ctx->launches++;
   if (ctx->trace_on) {      // one trace site per GEMM shape and form
     static std::vector<std::string *> keys;

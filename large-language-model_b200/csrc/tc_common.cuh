@@ -158,6 +158,22 @@ __device__ __forceinline__ void stage_store_bf16(uint8_t *stg, int lane, const u
   __syncwarp();
 }
 
+// ---- bulk tensor stores (shared memory -> global memory through a tensor map) ----
+// The smem box must be laid out in the map's swizzle mode; out-of-range rows / columns of the box are not written.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap *map, const void *src, int c0, int c1) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(map), "r"(smem_u32(src)), "r"(c0), "r"(c1) : "memory");
+}
+// element-wise add of the box into global memory (element type of the map: fp32)
+__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap *map, const void *src, int c0, int c1) {
+  asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(map), "r"(smem_u32(src)), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// all but the newest `N` committed groups of this thread have finished READING their shared-memory source
+template <int N> __device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
 // ---- descriptors -------------------------------------------------------------
 // Shared-memory matrix descriptor for a 128-byte-swizzled tile (tile base 1024-byte aligned):
 //   bits [0,14)  start address >> 4        bits [16,30) leading byte offset >> 4
@@ -189,6 +205,8 @@ __host__ __device__ constexpr uint32_t make_idesc_bf16(int M, int N, bool a_mn_m
 // dims/box in elements; row_stride_bytes must be a multiple of 16.
 int tc_make_map_2d(CUtensorMap *map, const void *base, uint64_t inner, uint64_t outer, uint64_t row_stride_bytes,
                    uint32_t box_inner, uint32_t box_outer);
+// Map for result stores of 32-column x 32-row boxes: elem_bytes 2 (bf16, 64-byte swizzle) or 4 (fp32, 128-byte swizzle).
+int tc_make_map_store_2d(CUtensorMap *map, const void *base, int elem_bytes, uint64_t inner, uint64_t outer, uint64_t row_stride_bytes);
 int tc_make_map_3d(CUtensorMap *map, const void *base, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t stride1_bytes,
                    uint64_t stride2_bytes, uint32_t b0, uint32_t b1, uint32_t b2);
 int tc_make_map_4d(CUtensorMap *map, const void *base, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t d3,
