@@ -154,6 +154,22 @@ extern "C" int b200_internal_set_gemm_skinny(b200_ctx *ctx, int enable) {
   ctx->gemm_skinny = enable != 0;
   return B200_OK;
 }
+// Test hook for the epilogues of the few-row GEMM that only the decode step uses (bf16; null pointers switch a part off):
+//   producer half: C = residual + A W, xw_out = C * next_norm_w, stat_acc[row * 2 + {0, 1}] += the row's sums of squares (2^-32 fixed point);
+//   consumer half: C = rstd(row_acc) * (A W), optionally through the SwiGLU or the rotary epilogue (table row `pos`).
+extern "C" int b200_internal_few_row_gemm(b200_ctx *ctx, const void *A, const void *W, void *C, size_t M, size_t N, size_t K,
+                                          const void *residual, const void *next_norm_w, void *xw_out, unsigned long long *stat_acc,
+                                          const unsigned long long *row_acc, int norm_double, float eps,
+                                          int swiglu_I, const float *cos_t, const float *sin_t, int hd, int rope_cols, int pos) {
+  if (!ctx) return B200_ERR_INVALID;
+  GemmEpilogue epi;
+  epi.residual = residual; epi.ld_res = N;
+  epi.next_norm_w = next_norm_w; epi.xw_out = xw_out; epi.ld_xw = N; epi.stat_acc = stat_acc;
+  epi.row_acc = row_acc; epi.norm_double = norm_double; epi.norm_eps = eps;
+  epi.swiglu_I = swiglu_I;
+  if (cos_t) { epi.cos_t = cos_t + (size_t)pos * (hd / 2); epi.sin_t = sin_t + (size_t)pos * (hd / 2); epi.S = 1; epi.hd = hd; epi.cols = rope_cols; }
+  return b200_gemm_ld(ctx, A, W, C, M, N, K, 0, 0, 0, B200_BF16, B200_BF16, K, N, swiglu_I > 0 ? (size_t)swiglu_I : N, &epi);
+}
 extern "C" int b200_profile_gemm(b200_ctx *ctx, int enable) {
   if (!ctx) return B200_ERR_INVALID;
   ctx->time_gemm = enable != 0;
@@ -281,7 +297,8 @@ int b200_gemm_ld(b200_ctx *ctx, const void *A, const void *B, void *C, size_t M,
                              gemm_tc_supported(A, B, C, M, N, K, lda, ldb, ldc, out_dt)),
                "gemm: a fused epilogue needs the tensor-core path");
   const bool few_rows = K > 0 && ctx->gemm_skinny && gemm_skinny_supported(M, ta, tb, acc);
-  B200_REQUIRE(ctx, !(epi && epi->pos_dev) || few_rows, "gemm: device-side positions exist only in the few-row kernel");
+  B200_REQUIRE(ctx, !(epi && (epi->pos_dev || epi->row_acc || epi->next_norm_w || epi->residual)) || few_rows,
+               "gemm: device-side positions, the folded normalisation and the residual epilogue exist only in the few-row kernel");
   B200_REQUIRE(ctx, !(epi && epi->swiglu_I) || few_rows || (epi->act_out && K > 0 && gemm_tc2_swiglu_eligible(ctx, M, (size_t)epi->swiglu_I)),
                "gemm: no kernel with a SwiGLU epilogue takes this shape");
   if (M == 0 || N == 0) return B200_OK;

@@ -152,6 +152,24 @@ struct GemmEpilogue {
   // W = [gate | up] (I columns each).  Few-row kernel: C[M, I] = silu(A*gate) * (A*up) and nothing else is written.
   // Two-CTA kernel (act_out set): C[M, 2I] = A*W as usual AND act_out[M, I] = silu(gate) * up computed from the fp32
   // accumulators (slightly more accurate than the separate SwiGLU kernel, which reads the bf16-rounded products back).
+  // Few-row kernel only: an RMS normalisation split between the projection that PRODUCES a row h and the one that
+  // CONSUMES norm(h), so that a decode step needs no normalisation kernel.
+  //   producer: C = h = residual + A*W (residual: type of C, leading dimension ld_res).  With next_norm_w (N elements)
+  //     it also writes xw_out = bf16(h * next_norm_w) (leading dimension ld_xw) and adds every row's sums of h^2 and
+  //     xw^2 over its columns to stat_acc[row * 2 + {0, 1}] as 2^-32 fixed-point integers (integer atomics: the total
+  //     does not depend on the order of the CTAs).  The caller zeroes stat_acc beforehand.
+  //   consumer: A = xw.  With row_acc (the producer's stat_acc) the product is scaled by
+  //     rstd = rsqrt(sum h^2 / K + norm_eps); norm_double applies the second, unit-weight norm of the normalised row as
+  //     well (its statistic is rstd^2 * sum xw^2 / K).
+  const void *residual = nullptr;
+  size_t ld_res = 0;
+  const void *next_norm_w = nullptr;
+  void *xw_out = nullptr;
+  size_t ld_xw = 0;
+  unsigned long long *stat_acc = nullptr;
+  const unsigned long long *row_acc = nullptr;
+  int norm_double = 0;
+  float norm_eps = 0.f;
   int swiglu_I = 0;
   void *act_out = nullptr;
   size_t ld_act = 0;

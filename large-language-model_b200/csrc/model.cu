@@ -128,6 +128,7 @@ struct b200_model {
   float *dec_attn_ws = nullptr;                      // partial results of the split-key decode attention
   int *dec_attn_tickets = nullptr;                   // [cache_batch, nH], zero between launches
   uint64_t dec_graph_nodes = 0;                      // kernel launches in one captured decode step
+  unsigned long long *dec_stats = nullptr;           // [2 L][cache_batch][2] row sums of the normalisations folded into the decode projections
   int *dec_pos = nullptr;                            // device copy of the position being decoded (captured steps read it)
   // data parallel
   nccl::comm_t comm = nullptr;
@@ -944,10 +945,10 @@ extern "C" int b200_model_decode_begin(b200_model *m, size_t batch, size_t max_t
     for (void *p : m->k_cache) drop(p);
     for (void *p : m->v_cache) drop(p);
     drop(m->dec_logits); drop(m->dec_h); drop(m->dec_history); drop(m->dec_next); drop(m->dec_attn_ws);
-    drop(m->dec_attn_tickets); drop(m->dec_pos);
+    drop(m->dec_attn_tickets); drop(m->dec_pos); drop(m->dec_stats);
     m->k_cache.clear(); m->v_cache.clear();
     m->dec_logits = m->dec_h = nullptr; m->dec_history = m->dec_next = nullptr; m->dec_attn_ws = nullptr;
-    m->dec_attn_tickets = nullptr; m->dec_pos = nullptr;
+    m->dec_attn_tickets = nullptr; m->dec_pos = nullptr; m->dec_stats = nullptr;
     batch = batch > m->cache_batch ? batch : m->cache_batch;
     max_total_len = max_total_len > m->cache_len ? max_total_len : m->cache_len;
     m->cache_batch = m->cache_len = 0;
@@ -967,6 +968,9 @@ extern "C" int b200_model_decode_begin(b200_model *m, size_t batch, size_t max_t
   TRY(dalloc(m, (void **)&m->dec_attn_tickets, batch * m->nH * sizeof(int)));
   TRY(b200_fill_zero(ctx, m->dec_attn_tickets, batch * m->nH * sizeof(int)));
   TRY(dalloc(m, (void **)&m->dec_pos, sizeof(int)));
+  if (m->dt == B200_BF16) {
+    TRY(dalloc(m, (void **)&m->dec_stats, 2 * m->L * batch * 2 * sizeof(unsigned long long)));
+  }
   m->cache_batch = batch; m->cache_len = max_total_len;
   return B200_OK;
 }
@@ -988,7 +992,24 @@ extern "C" int b200_model_prefill(b200_model *m, const int32_t *tok, size_t B, s
 // training forward so that the caller fuses the residual add with the next norm.
 // pos_dev (optional): device int holding `pos`; the kernels then read the position on the device, which makes the
 // enqueued step independent of the position (it can be captured once and replayed).  Needs the few-row GEMM path.
-static int layer_decode_core(b200_model *m, size_t l, const void *h_in, size_t B, size_t pos, const int *pos_dev = nullptr) {
+// True when a decode step of B sequences runs every projection on the few-row GEMM kernel with the normalisations and
+// residual adds folded into it (bf16; B200_DECODE_FOLD_NORM=0 keeps the separate kernels).
+static bool decode_folded(const b200_model *m, size_t B) {
+  const char *env = getenv("B200_DECODE_FOLD_NORM");
+  if (env && env[0] == '0') return false;
+  if (m->dt != B200_BF16 || !m->ctx->gemm_skinny || !gemm_skinny_supported(B, 0, 0, 0) || m->L == 0) return false;
+  if (m->H % 8 || m->I % 8 || m->hd % 2 || !m->dec_stats) return false;
+  const b200_model::Act &a = m->acts[0];
+  const size_t H = m->H, I = m->I;
+  return gemm_tc_supported(a.a2, m->P(m->off_qkv(0)), a.qkv, B, m->QKV, H, H, m->QKV, m->QKV, m->dt) &&
+         gemm_tc_supported(a.o, m->P(m->off_o(0)), a.h_mid, B, H, m->Q, m->Q, H, H, m->dt) &&
+         gemm_tc_supported(a.h_mid, m->P(m->off_gate_up(0)), a.act, B, 2 * I, H, H, 2 * I, I, m->dt) &&
+         gemm_tc_supported(a.act, m->P(m->off_down(0)), m->hs[1], B, H, I, I, H, H, m->dt) &&
+         gemm_tc_supported(m->fh, m->P(m->off_out()), a.qkv, B, m->V, H, H, m->V, m->V, m->dt);
+}
+
+static int layer_decode_core(b200_model *m, size_t l, const void *h_in, size_t B, size_t pos, const int *pos_dev = nullptr,
+                             bool fold = false) {
   b200_ctx *ctx = m->ctx;
   const size_t H = m->H, I = m->I;
   const float eps = m->cfg.rms_norm_eps;
@@ -996,13 +1017,17 @@ static int layer_decode_core(b200_model *m, size_t l, const void *h_in, size_t B
   const b200_dtype dt = m->dt;
   const size_t es = dtype_size(dt), half = m->hd / 2;
   const float *cos_p = m->cos_t + pos * half, *sin_p = m->sin_t + pos * half;    // every row is at position `pos`
-  const bool rope_in_gemm = dt == B200_BF16 && m->hd % 32 == 0 && (pos * half * 4) % 16 == 0 &&
-                            gemm_tc_supported(a.a2, m->P(m->off_qkv(l)), a.qkv, B, m->QKV, H, H, m->QKV, m->QKV, dt);
+  const bool rope_in_gemm = fold || (dt == B200_BF16 && m->hd % 32 == 0 && (pos * half * 4) % 16 == 0 &&
+                            gemm_tc_supported(a.a2, m->P(m->off_qkv(l)), a.qkv, B, m->QKV, H, H, m->QKV, m->QKV, dt));
   B200_REQUIRE(ctx, !pos_dev || rope_in_gemm, "decode: device-side positions need the bf16 few-row GEMM path");
   if (rope_in_gemm) {
     GemmEpilogue epi;
     epi.cos_t = cos_p; epi.sin_t = sin_p; epi.S = 1; epi.hd = (int)m->hd; epi.cols = (int)(m->Q + m->KV);
     if (pos_dev) { epi.cos_t = m->cos_t; epi.sin_t = m->sin_t; epi.pos_dev = pos_dev; }
+    // folded, layers after the first: a2 holds h * w_attn_norm and slot 2l-1 of dec_stats the row sums, both left by the
+    // previous layer's down projection; the scale applies the layer norm and the attention's inner unit norm
+    // (cpp/src/Transformer.cpp layer forward: attn_norm, then Attention's own input norm)
+    if (fold && l > 0) { epi.row_acc = m->dec_stats + (2 * l - 1) * 2 * m->cache_batch; epi.norm_double = 1; epi.norm_eps = eps; }
     TRY(b200_gemm_ld(ctx, a.a2, m->P(m->off_qkv(l)), a.qkv, B, m->QKV, H, 0, 0, 0, dt, dt, H, m->QKV, m->QKV, &epi));
   } else {
     TRY(b200_gemm_ld(ctx, a.a2, m->P(m->off_qkv(l)), a.qkv, B, m->QKV, H, 0, 0, 0, dt, dt, H, m->QKV, m->QKV));
@@ -1017,6 +1042,21 @@ static int layer_decode_core(b200_model *m, size_t l, const void *h_in, size_t B
   TRY(attn_decode(ctx, a.qkv, fused_append ? (const char *)a.qkv + m->Q * es : nullptr,
                   fused_append ? (const char *)a.qkv + (m->Q + m->KV) * es : nullptr, m->k_cache[l], m->v_cache[l],
                   a.o, B, m->nH, m->nKV, m->hd, m->cache_len, pos + 1, m->QKV, m->Q, m->dec_attn_ws, m->dec_attn_tickets, dt, pos_dev));
+  if (fold) {
+    const bool last = l + 1 == m->L;
+    GemmEpilogue eo;                                // h_mid = h + o Wo;  ffn_in = h_mid * w_ffn_norm, row sums
+    eo.residual = h_in; eo.ld_res = H;
+    eo.next_norm_w = m->P(m->off_ffn_norm(l)); eo.xw_out = a.ffn_in; eo.ld_xw = H; eo.stat_acc = m->dec_stats + (2 * l) * 2 * m->cache_batch;
+    TRY(b200_gemm_ld(ctx, a.o, m->P(m->off_o(l)), a.h_mid, B, H, m->Q, 0, 0, 0, dt, dt, m->Q, H, H, &eo));
+    GemmEpilogue eg;                                // act = silu(g) * u of rstd * (ffn_in [Wg | Wu])
+    eg.swiglu_I = (int)I; eg.row_acc = eo.stat_acc; eg.norm_eps = eps;
+    TRY(b200_gemm_ld(ctx, a.ffn_in, m->P(m->off_gate_up(l)), a.act, B, 2 * I, H, 0, 0, 0, dt, dt, H, 2 * I, I, &eg));
+    GemmEpilogue ed;                                // next stream = h_mid + act Wd;  the next norm's input and row sums
+    ed.residual = a.h_mid; ed.ld_res = H;
+    ed.next_norm_w = m->P(last ? m->off_final_norm() : m->off_attn_norm(l + 1));
+    ed.xw_out = last ? m->fh : m->acts[l + 1].a2; ed.ld_xw = H; ed.stat_acc = m->dec_stats + (2 * l + 1) * 2 * m->cache_batch;
+    return b200_gemm_ld(ctx, a.act, m->P(m->off_down(l)), m->hs[l + 1], B, H, I, 0, 0, 0, dt, dt, I, H, H, &ed);
+  }
   TRY(b200_gemm_ld(ctx, a.o, m->P(m->off_o(l)), m->tmpH, B, H, m->Q, 0, 0, 0, dt, dt, m->Q, H, H));
   TRY(add_norm_oop(ctx, h_in, m->tmpH, a.h_mid, m->P(m->off_ffn_norm(l)), a.ffn_in, B, H, eps, dt));
   if (dt == B200_BF16 && ctx->gemm_skinny && gemm_skinny_supported(B, 0, 0, 0) && I % 8 == 0 &&
@@ -1051,6 +1091,9 @@ static int decode_step_impl(b200_model *m, const int32_t *tok, size_t B, size_t 
   const size_t H = m->H;
   const float eps = m->cfg.rms_norm_eps;
   const b200_dtype dt = m->dt;
+  const bool folded = decode_folded(m, B);
+  if (folded)      // the row-sum accumulators of the folded normalisations start every step at zero
+    B200_CUDA(ctx, cudaMemsetAsync(m->dec_stats, 0, 2 * m->L * m->cache_batch * 2 * sizeof(unsigned long long), ctx->stream));
   {
     // The first kernel of a step is launched WITHOUT programmatic serialization, so it starts only when every kernel of
     // the previous step has completed: programmatic dependent launch orders a kernel against its immediate predecessor
@@ -1060,6 +1103,14 @@ static int decode_step_impl(b200_model *m, const int32_t *tok, size_t B, size_t 
     const int rc = b200_embedding_forward(ctx, (const uint32_t *)tok, m->P(m->off_emb()), m->hs[0], B, H, m->V, dt);
     ctx->pdl = keep;
     TRY(rc);
+  }
+  if (folded) {
+    // five launches per layer: after the first layer's input norm every normalisation and residual add rides in a projection
+    TRY(add_norm_norm_oop(ctx, m->hs[0], nullptr, nullptr, m->P(m->off_attn_norm(0)), nullptr, m->ones, m->acts[0].a2, m->acts[0].a1, B, H, eps, dt));
+    for (size_t l = 0; l < m->L; ++l) TRY(layer_decode_core(m, l, m->hs[l], B, pos, pos_dev, true));
+    GemmEpilogue ev;
+    ev.row_acc = m->dec_stats + (2 * m->L - 1) * 2 * m->cache_batch; ev.norm_eps = eps;
+    return b200_gemm_ld(ctx, m->fh, m->P(m->off_out()), logits, B, m->V, H, 0, 0, 0, dt, dt, H, m->V, m->V, &ev);
   }
   if (m->L == 0) {
     TRY(b200_rms_norm_forward(ctx, m->hs[0], m->fh, m->P(m->off_final_norm()), nullptr, eps, B, H, dt));

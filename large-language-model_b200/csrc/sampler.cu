@@ -11,12 +11,15 @@
 // Nothing is sorted: the k-th largest value and the top-p crossing value are found by repeated linear
 // histograms (2048 bins) over a shrinking value range, walking the bins from the largest values down.
 // Probability mass is accumulated as 2^-40 fixed point integers, so the result does not depend on the order
-// in which threads add to a bin, and a given (logits, seed, step, row) always yields the same token.
+// in which threads add to a bin, and a given (logits, seed, step, row) always yields the same token.  A bin's
+// mass is kept as three 14-bit-wide pieces in 32-bit counters (native shared-memory atomics; a piece cannot overflow
+// below 2^17 keys) and as one 64-bit counter for larger vocabularies.  Every pass over the keys reads four at a time.
 #include "common.cuh"
 
 namespace {
 
 constexpr int THREADS = 1024, BINS = 2048, MAX_V = 32768, WINDOW = 128;
+constexpr int PIECE_BITS = 14, PIECE_MAX_V = 1 << 17;   // 2^17 keys * 2^14 < 2^32
 
 __device__ __forceinline__ uint64_t mix64(uint64_t x) {
   x += 0x9E3779B97F4A7C15ull;
@@ -37,9 +40,13 @@ struct SamplerArgs {
 
 struct Scratch {
   uint32_t cnt[BINS];
-  unsigned long long mass[BINS];
+  union {
+    uint32_t piece[3][BINS];          // mass = piece[0] + (piece[1] << 14) + (piece[2] << 28)
+    unsigned long long mass[BINS];    // vocabularies of 2^17 entries and more
+  };
+  unsigned long long total;
   unsigned long long wtot[32], ctot[32];
-  float fred[32], fred2[32];
+  float fred[64];
   int ired[32];
   int sel_bin, sel_above_c;
   unsigned long long sel_above_w;
@@ -54,7 +61,6 @@ __device__ __forceinline__ float block_max(float v, float *red) {
   float r = red[threadIdx.x & 31];
   return warp_max(r);
 }
-__device__ __forceinline__ float block_min(float v, float *red) { return -block_max(-v, red); }
 __device__ __forceinline__ unsigned long long block_sum_u64(unsigned long long v, unsigned long long *red) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
@@ -66,54 +72,114 @@ __device__ __forceinline__ unsigned long long block_sum_u64(unsigned long long v
   for (int o = 16; o > 0; o >>= 1) r += __shfl_xor_sync(0xffffffffu, r, o);
   return r;
 }
-// exclusive prefix over the 1024 threads (thread order), 64-bit
-__device__ __forceinline__ unsigned long long block_excl_scan(unsigned long long v, unsigned long long *red) {
+// exclusive prefix over the 1024 threads (thread order) of a (64-bit, 32-bit) pair in one round
+__device__ __forceinline__ void block_excl_scan2(unsigned long long v, uint32_t c, unsigned long long *red, unsigned long long *red_c,
+                                                 unsigned long long &ex_v, uint32_t &ex_c) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  unsigned long long inc = v;
+  unsigned long long inc = v; uint32_t cin = c;
 #pragma unroll
-  for (int o = 1; o < 32; o <<= 1) { const unsigned long long t = __shfl_up_sync(0xffffffffu, inc, o); if (lane >= o) inc += t; }
+  for (int o = 1; o < 32; o <<= 1) {
+    const unsigned long long t = __shfl_up_sync(0xffffffffu, inc, o); const uint32_t u = __shfl_up_sync(0xffffffffu, cin, o);
+    if (lane >= o) { inc += t; cin += u; }
+  }
   __syncthreads();
-  if (lane == 31) red[warp] = inc;
+  if (lane == 31) { red[warp] = inc; red_c[warp] = cin; }
   __syncthreads();
-  unsigned long long w = red[lane], winc = w;
+  unsigned long long w = red[lane], winc = w; uint32_t wc = (uint32_t)red_c[lane], wcinc = wc;
 #pragma unroll
-  for (int o = 1; o < 32; o <<= 1) { const unsigned long long t = __shfl_up_sync(0xffffffffu, winc, o); if (lane >= o) winc += t; }
-  const unsigned long long wex = __shfl_sync(0xffffffffu, winc - w, warp);
-  return wex + inc - v;
+  for (int o = 1; o < 32; o <<= 1) {
+    const unsigned long long t = __shfl_up_sync(0xffffffffu, winc, o); const uint32_t u = __shfl_up_sync(0xffffffffu, wcinc, o);
+    if (lane >= o) { winc += t; wcinc += u; }
+  }
+  ex_v = __shfl_sync(0xffffffffu, winc - w, warp) + inc - v;
+  ex_c = __shfl_sync(0xffffffffu, wcinc - wc, warp) + cin - c;
+}
+// (max, min) over the block in one round; red holds 64 floats
+__device__ __forceinline__ void block_max_min(float &mx, float &mn, float *red) {
+  mx = warp_max(mx); mn = -warp_max(-mn);
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) { red[threadIdx.x >> 5] = mx; red[32 + (threadIdx.x >> 5)] = mn; }
+  __syncthreads();
+  mx = warp_max(red[threadIdx.x & 31]); mn = -warp_max(-red[32 + (threadIdx.x & 31)]);
+}
+
+// Calls f(x, index) for every key, four keys per load when the array allows it.
+template <class F>
+__device__ __forceinline__ void for_keys(const float *keys, int V, F f) {
+  const int tid = threadIdx.x;
+  if (((uintptr_t)keys & 15) == 0) {
+    const int V4 = V >> 2;
+    for (int i = tid; i < V4; i += THREADS) {
+      const float4 x = reinterpret_cast<const float4 *>(keys)[i];
+      f(x.x, 4 * i); f(x.y, 4 * i + 1); f(x.z, 4 * i + 2); f(x.w, 4 * i + 3);
+    }
+    for (int i = (V4 << 2) + tid; i < V; i += THREADS) f(keys[i], i);
+  } else {
+    for (int i = tid; i < V; i += THREADS) f(keys[i], i);
+  }
 }
 
 __device__ __forceinline__ unsigned long long qmass(float x, float mx) { return (unsigned long long)(__expf(x - mx) * 1099511627776.0f); }
 
-// Walk the finite keys >= floor_v from the largest down, adding 1 per key (BY_COUNT) or its fixed-point softmax
-// numerator; find the value v* at which the running total first exceeds `target`.  above_c / above_w are the count and
-// weight of the keys strictly greater than v*.  Returns false when the total never exceeds the target.
-template <bool BY_COUNT>
-__device__ bool select_desc(const float *keys, int V, float floor_v, float mx, unsigned long long target, float &vstar,
-                            int &above_c, unsigned long long &above_w, Scratch *s) {
+// Walk the finite keys in [lo, mx] from the largest down, adding 1 per key (BY_COUNT) or its fixed-point softmax
+// numerator; find the value v* at which the running total first exceeds the target: `target` itself when BY_COUNT,
+// else frac * (total mass of the keys in range).  above_c is the count of the keys strictly greater than v*.
+// `lo` must be the smallest key of the range.  Returns false when the total never exceeds the target.
+// WIDE: 64-bit bin counters (any vocabulary size) instead of three 32-bit pieces.
+template <bool BY_COUNT, bool WIDE>
+__device__ bool select_desc(const float *keys, int V, float lo, float mx, unsigned long long target, double frac, float &vstar,
+                            int &above_c, Scratch *s) {
   const int tid = threadIdx.x;
-  float lo_l = INFINITY;
-  for (int i = tid; i < V; i += THREADS) { const float x = keys[i]; if (x >= floor_v && x > -INFINITY) lo_l = fminf(lo_l, x); }
-  float lo = block_min(lo_l, s->fred), hi = mx;
-  above_c = 0; above_w = 0;
-  if (!(lo <= hi)) return false;                       // no finite key at or above the floor
+  float hi = mx;
+  above_c = 0;
+  unsigned long long above_w = 0;
+  if (!(lo <= hi)) return false;                       // no finite key in range
   for (int iter = 0; iter < 8; ++iter) {
     const float scale = hi > lo ? (float)(BINS - 1) / (hi - lo) : 0.f;
-    s->cnt[tid] = 0; s->cnt[tid + THREADS] = 0; s->mass[tid] = 0; s->mass[tid + THREADS] = 0;
+    s->cnt[tid] = 0; s->cnt[tid + THREADS] = 0;
+    if (!BY_COUNT) {
+      if (WIDE) { s->mass[tid] = 0; s->mass[tid + THREADS] = 0; }
+      else {
+#pragma unroll
+        for (int k = 0; k < 3; ++k) { s->piece[k][tid] = 0; s->piece[k][tid + THREADS] = 0; }
+      }
+    }
     if (tid == 0) s->sel_bin = -1;
     __syncthreads();
-    for (int i = tid; i < V; i += THREADS) {
-      const float x = keys[i];
+    for_keys(keys, V, [&](float x, int) {
       if (x >= lo && x <= hi) {
         const int bin = min(BINS - 1, (int)((hi - x) * scale));
         atomicAdd(&s->cnt[bin], 1u);
-        if (!BY_COUNT) atomicAdd(&s->mass[bin], qmass(x, mx));
+        if (!BY_COUNT) {
+          const unsigned long long q = qmass(x, mx);
+          if (WIDE) atomicAdd(&s->mass[bin], q);
+          else {
+            const uint32_t q0 = (uint32_t)q & ((1u << PIECE_BITS) - 1), q1 = (uint32_t)(q >> PIECE_BITS) & ((1u << PIECE_BITS) - 1),
+                           q2 = (uint32_t)(q >> (2 * PIECE_BITS));
+            if (q0) atomicAdd(&s->piece[0][bin], q0);
+            if (q1) atomicAdd(&s->piece[1][bin], q1);
+            if (q2) atomicAdd(&s->piece[2][bin], q2);
+          }
+        }
       }
-    }
+    });
     __syncthreads();
-    const unsigned long long c0 = s->cnt[2 * tid], c1 = s->cnt[2 * tid + 1];
-    const unsigned long long w0 = BY_COUNT ? c0 : s->mass[2 * tid], w1 = BY_COUNT ? c1 : s->mass[2 * tid + 1];
-    const unsigned long long ex_w = block_excl_scan(w0 + w1, s->wtot);
-    const unsigned long long ex_c = BY_COUNT ? ex_w : block_excl_scan(c0 + c1, s->ctot);
+    auto bin_mass = [&](int bin) -> unsigned long long {
+      if (BY_COUNT) return s->cnt[bin];
+      if (WIDE) return s->mass[bin];
+      return (unsigned long long)s->piece[0][bin] + ((unsigned long long)s->piece[1][bin] << PIECE_BITS) +
+             ((unsigned long long)s->piece[2][bin] << (2 * PIECE_BITS));
+    };
+    const uint32_t c0 = s->cnt[2 * tid], c1 = s->cnt[2 * tid + 1];
+    const unsigned long long w0 = bin_mass(2 * tid), w1 = bin_mass(2 * tid + 1);
+    unsigned long long ex_w; uint32_t ex_c;
+    block_excl_scan2(w0 + w1, c0 + c1, s->wtot, s->ctot, ex_w, ex_c);
+    if (!BY_COUNT && iter == 0) {
+      // the first histogram holds every key of the range: its total is the softmax denominator
+      if (tid == THREADS - 1) s->total = ex_w + w0 + w1;
+      __syncthreads();
+      target = (unsigned long long)(frac * (double)s->total);
+    }
     const unsigned long long base = above_w + ex_w;
     if (base <= target && target < base + w0) { s->sel_bin = 2 * tid; s->sel_above_w = base; s->sel_above_c = above_c + (int)ex_c; }
     else if (base + w0 <= target && target < base + w0 + w1) { s->sel_bin = 2 * tid + 1; s->sel_above_w = base + w0; s->sel_above_c = above_c + (int)(ex_c + c0); }
@@ -122,11 +188,10 @@ __device__ bool select_desc(const float *keys, int V, float floor_v, float mx, u
     if (sel < 0) return false;
     above_w = s->sel_above_w; above_c = s->sel_above_c;
     float nlo = INFINITY, nhi = -INFINITY;
-    for (int i = tid; i < V; i += THREADS) {
-      const float x = keys[i];
+    for_keys(keys, V, [&](float x, int) {
       if (x >= lo && x <= hi && min(BINS - 1, (int)((hi - x) * scale)) == sel) { nlo = fminf(nlo, x); nhi = fmaxf(nhi, x); }
-    }
-    nlo = block_min(nlo, s->fred); nhi = block_max(nhi, s->fred2);
+    });
+    block_max_min(nhi, nlo, s->fred);
     hi = nhi; lo = nlo;
     if (hi == lo) break;
   }
@@ -141,13 +206,25 @@ sample_kernel(const T *__restrict__ logits, int32_t *history, int32_t *__restric
   pdl_launch_dependents();
   pdl_wait();
   if (a.pos_dev) { a.hist_len = *a.pos_dev + 1; a.step = (uint64_t)a.hist_len; }
-  extern __shared__ float smem_keys[];
+  extern __shared__ __align__(16) float smem_keys[];
   float *keys = a.gkeys ? a.gkeys + (size_t)blockIdx.x * a.V : smem_keys;      // V penalised logits
   __shared__ Scratch sc;
   __shared__ int recent[WINDOW];
   const int b = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const T *row = logits + (size_t)b * a.V;
-  for (int v = tid; v < a.V; v += THREADS) keys[v] = to_f(row[v]);
+  if (sizeof(T) == 2 && (((uintptr_t)row | (uintptr_t)keys) & 15) == 0) {       // eight bf16 logits per load
+    const int V8 = a.V >> 3;
+    for (int i = tid; i < V8; i += THREADS) {
+      const uint4 x = reinterpret_cast<const uint4 *>(row)[i];
+      const float2 f0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&x.x)), f1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&x.y)),
+                   f2 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&x.z)), f3 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&x.w));
+      reinterpret_cast<float4 *>(keys)[2 * i] = make_float4(f0.x, f0.y, f1.x, f1.y);
+      reinterpret_cast<float4 *>(keys)[2 * i + 1] = make_float4(f2.x, f2.y, f3.x, f3.y);
+    }
+    for (int v = (V8 << 3) + tid; v < a.V; v += THREADS) keys[v] = to_f(row[v]);
+  } else {
+    for (int v = tid; v < a.V; v += THREADS) keys[v] = to_f(row[v]);
+  }
   const int n_hist = a.penalty != 1.0f ? min(a.hist_len, WINDOW) : 0;
   if (tid < n_hist) recent[tid] = history[(size_t)b * a.hist_ld + a.hist_len - n_hist + tid];
   __syncthreads();
@@ -159,28 +236,29 @@ sample_kernel(const T *__restrict__ logits, int32_t *history, int32_t *__restric
     if (!skip) { const float x = keys[id]; keys[id] = (x > 0.f ? x / a.penalty : x * a.penalty) - (a.penalty - 1.0f) * 35.0f; }
   }
   __syncthreads();
-  float mx_l = -INFINITY;
-  for (int v = tid; v < a.V; v += THREADS) mx_l = fmaxf(mx_l, keys[v]);
-  const float mx = block_max(mx_l, sc.fred);
+  float mx = -INFINITY, mn = INFINITY;               // largest key, smallest finite key
+  for_keys(keys, a.V, [&](float x, int) { mx = fmaxf(mx, x); if (x > -INFINITY) mn = fminf(mn, x); });
+  block_max_min(mx, mn, sc.fred);
 
   float thr = -INFINITY;
   const bool want_filters = a.temperature > 0.f || out_threshold != nullptr || out_kept != nullptr;
   if (want_filters) {
-    int above_c; unsigned long long above_w; float vstar;
+    int above_c; float vstar;
     if (a.top_k > 0 && a.top_k < a.V) {
-      if (select_desc<true>(keys, a.V, -INFINITY, mx, (unsigned long long)(a.top_k - 1), vstar, above_c, above_w, &sc)) thr = vstar;
+      if (select_desc<true, false>(keys, a.V, mn, mx, (unsigned long long)(a.top_k - 1), 0.0, vstar, above_c, &sc)) thr = vstar;
     }
     if (a.top_p < 1.0f) {
-      unsigned long long z_l = 0;
-      for (int v = tid; v < a.V; v += THREADS) { const float x = keys[v]; if (x >= thr && x > -INFINITY) z_l += qmass(x, mx); }
-      const unsigned long long Z = block_sum_u64(z_l, sc.wtot);
-      const unsigned long long target = (unsigned long long)((double)a.top_p * (double)Z);
-      if (select_desc<false>(keys, a.V, thr, mx, target, vstar, above_c, above_w, &sc)) {
+      // the range starts at the smallest kept key: the top-k threshold is itself a key
+      const float lo = thr > -INFINITY ? thr : mn;
+      const bool found = a.V < PIECE_MAX_V ? select_desc<false, false>(keys, a.V, lo, mx, 0ull, (double)a.top_p, vstar, above_c, &sc)
+                                           : select_desc<false, true>(keys, a.V, lo, mx, 0ull, (double)a.top_p, vstar, above_c, &sc);
+      if (found) {
         float cut = vstar;
-        if (above_c == 0 && qmass(mx, mx) > target) {
-          // the top token alone crosses p: the reference still keeps the second entry of the sorted order
+        if (above_c == 0 && vstar == mx) {
+          // the crossing happens at the largest value.  If one top token alone crosses p, the reference still keeps the
+          // second entry of the sorted order; if several share the maximum, the second entry is one of them.
           int n_top = 0; float second_l = -INFINITY;
-          for (int v = tid; v < a.V; v += THREADS) { const float x = keys[v]; if (x == mx) ++n_top; else second_l = fmaxf(second_l, x); }
+          for_keys(keys, a.V, [&](float x, int) { if (x == mx) ++n_top; else second_l = fmaxf(second_l, x); });
           const unsigned long long n_max = block_sum_u64((unsigned long long)n_top, sc.ctot);
           const float second = block_max(second_l, sc.fred);
           cut = n_max >= 2 ? mx : second;

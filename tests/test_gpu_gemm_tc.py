@@ -94,6 +94,105 @@ def test_few_row_weight_streaming_kernel(ctx, M, N, K):
     assert rel(out32, tile) < 1e-5
 
 
+def _few_row_hook(ctx):
+    f = ctx.lib.b200_internal_few_row_gemm
+    vp, i, z, fl = bridge._vp, bridge._i, bridge.C.c_size_t, bridge.C.c_float
+    f.argtypes = [vp, vp, vp, vp, z, z, z, vp, vp, vp, vp, vp, i, fl, i, vp, vp, i, i, i]
+    f.restype = i
+    return f
+
+
+def _produce(ctx, A, W, res, wn, M, N, K):
+    """Producer half on the GPU: h = res + A W, xw = h * wn, row sums (2^-32 fixed point, 64-bit; two fp32 words each here)."""
+    f = _few_row_hook(ctx)
+    h, xw = ctx.empty((M, N), "bf16"), ctx.empty((M, N), "bf16")
+    stats = ctx.array(np.zeros((M, 2, 2), np.float32))
+    ctx._check(f(ctx.h, ctx.array(A, "bf16").ptr, ctx.array(W, "bf16").ptr, h.ptr, M, N, K, ctx.array(res, "bf16").ptr,
+                 ctx.array(wn, "bf16").ptr, xw.ptr, stats.ptr, None, 0, 0.0, 0, None, None, 0, 0, 0))
+    return h, xw, stats
+
+
+def _sums(stats):
+    return stats.download().view(np.uint64).reshape(-1, 2).astype(np.float64) / 2.0 ** 32
+
+
+@pytest.mark.parametrize("M", [1, 5, 32, 64])
+@pytest.mark.parametrize("N,K,N2,double", [(2048, 2048, 3072, 1), (2048, 5632, 32000, 0), (128, 256, 104, 1), (72, 64, 72, 0), (2048, 2048, 2048, 0)])
+def test_few_row_kernel_residual_and_split_normalisation(ctx, M, N, K, N2, double):
+    """Decode epilogues of the few-row kernel.  Producer: h = residual + A W, h * w_norm and the rows' sums of squares per
+    row.  Consumer: rstd * ((h * w_norm) W2), with the attention's second unit norm when `double` (RMSNorm forward of
+    cpp/src/RMSNorm.cpp applied twice) -- against numpy in float64 with the same bf16 roundings of the stored tensors."""
+    eps = 1e-5
+    A, W = _ab(M, N, K, False, False, std_b=0.05)
+    res = synth.bf16_round(synth.normal(SEED, f"res{M}{N}", (M, N)) * (1.0 + np.arange(M, dtype=np.float32)[:, None] / 7.0))
+    wn = synth.bf16_round(1.0 + 0.2 * synth.normal(SEED, f"wn{N}", (N,)))
+    W2 = synth.bf16_round(synth.normal(SEED, f"W2{N}{N2}", (N, N2), 0.05))
+    h_dev, xw_dev, stats_dev = _produce(ctx, A, W, res, wn, M, N, K)
+    h, xw, stats = h_dev.download(), xw_dev.download(), _sums(stats_dev)
+    exp_h = _ref(A, W, False, False) + res
+    assert rel(h, exp_h) < 4e-3
+    np.testing.assert_array_equal(xw, synth.bf16_round(h * wn))                       # from the values as stored
+    hs = h.astype(np.float64)
+    np.testing.assert_allclose(stats[:, 0], (hs * hs).sum(-1), rtol=1e-5)
+    np.testing.assert_allclose(stats[:, 1], (xw.astype(np.float64) ** 2).sum(-1), rtol=1e-5)
+    # consumer
+    y = xw.astype(np.float64) / np.sqrt((hs * hs).mean(-1, keepdims=True) + eps)
+    if double:
+        y = y / np.sqrt((y * y).mean(-1, keepdims=True) + eps)
+    exp = y @ W2.astype(np.float64)
+    out = ctx.empty((M, N2), "bf16")
+    ctx._check(_few_row_hook(ctx)(ctx.h, xw_dev.ptr, ctx.array(W2, "bf16").ptr, out.ptr, M, N2, N, None, None, None, None,
+                                  stats_dev.ptr, double, eps, 0, None, None, 0, 0, 0))
+    got = out.download()
+    assert rel(got, exp) < 5e-3, rel(got, exp)
+    assert np.abs(got - exp).max() < 2e-2 * np.abs(exp).max()
+
+
+@pytest.mark.parametrize("M,I,H", [(3, 5632, 2048), (32, 5632, 2048), (64, 704, 256), (17, 64, 128)])
+def test_few_row_kernel_swiglu_on_a_normalised_row(ctx, M, I, H):
+    eps = 1e-5
+    A, W = _ab(M, H, 192, False, False, std_b=0.3)
+    res = synth.bf16_round(synth.normal(SEED, f"sres{M}{H}", (M, H), 2.0))
+    wn = synth.bf16_round(1.0 + 0.2 * synth.normal(SEED, f"swn{H}", (H,)))
+    Wgu = synth.bf16_round(synth.normal(SEED, f"sW{H}{I}", (H, 2 * I), 0.03))
+    h_dev, xw_dev, stats_dev = _produce(ctx, A, W, res, wn, M, H, 192)
+    hs, xw = h_dev.download().astype(np.float64), xw_dev.download().astype(np.float64)
+    gu = (xw / np.sqrt((hs * hs).mean(-1, keepdims=True) + eps)) @ Wgu.astype(np.float64)
+    g, u = gu[:, :I], gu[:, I:]
+    exp = g / (1.0 + np.exp(-g)) * u
+    out = ctx.empty((M, I), "bf16")
+    ctx._check(_few_row_hook(ctx)(ctx.h, xw_dev.ptr, ctx.array(Wgu, "bf16").ptr, out.ptr, M, 2 * I, H, None, None, None, None,
+                                  stats_dev.ptr, 0, eps, I, None, None, 0, 0, 0))
+    assert rel(out.download(), exp) < 8e-3
+
+
+@pytest.mark.parametrize("M,hd,pos", [(4, 128, 37), (32, 64, 5), (7, 6, 3)])
+def test_few_row_kernel_rotary_epilogue_on_a_normalised_row(ctx, M, hd, pos):
+    """Q and K columns rotated at one position (RoPE::forward, cpp/src/Positional.cpp: interleaved pairs), V columns left alone."""
+    eps, H = 1e-5, 256
+    nq, nkv = 4, 2
+    N, cols = (nq + 2 * nkv) * hd, (nq + nkv) * hd
+    A, W = _ab(M, H, 128, False, False, std_b=0.3)
+    res = synth.bf16_round(synth.normal(SEED, f"rres{M}", (M, H)))
+    wn = synth.bf16_round(1.0 + 0.2 * synth.normal(SEED, "rwn", (H,)))
+    Wqkv = synth.bf16_round(synth.normal(SEED, f"rW{N}", (H, N), 0.05))
+    h_dev, xw_dev, stats_dev = _produce(ctx, A, W, res, wn, M, H, 128)
+    hs, xw = h_dev.download().astype(np.float64), xw_dev.download().astype(np.float64)
+    half = hd // 2
+    ang = np.arange(64)[:, None] * (10000.0 ** (-np.arange(half) / half))[None, :]
+    cos_t, sin_t = np.cos(ang).astype(np.float32), np.sin(ang).astype(np.float32)
+    y = xw / np.sqrt((hs * hs).mean(-1, keepdims=True) + eps)
+    y = (y / np.sqrt((y * y).mean(-1, keepdims=True) + eps)) @ Wqkv.astype(np.float64)
+    exp = y.copy()
+    r = y[:, :cols].reshape(M, -1, half, 2)
+    c, s_ = cos_t[pos].astype(np.float64), sin_t[pos].astype(np.float64)
+    exp[:, :cols] = np.stack([r[..., 0] * c - r[..., 1] * s_, r[..., 0] * s_ + r[..., 1] * c], -1).reshape(M, cols)
+    out = ctx.empty((M, N), "bf16")
+    ctx._check(_few_row_hook(ctx)(ctx.h, xw_dev.ptr, ctx.array(Wqkv, "bf16").ptr, out.ptr, M, N, H, None, None, None, None,
+                                  stats_dev.ptr, 1, eps, 0, ctx.array(cos_t).ptr, ctx.array(sin_t).ptr, hd, cols, pos))
+    assert rel(out.download(), exp) < 6e-3
+
+
 PROJ = [("qkv", 2048, 3072), ("o", 2048, 2048), ("gate_up", 2048, 11264), ("down", 5632, 2048)]
 
 
