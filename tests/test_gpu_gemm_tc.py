@@ -64,6 +64,24 @@ def test_accumulate_into_fp32_c(ctx):
     assert rel(dc.download(), _ref(A, B, True, False) + C0) < 1e-5
 
 
+@pytest.mark.parametrize("M,N,K,acc", [(1024, 1280, 8192, False), (1000, 1300, 8200, False), (2048, 2048, 16384, False), (512, 2304, 12288, True)])
+def test_weight_gradient_shapes_whole_result(ctx, M, N, K, acc):
+    """Few tiles and a deep K (the weight-gradient form, fp32 result, split K where the tiles fill the GPU badly; partial
+    tiles are added with reductions): the whole result against the float64 product."""
+    A, B = _ab(M, N, K, True, False, std_b=0.05)
+    exp = _ref(A, B, True, False)
+    da, db = ctx.array(A, "bf16"), ctx.array(B, "bf16")
+    if acc:
+        C0 = synth.normal(SEED, "C0s", (M, N))
+        dc = ctx.array(C0)
+        ctx.gemm(da, db, M, N, K, True, False, C_acc=dc)
+        got, exp = dc.download(), exp + C0
+    else:
+        got = ctx.gemm(da, db, M, N, K, True, False, out_dtype="f32").download()
+    assert rel(got, exp) < 2.5e-5              # fp32 accumulation over up to 16384 products
+    assert np.abs(got - exp).max() < 2e-4 * np.abs(exp).max()
+
+
 def test_many_tiles_exercise_the_persistent_schedule(ctx):
     M, N, K = 128 * 21, 256 * 9, 320          # 189 tiles > 148 SMs, odd counts
     A, B = _ab(M, N, K, False, False)
