@@ -3,40 +3,17 @@
   Python generate loop, python/pipeline/inference/sampler.py:115-148) re-runs the full context per token;
 * the bf16 cache path reproduces the engine's own full-context forward (logits within 2e-2, same greedy ids);
 * the sampler's deterministic filters (repetition penalty, top-k, top-p) match a numpy restatement of
-  sampler.py:43-98 exactly (threshold and kept count); the random draw is pinned only by seed
-  self-consistency and by staying inside the kept set (the reference draws with MLX's RNG: unpinned)."""
+  sampler.py:43-98 exactly (threshold and kept count; the restatement itself is pinned in test_sampler_golden.py);
+  the random draw is pinned only by seed self-consistency and by staying inside the kept set (the reference draws
+  with MLX's RNG: unpinned)."""
 import numpy as np
 import pytest
 
 from gpu_util import BF16_TOL, bridge, ctx, rel, synth  # noqa: F401
 from oracle import oracle
+from sampler_rules import ref_filters
 
 pytestmark = pytest.mark.gpu
-
-
-# ---- numpy restatement of the reference sampler's filters -------------------------------------
-def ref_filters(logits, generated, penalty, top_k, top_p, whitespace=(), window=128):
-    lg = np.asarray(logits, np.float32).copy()
-    if penalty != 1.0 and len(generated):
-        seen = set(int(t) for t in generated[-window:]) - set(whitespace)
-        for t in seen:
-            v = lg[t]
-            lg[t] = np.float32((v / np.float32(penalty) if v > 0 else v * np.float32(penalty)) - np.float32((penalty - 1.0) * 35.0))
-    pen = lg.copy()
-    if top_k > 0:
-        thr = np.sort(lg)[-top_k]
-        lg = np.where(lg >= thr, lg, -np.inf).astype(np.float32)
-    if top_p < 1.0:
-        order = np.argsort(-lg, kind="stable")
-        s = lg[order]
-        p = np.exp(s - s[0], dtype=np.float32)
-        p = p / p.sum(dtype=np.float32)
-        cum = np.cumsum(p, dtype=np.float32)
-        idx = np.nonzero(cum > np.float32(top_p))[0]
-        if len(idx):
-            cutoff = max(1, int(idx[0]))
-            lg = np.where(lg >= s[cutoff], lg, -np.inf).astype(np.float32)
-    return pen, lg
 
 
 # 32000: the benchmark model; 100352: the vocabulary of the reference's own training configurations
@@ -173,6 +150,44 @@ def test_bf16_cache_decode_matches_full_context_forward(ctx, hd, nH, nKV):
         logits = model.decode_step(ctx.array(nxt, "i32"), B, P + t).download()
         ctxt = np.concatenate([ctxt, nxt[:, None]], 1)
     model.close()
+
+@pytest.mark.parametrize("B", [3, 40, 64])          # 32- and 64-row forms of the few-row projections
+def test_decode_step_with_norms_inside_the_projections_matches_the_separate_kernels(ctx, B, monkeypatch):
+    """By default the residual adds and RMS norms of a decode step ride in the few-row projections (the producer of the
+    residual stream leaves h * w_norm and the rows' sums of squares, the consumer scales by rstd).  The logits must agree
+    with the step that runs them as kernels of their own, and with the full-context forward, and take fewer launches."""
+    P, NEW = 24, 4
+    shape = dict(H=256, I=512, nH=4, nKV=2, hd=64, V=1024, L=3)
+    S = P + NEW
+    model = bridge.Model(ctx, bridge.Shape(B=B, S=S, **shape), "bf16", with_optimizer=False)
+    model.init_synthetic(11, 0.05)
+    prompt = synth.token_ids(11, "prompt", (B, P), shape["V"])
+
+    def run(folded, forced=None):
+        monkeypatch.setenv("B200_DECODE_FOLD_NORM", "1" if folded else "0")
+        model.decode_begin(B, S)
+        logits = model.prefill(ctx.array(prompt, "i32"), B, P).download()
+        out, ids = [], []
+        n0 = ctx.launch_count()
+        for t in range(NEW):
+            nxt = logits.argmax(-1).astype(np.int32) if forced is None else forced[t]
+            ids.append(nxt)
+            logits = model.decode_step(ctx.array(nxt, "i32"), B, P + t).download()
+            out.append(logits)
+        return out, ids, ctx.launch_count() - n0
+
+    try:
+        fold_out, ids, n_fold = run(True)
+        sep_out, _, n_sep = run(False, ids)
+        for t, (a, b) in enumerate(zip(fold_out, sep_out)):
+            assert rel(a, b) < 1e-2, (t, rel(a, b))
+        ctxt = np.concatenate([prompt] + [i[:, None] for i in ids], 1)
+        full = model.forward(ctx.array(ctxt, "i32"), B, ctxt.shape[1]).download().reshape(B, ctxt.shape[1], -1)[:, -1]
+        assert rel(fold_out[-1], full) < BF16_TOL
+        assert n_fold == n_sep - NEW * 2 * shape["L"]           # two norm kernels fewer per layer and step
+    finally:
+        model.close()
+
 
 @pytest.mark.parametrize("nH,nKV,P", [(4, 2, 150), (8, 2, 700), (8, 1, 130), (4, 2, 1100)])   # groups of 2, 4, 8, 2; 2, 6, 2 and 9 cache tiles
 def test_tensor_core_decode_attention(ctx, nH, nKV, P, monkeypatch):
