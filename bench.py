@@ -45,7 +45,7 @@ METRIC, UNIT = "train_tokens_per_sec", "tokens/s"
 # DRAM traffic of the GEMM kernels, average per launch over one training step (ncu dram__bytes_read.sum +
 # dram__bytes_write.sum of the 15 GEMM launches of a 1-layer step, the 12 layer GEMMs weighted x28), and the
 # algorithmic bytes (each operand read once, the result written once) over the same launches.
-GEMM_DRAM_BYTES_PER_LAUNCH = 438025669
+GEMM_DRAM_BYTES_PER_LAUNCH = 442382891
 GEMM_ALGO_BYTES_PER_LAUNCH = 301730064
 GEMM_TRAFFIC_SOURCE = "profiles/gemm_dram_traffic_train_step.md (ncu, 1-layer step scaled by launch counts to 28 layers)"
 

@@ -504,7 +504,9 @@ int launch_variant(b200_ctx *ctx, const CUtensorMap &ma, const CUtensorMap &mb, 
   static const bool bulk_wanted = [] { const char *e = getenv("B200_GEMM_BULK_STORE"); return !(e && e[0] == '0'); }();
   CUtensorMap mc = ma, mact = ma;    // placeholders when the route is off (never dereferenced)
   int bulk = 0;
-  if (bulk_wanted && C && (uintptr_t)C % 16 == 0 && (ldc * sizeof(TO)) % 16 == 0) {
+  // (not for the vocabulary-sized products: with bulk stores the three vocabulary GEMMs of a step read 1.70 / 2.94 / 4.03 GB
+  // from DRAM, with vector stores 1.17-1.36 / 2.13-2.41 / 2.80-3.45 GB over two captures, at the same speed)
+  if (bulk_wanted && C && (uintptr_t)C % 16 == 0 && (ldc * sizeof(TO)) % 16 == 0 && N <= 16384 && K <= 16384) {
     bulk = tc_make_map_store_2d(&mc, C, (int)sizeof(TO), (uint64_t)N, (uint64_t)M, ldc * sizeof(TO)) == 0;
     if (bulk && epi.swiglu_I > 0)
       bulk = tc_make_map_store_2d(&mact, epi.act_out, 2, (uint64_t)epi.swiglu_I, (uint64_t)M, (uint64_t)epi.ld_act * 2) == 0;
