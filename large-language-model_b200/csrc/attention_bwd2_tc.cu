@@ -86,7 +86,7 @@ __device__ __forceinline__ void load_subtile(uint8_t *dst, const CUtensorMap *ma
 __global__ void __launch_bounds__(BWD2_THREADS, 1)
 attn_bwd2_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                     const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
-                    float *__restrict__ dQacc, const float *__restrict__ lse2,
+                    float *__restrict__ dQacc, long long dq_tile_stride, const float *__restrict__ lse2,
                     const float *__restrict__ Dsum, bf16 *__restrict__ dK, bf16 *__restrict__ dV, int nH, int nKV, int S,
                     long long dk_b, long long dk_h, long long dk_s, long long dv_b, long long dv_h, long long dv_s,
                     float scale, int *status, const float *__restrict__ rope_cos, const float *__restrict__ rope_sin) {
@@ -234,11 +234,17 @@ attn_bwd2_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
       __syncwarp();
       if (lane == 0) tc::mbar_arrive(&sh->dq_consumed[s]);        // the columns may take dP^T of step st+2
       const int q0 = (2 * j + sub) * SQ, nq = min(SQ, S - q0);
-      float *dst = dQacc + (((long long)b * nH + head) * S + q0) * HD + quarter * 32 + lane;
+      float *dst = dQacc + (long long)j * dq_tile_stride + (((long long)b * nH + head) * S + q0) * HD + quarter * 32 + lane;
       if (++sub == per_head) { sub = 0; ++head; }
+      if (dq_tile_stride) {           // bit-reproducible form: this key tile's own slice; the store kernel adds the slices in order
 #pragma unroll
-      for (int q = 0; q < SQ; ++q)
-        if (q < nq) asm volatile("red.global.add.f32 [%0], %1;" ::"l"(dst + (size_t)q * HD), "f"(__uint_as_float(v[q])) : "memory");
+        for (int q = 0; q < SQ; ++q)
+          if (q < nq) dst[(size_t)q * HD] = __uint_as_float(v[q]);
+      } else {
+#pragma unroll
+        for (int q = 0; q < SQ; ++q)
+          if (q < nq) asm volatile("red.global.add.f32 [%0], %1;" ::"l"(dst + (size_t)q * HD), "f"(__uint_as_float(v[q])) : "memory");
+      }
     }
   } else {
     // ---- compute warps: two threads per key row (tensor-memory lane), 32 of the step's 64 queries each ----------
@@ -385,9 +391,10 @@ bool attn_bwd2_supported(size_t S, size_t hd) { return hd == 128 && S % 4 == 0 &
 
 // Dsum must hold rowsum(dO * O) and lse2 the log-sum-exp times log2(e) (attn_dsum_kernel of attention_bwd_tc.cu); dQ comes
 // out WITHOUT the softmax scale (the caller's store kernel multiplies it in); dQacc: the zeroed fp32 accumulator
-// [B*nH*S][128] that the caller afterwards turns into dQ rows.
+// [B*nH*S][128] that the caller afterwards turns into dQ rows.  dq_tile_stride > 0 (elements): key tile j writes its
+// contribution to the slice dQacc + j * dq_tile_stride instead of adding to one accumulator (queries from 128 j on).
 int attn_bwd2_tc_run(b200_ctx *ctx, const void *Q, const void *K, const void *V, const void *dO, const float *lse2, const float *Dsum,
-                     float *dQacc, void *dK, void *dV, size_t B, size_t nH, size_t nKV, size_t S, const AttnStrides &st,
+                     float *dQacc, long long dq_tile_stride, void *dK, void *dV, size_t B, size_t nH, size_t nKV, size_t S, const AttnStrides &st,
                      const AttnStrides &gst, const float *rope_cos, const float *rope_sin) {
   CUtensorMap mq, mk, mv, mdo;
   if (tc_make_map_4d(&mq, Q, HD, S, nH, B, (uint64_t)st.q_s * 2, (uint64_t)st.q_h * 2, (uint64_t)st.q_b * 2, 64, SQ) ||
@@ -399,7 +406,7 @@ int attn_bwd2_tc_run(b200_ctx *ctx, const void *Q, const void *K, const void *V,
   static bool attr = false;
   if (!attr) { B200_CUDA(ctx, cudaFuncSetAttribute(attn_bwd2_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)); attr = true; }
   dim3 grid((unsigned)(nKV * B), (unsigned)((S + TK - 1) / TK), 1);
-  B200_CUDA(ctx, launch_k(ctx, attn_bwd2_tc_kernel, grid, dim3(BWD2_THREADS), (size_t)smem, 0, mq, mk, mv, mdo, dQacc, lse2, Dsum, (bf16 *)dK, (bf16 *)dV, (int)nH,
+  B200_CUDA(ctx, launch_k(ctx, attn_bwd2_tc_kernel, grid, dim3(BWD2_THREADS), (size_t)smem, 0, mq, mk, mv, mdo, dQacc, dq_tile_stride, lse2, Dsum, (bf16 *)dK, (bf16 *)dV, (int)nH,
                           (int)nKV, (int)S, gst.k_b, gst.k_h, gst.k_s, gst.v_b, gst.v_h, gst.v_s, 1.0f / sqrtf((float)HD), ctx->dev_status, rope_cos, rope_sin));
   B200_LAUNCHED(ctx);
   return B200_OK;

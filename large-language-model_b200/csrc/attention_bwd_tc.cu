@@ -317,9 +317,11 @@ attn_dsum_kernel(const bf16 *__restrict__ O, const bf16 *__restrict__ dO, float 
   }
 }
 // fp32 [B,nH,S,hd] accumulator -> strided bf16 dQ
+// tile_stride > 0: acc holds one slice per 128-key tile (slice j covers the queries from 128 j on); they are added in order.
 __global__ void attn_dq_store_kernel(const float *__restrict__ acc, bf16 *__restrict__ dQ, int B, int nH, int S,
                                      int hd, long long q_b, long long q_h, long long q_s,
-                                     const float *__restrict__ rope_cos, const float *__restrict__ rope_sin, float mul) {
+                                     const float *__restrict__ rope_cos, const float *__restrict__ rope_sin, float mul,
+                                     long long tile_stride) {
   pdl_launch_dependents();
   pdl_wait();
   const size_t total = (size_t)B * nH * S * (hd / 8);
@@ -328,6 +330,12 @@ __global__ void attn_dq_store_kernel(const float *__restrict__ acc, bf16 *__rest
     const int s = (int)(r % S); r /= S;
     const int h = (int)(r % nH), b = (int)(r / nH);
     float4 x = *reinterpret_cast<const float4 *>(acc + idx * 8), y = *reinterpret_cast<const float4 *>(acc + idx * 8 + 4);
+    if (tile_stride) {
+      for (int t = 1; t <= s / TK; ++t) {
+        const float4 x2 = *reinterpret_cast<const float4 *>(acc + t * tile_stride + idx * 8), y2 = *reinterpret_cast<const float4 *>(acc + t * tile_stride + idx * 8 + 4);
+        x.x += x2.x; x.y += x2.y; x.z += x2.z; x.w += x2.w; y.x += y2.x; y.y += y2.y; y.z += y2.z; y.w += y2.w;
+      }
+    }
     x.x *= mul; x.y *= mul; x.z *= mul; x.w *= mul; y.x *= mul; y.y *= mul; y.z *= mul; y.w *= mul;   // 1, or the softmax scale
     if (rope_cos != nullptr) {   // gradient of the rotary embedding on dQ: inverse rotation at position s
       const float4 c = *reinterpret_cast<const float4 *>(rope_cos + (size_t)s * (hd / 2) + u * 4);
@@ -346,7 +354,7 @@ __global__ void attn_dq_store_kernel(const float *__restrict__ acc, bf16 *__rest
 
 bool attn_bwd2_supported(size_t S, size_t hd);
 int attn_bwd2_tc_run(b200_ctx *ctx, const void *Q, const void *K, const void *V, const void *dO, const float *lse2, const float *Dsum,
-                     float *dQacc, void *dK, void *dV, size_t B, size_t nH, size_t nKV, size_t S, const AttnStrides &st,
+                     float *dQacc, long long dq_tile_stride, void *dK, void *dV, size_t B, size_t nH, size_t nKV, size_t S, const AttnStrides &st,
                      const AttnStrides &gst, const float *rope_cos, const float *rope_sin);
 
 namespace {
@@ -357,10 +365,13 @@ int bwd_launch_t(b200_ctx *ctx, const void *Q, const void *K, const void *V, con
   const size_t rows = B * nH * S;
   // scratch: D [rows] fp32, dQ accumulator [rows, HD] fp32 (zeroed here, added to by TMA reduce)
   const size_t d_elems = ((rows + 63) / 64) * 64;
-  float *scr = (float *)b200_scratch(ctx, (2 * d_elems + rows * HD) * sizeof(float));
+  const bool second_form = HD == 128 && ctx->attn_bwd2 && attn_bwd2_supported(S, HD);
+  // bit-reproducible form (second form only): one dQ slice per key tile instead of one accumulator all tiles add to
+  const size_t dq_slices = (ctx->deterministic && second_form) ? (S + TK - 1) / TK : 1;
+  const long long dq_tile_stride = dq_slices > 1 ? (long long)(rows * HD) : 0;
+  float *scr = (float *)b200_scratch(ctx, (2 * d_elems + dq_slices * rows * HD) * sizeof(float));
   if (!scr) return B200_ERR_NOMEM;
   float *Dsum = scr, *lse2 = scr + d_elems, *dQacc = scr + 2 * d_elems;
-  const bool second_form = HD == 128 && ctx->attn_bwd2 && attn_bwd2_supported(S, HD);
   {
     size_t blocks = (rows + 63) / 64, cap = (size_t)ctx->sm_count * 16;      // 32 lane groups x 2 rows per block pass
     B200_CUDA(ctx, launch_k(ctx, attn_dsum_kernel<HD>, dim3((unsigned)(blocks < cap ? blocks : cap)), dim3(256), 0, 0, (const bf16 *)O, (const bf16 *)dO, Dsum,
@@ -368,7 +379,7 @@ int bwd_launch_t(b200_ctx *ctx, const void *Q, const void *K, const void *V, con
     B200_LAUNCHED(ctx);
   }
   if (second_form) {
-    int rc = attn_bwd2_tc_run(ctx, Q, K, V, dO, lse2, Dsum, dQacc, dK, dV, B, nH, nKV, S, st, gst, rope_cos, rope_sin);
+    int rc = attn_bwd2_tc_run(ctx, Q, K, V, dO, lse2, Dsum, dQacc, dq_tile_stride, dK, dV, B, nH, nKV, S, st, gst, rope_cos, rope_sin);
     if (rc != B200_OK) return rc;
   } else {
     CUtensorMap mq, mk, mv, mdo, mdq;
@@ -388,7 +399,7 @@ int bwd_launch_t(b200_ctx *ctx, const void *Q, const void *K, const void *V, con
   {
     size_t items = rows * (HD / 8), blocks = (items + 255) / 256, cap = (size_t)ctx->sm_count * 16;
     B200_CUDA(ctx, launch_k(ctx, attn_dq_store_kernel, dim3((unsigned)(blocks < cap ? blocks : cap)), dim3(256), 0, 0, (const float *)dQacc, (bf16 *)dQ, (int)B, (int)nH,
-                            (int)S, (int)HD, gst.q_b, gst.q_h, gst.q_s, rope_cos, rope_sin, second_form ? 1.0f / sqrtf((float)HD) : 1.0f));
+                            (int)S, (int)HD, gst.q_b, gst.q_h, gst.q_s, rope_cos, rope_sin, second_form ? 1.0f / sqrtf((float)HD) : 1.0f, dq_tile_stride));
     B200_LAUNCHED(ctx);
   }
   return B200_OK;

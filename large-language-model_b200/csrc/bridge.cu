@@ -83,6 +83,7 @@ extern "C" int b200_init(int device, b200_ctx **out) {
   // (it is a chain of microsecond kernels); for training steps it measured no gain on a power-capped B200
   // (152.5 vs 152.7 ms per step, same GPU), so plain stream order is the default there.
   ctx->pdl = getenv("B200_PDL") && getenv("B200_PDL")[0] == '1';
+  ctx->deterministic = getenv("B200_DETERMINISTIC") && getenv("B200_DETERMINISTIC")[0] == '1';
   cudaMemsetAsync(ctx->dev_status, 0, sizeof(int), ctx->stream);
   cudaStreamSynchronize(ctx->stream);
   *out = ctx;
@@ -146,6 +147,12 @@ extern "C" int b200_internal_set_attn_bwd2(b200_ctx *ctx, int enable) {
 extern "C" int b200_internal_set_attn_fwd2(b200_ctx *ctx, int enable) {
   if (!ctx) return B200_ERR_INVALID;
   ctx->attn_fwd2 = enable != 0;
+  return B200_OK;
+}
+// Test hook: bit-reproducible gradient paths on or off (B200_DETERMINISTIC sets the initial value).
+extern "C" int b200_internal_set_deterministic(b200_ctx *ctx, int enable) {
+  if (!ctx) return B200_ERR_INVALID;
+  ctx->deterministic = enable != 0;
   return B200_OK;
 }
 // Same kind of hook: 0 sends few-row GEMMs through the general tile kernel instead of the weight-streaming one.

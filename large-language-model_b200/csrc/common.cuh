@@ -36,6 +36,10 @@ struct b200_ctx {
   // decode step: kernels are launched with programmatic stream serialization, so a kernel's launch and set-up overlap the
   // tail of the one before it; each such kernel waits (griddepcontrol.wait) before it touches anything a predecessor wrote
   bool pdl = false;
+  // Bit-reproducible gradients (B200_DETERMINISTIC=1; for chasing a divergence between runs or ranks): no split-K in the
+  // GEMMs, attention backward writes dQ per key tile and adds the tiles in order, the embedding gradient is added token
+  // by token.  The default paths add fp32 values with device atomics whose order varies from run to run.
+  bool deterministic = false;
   bool time_gemm = false;
   struct Timed { cudaEvent_t start, stop; double flops; };
   std::vector<Timed> timed;

@@ -609,6 +609,17 @@ __global__ void embedding_bwd_kernel(const uint32_t *__restrict__ ids, const T *
     for (size_t c = threadIdx.x; c < H; c += blockDim.x) atomicAdd(gtable + (size_t)id * H + c, to_f(gh[t * H + c]));
   }
 }
+// Bit-reproducible form: one thread per column walks the tokens in order.
+template <class T>
+__global__ void embedding_bwd_ordered_kernel(const uint32_t *__restrict__ ids, const T *__restrict__ gh,
+                                             float *gtable, size_t tokens, size_t H, size_t V) {
+  const size_t c = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= H) return;
+  for (size_t t = 0; t < tokens; ++t) {
+    const uint32_t id = ids[t];
+    if (id < V) gtable[(size_t)id * H + c] += to_f(gh[t * H + c]);
+  }
+}
 extern "C" int b200_embedding_forward(b200_ctx *ctx, const uint32_t *ids, const void *table, void *out,
                                       size_t tokens, size_t H, size_t V, b200_dtype dt) {
   B200_REQUIRE(ctx, ids && table && out && H && V, "embedding_forward: bad arguments");
@@ -624,6 +635,13 @@ extern "C" int b200_embedding_backward(b200_ctx *ctx, const uint32_t *ids, const
   B200_REQUIRE(ctx, ids && gh && gtable && H && V, "embedding_backward: bad arguments");
   B200_CUDA(ctx, cudaMemsetAsync(gtable, 0, V * H * sizeof(float), ctx->stream));   // reference zero-fills first (Transformer.cpp:528)
   if (!tokens) return B200_OK;
+  if (ctx->deterministic) {
+    const unsigned blocks = (unsigned)((H + 63) / 64);
+    if (dt == B200_BF16) embedding_bwd_ordered_kernel<bf16><<<blocks, 64, 0, ctx->stream>>>(ids, (const bf16 *)gh, gtable, tokens, H, V);
+    else embedding_bwd_ordered_kernel<float><<<blocks, 64, 0, ctx->stream>>>(ids, (const float *)gh, gtable, tokens, H, V);
+    B200_LAUNCHED(ctx);
+    return B200_OK;
+  }
   int grid = (int)(tokens < (size_t)ctx->sm_count * 16 ? tokens : (size_t)ctx->sm_count * 16);
   if (dt == B200_BF16) embedding_bwd_kernel<bf16><<<grid, 256, 0, ctx->stream>>>(ids, (const bf16 *)gh, gtable, tokens, H, V);
   else embedding_bwd_kernel<float><<<grid, 256, 0, ctx->stream>>>(ids, (const float *)gh, gtable, tokens, H, V);

@@ -539,6 +539,7 @@ int launch_variant(b200_ctx *ctx, const CUtensorMap &ma, const CUtensorMap &mb, 
     for (int s = 2; s <= 4; ++s)
       if (num_kb / s >= 16 && eff(s) > best + 0.08) { best = eff(s); splits = s; }
   }
+  if (ctx->deterministic) splits = 1;          // partial tiles would be added in an order that varies
   const int items = pairs * splits;
   const int clusters = items < max_clusters ? items : max_clusters;
   cfg.gridDim = dim3(2 * clusters);

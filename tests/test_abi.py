@@ -35,7 +35,7 @@ def test_kernel_choice_hooks_of_the_gpu_tests_exist(lib):
     """The GPU parity tests run both forms of a kernel through these undeclared A/B hooks."""
     for name in ("b200_internal_set_gemm_2cta", "b200_internal_set_gemm_skinny", "b200_internal_set_attn_fwd2",
                  "b200_internal_set_attn_bwd2", "b200_internal_set_attn_decode_tc", "b200_internal_wait_probe",
-                 "b200_internal_dp_inject_failure", "b200_internal_dp_comm_failed", "b200_internal_few_row_gemm"):
+                 "b200_internal_dp_inject_failure", "b200_internal_dp_comm_failed", "b200_internal_few_row_gemm", "b200_internal_set_deterministic"):
         assert hasattr(lib, name), name
 
 

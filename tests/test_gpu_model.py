@@ -151,6 +151,34 @@ def test_bf16_model_against_fp32_checker(ctx, orc, cfgd):
     model.close()
 
 
+def test_bit_reproducible_gradient_mode(ctx, orc):
+    """With the reproducible paths on (no split-K, attention backward writes dQ per key tile and adds the tiles in order,
+    the embedding gradient is added token by token) two runs give bit-identical gradients; they agree with the
+    default paths, whose atomics add the same terms in a varying order, and with the checker."""
+    cfg = oracle.Config(B=2, S=512, H=256, I=512, nH=2, nKV=1, hd=128, V=1024, L=2)     # 4 key tiles; wgrads with a 1024-deep K
+    params, tok, tgt = inputs(cfg, seed=13)
+    tok[:, ::3] = tok[:, :1]                                   # repeated ids: several tokens add into one embedding row
+    params = synth.bf16_round(params)
+    _, grads_ref, _ = orc.model_loss_and_grads(cfg, tok, tgt, params, want_logits=True)
+    model = bridge.Model(ctx, cfg, "bf16")
+    model.load_params(params)
+    ctx.lib.b200_internal_set_deterministic.argtypes = [bridge._vp, bridge._i]
+    try:
+        ctx.lib.b200_internal_set_deterministic(ctx.h, 1)
+        loss_a = model.loss_and_grads_host(tok, tgt); ga = model.read_grads()
+        loss_b = model.loss_and_grads_host(tok, tgt); gb = model.read_grads()
+        assert loss_a == loss_b
+        np.testing.assert_array_equal(ga, gb)
+        ctx.lib.b200_internal_set_deterministic(ctx.h, 0)
+        loss_c = model.loss_and_grads_host(tok, tgt); gc = model.read_grads()
+        assert loss_c == loss_a and rel(gc, ga) < 1e-5
+        nz = grads_ref != 0
+        assert rel(ga[nz & (ga != 0)], grads_ref[nz & (ga != 0)]) < BF16_TOL
+    finally:
+        ctx.lib.b200_internal_set_deterministic(ctx.h, 0)
+        model.close()
+
+
 def test_adamw_training_steps_match_the_checker_and_reduce_the_loss(ctx, orc):
     cfg = oracle.Config(B=2, S=16, H=64, I=96, nH=4, nKV=2, hd=16, V=96, L=2)
     params, tok, tgt = inputs(cfg, seed=3)
