@@ -44,6 +44,27 @@ def test_sampler_filters_match_the_reference_rules(ctx, dtype, top_k, top_p, pen
         assert tok[b] == int(np.argmax(pen)), "greedy = lowest id among the maxima of the penalised logits"
 
 
+@pytest.mark.parametrize("top_k,top_p,penalty", [(0, 0.9, 1.1), (50, 0.9, 1.0)])
+def test_sampler_filters_beyond_two_to_the_seventeenth_entries(ctx, top_k, top_p, penalty):
+    """From 131072 vocabulary entries on, a histogram bin's probability mass is kept in one 64-bit counter instead of
+    three 32-bit pieces (which could overflow); same rules, same checker."""
+    B, Lh, V = 3, 150, 140000
+    lg = synth.normal(14, "logits_wide", (B, V), 2.5)
+    lg[1] *= 3.0
+    hist = synth.token_ids(14, "hist_wide", (B, Lh + 8), V)
+    ws = (220, 256, 198, 385)
+    cfg = bridge.SamplerConfig.make(temperature=0.0, top_p=top_p, repetition_penalty=penalty, top_k=top_k, whitespace_ids=ws)
+    tok, thr, kept = ctx.sample(ctx.array(lg, "f32"), ctx.array(hist, "i32"), Lh, cfg)
+    tok, thr, kept = tok.download(), thr.download(), kept.download()
+    for b in range(B):
+        pen, filt = ref_filters(lg[b], hist[b, :Lh], penalty, top_k, top_p, ws)
+        exp_kept = int(np.isfinite(filt).sum())
+        assert abs(int(kept[b]) - exp_kept) <= max(1, exp_kept // 500), (b, kept[b], exp_kept)
+        if int(kept[b]) == exp_kept and exp_kept < V:
+            assert abs(thr[b] - filt[np.isfinite(filt)].min()) <= 1e-6 * max(1.0, abs(thr[b]))
+        assert tok[b] == int(np.argmax(pen))
+
+
 def test_sampling_draw_is_seeded_and_stays_in_the_nucleus(ctx):
     B, V = 32, 4096
     base = synth.normal(8, "lg", (1, V), 2.0)
